@@ -1,0 +1,103 @@
+"""The engine's host logic on the CPU: the step function, the cache and the batch description run
+with the plain PyTorch kernels of tests/ref_ops.py in place of the CUDA kernels, and are compared
+with the plain whole-sequence implementation under several ways of cutting the same requests."""
+import random
+
+import pytest
+import torch
+
+import plain_lfm2
+import ref_ops
+from tiny_configs import PAGE_SIZE
+from zig_ai_b200.engine.runner import load_runner
+
+
+def plain_logits(model_dir, tokens):
+    c = plain_lfm2.read_config(model_dir)
+    W = plain_lfm2.read_weights(model_dir)
+    return plain_lfm2.forward(c, W, tokens)
+
+
+def make_runner(model_dir, name, max_tokens=512):
+    return load_runner(model_dir, "float32", max_tokens=max_tokens, max_requests=4,
+                       page_size=PAGE_SIZE[name], device="cpu", ops=ref_ops)
+
+
+def random_tokens(vocab, n, seed):
+    g = random.Random(seed)
+    return [g.randrange(vocab) for _ in range(n)]
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_whole_prompt_matches_plain(tiny_models, name):
+    r = make_runner(tiny_models[name], name)
+    toks = random_tokens(r.model.vocab_size, 37, 1)
+    want = plain_logits(tiny_models[name], toks)
+    r.add_request("a")
+    got = r.step([("a", toks, list(range(len(toks))))])
+    assert got.shape == want.shape
+    assert torch.allclose(got.double(), want, atol=2e-4, rtol=0), (got.double() - want).abs().max()
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_portions_and_decode_match_plain(tiny_models, name):
+    r = make_runner(tiny_models[name], name)
+    toks = random_tokens(r.model.vocab_size, 61, 2)
+    want = plain_logits(tiny_models[name], toks)
+    r.add_request("a")
+    cuts, g, left = [], random.Random(5), len(toks) - 12
+    while left > 0:
+        n = min(g.choice([2, 3, 5, 7, 11]), left)
+        cuts.append(n)
+        left -= n
+    cuts += [1] * 12
+    got, at = [], 0
+    for n in cuts:
+        got.append(r.step([("a", toks[at:at + n], list(range(n)))]))
+        at += n
+    got = torch.cat(got)
+    assert torch.allclose(got.double(), want, atol=2e-4, rtol=0), (got.double() - want).abs().max()
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_mixed_batches_with_page_reuse(tiny_models, name):
+    ps = PAGE_SIZE[name]
+    r = make_runner(tiny_models[name], name, max_tokens=6 * max(ps, 16))
+    V = r.model.vocab_size
+    g = random.Random(9)
+    lengths = [23, 40, 9, 31, 17, 28]
+    reqs = {f"r{i}": random_tokens(V, n, 100 + i) for i, n in enumerate(lengths)}
+    want = {k: plain_logits(tiny_models[name], t) for k, t in reqs.items()}
+    waiting = list(reqs)
+    live, at, got = [], {}, {k: [] for k in reqs}
+    budget_tokens = r.cache.num_pages * ps
+    while waiting or live:
+        # admit while fewer than three live and the pool can hold the whole request
+        while waiting and len(live) < 3:
+            k = waiting[0]
+            held = sum(-(-len(reqs[x]) // ps) * ps for x in live)
+            if held + -(-len(reqs[k]) // ps) * ps > budget_tokens:
+                break
+            waiting.pop(0)
+            r.add_request(k)
+            live.append(k)
+            at[k] = 0
+        entries = []
+        for k in live:
+            left = len(reqs[k]) - at[k]
+            n = 1 if left <= 4 else min(g.choice([1, 2, 4, 6]), left)
+            entries.append((k, reqs[k][at[k]:at[k] + n], list(range(n))))
+        out = r.step(entries)
+        row = 0
+        for k, t, w in entries:
+            got[k].append(out[row:row + len(w)])
+            row += len(w)
+            at[k] += len(t)
+        for k in [k for k in live if at[k] == len(reqs[k])]:
+            r.end_request(k)
+            live.remove(k)
+        r.cache.check()
+    assert r.cache.pages_reused > 0
+    for k in reqs:
+        diff = (torch.cat(got[k]).double() - want[k]).abs().max()
+        assert diff < 2e-4, (k, diff)

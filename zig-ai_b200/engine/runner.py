@@ -1,0 +1,134 @@
+"""The step function: run a batch of (request, its next tokens) from the cache and return the
+logits at the wanted places.
+
+The reference's driver loops the layers for one sequence, a prompt chunk or one token at a time
+(src/main.zig:832-865 and :1138-1217).  Here one call runs, as one flattened batch, prompt
+portions of some requests beside single decoded tokens of others; it runs only the tokens it is
+given, reads everything earlier from the cache, and computes the head only where logits are
+wanted.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..cache import CacheManager, OutOfPages
+from ..models import build_model
+from .batch import StepBatch, pack_step
+
+
+class StepError(ValueError):
+    """A step that cannot run: an unknown token id, a request that is too long, a bad entry."""
+
+
+class ModelRunner:
+    """Owns the model's tensors and the cache, and runs steps."""
+
+    def __init__(self, model, cache: CacheManager, ops, dtype: torch.dtype, device):
+        self.model, self.cache, self.ops, self.dtype, self.device = model, cache, ops, dtype, device
+        self.processed: Dict[object, int] = {}      # request -> tokens in the cache
+        self.steps = 0
+        self.tokens_run = 0
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, request_id) -> None:
+        self.cache.admit(request_id)
+        self.processed[request_id] = 0
+
+    def has_request(self, request_id) -> bool:
+        return request_id in self.processed
+
+    def end_request(self, request_id) -> None:
+        self.cache.release(request_id)
+        del self.processed[request_id]
+
+    # ------------------------------------------------------------------ the step
+    def prepare(self, entries: Sequence[Tuple[object, Sequence[int], Sequence[int]]]) -> StepBatch:
+        """Check the entries, reserve pages and build the batch description.  Nothing is reserved
+        if any entry is refused."""
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        seen = set()
+        V, max_pos = self.model.vocab_size, self.model.spec.max_positions
+        for rid, tokens, _want in entries:
+            if rid in seen:
+                raise StepError(f"request {rid!r} appears twice in one step")
+            seen.add(rid)
+            if rid not in self.processed:
+                raise StepError(f"request {rid!r} was not added")
+            if len(tokens) < 1:
+                raise StepError(f"request {rid!r} brings no tokens")
+            bad = [int(t) for t in tokens if not 0 <= int(t) < V]
+            if bad:
+                raise StepError(f"request {rid!r}: token ids {bad[:8]} are outside the vocabulary of {V}")
+            if self.processed[rid] + len(tokens) > max_pos:
+                raise StepError(f"request {rid!r} would reach {self.processed[rid] + len(tokens)} positions; "
+                                f"the model allows {max_pos}")
+        # all-or-nothing reservation over the whole step
+        demand: Dict[int, int] = {}
+        for rid, tokens, _want in entries:
+            for g, n in self.cache.pages_to_take(rid, self.processed[rid] + len(tokens)).items():
+                demand[g] = demand.get(g, 0) + n
+        for g, n in demand.items():
+            if n > self.cache.groups[g].pool.n_free:
+                raise OutOfPages(f"the step needs {n} more pages of group {g}; "
+                                 f"{self.cache.groups[g].pool.n_free} are free")
+        for rid, tokens, _want in entries:
+            self.cache.reserve(rid, self.processed[rid] + len(tokens))
+        spans = [(rid, self.processed[rid], tokens, want, self.cache.requests[rid].slot)
+                 for rid, tokens, want in entries]
+        rids = [e[0] for e in entries]
+        tables = {}
+        for g in self.cache.paged_groups():
+            width = max(max(len(self.cache.requests[r].tables[g]) for r in rids), 1)
+            tables[g] = self.cache.table_rows(rids, g, width)
+        return pack_step(self.ops, self.dtype, self.device, spans, tables, pin=True)
+
+    def step(self, entries) -> torch.Tensor:
+        """entries: (request, its next tokens, wanted places among them).  Returns 32-bit logits
+        [wanted, vocab] in the order of the entries and of their wanted places."""
+        batch = self.prepare(entries)
+        logits = self.model.forward(batch, self.cache)
+        for rid, tokens, _ in entries:
+            self.processed[rid] += len(tokens)
+        self.steps += 1
+        self.tokens_run += batch.n_tokens
+        return logits
+
+
+def load_runner(model_dir: str, dtype="bfloat16", max_tokens: int = 4096, max_requests: int = 64,
+                page_size: int = 16, device=None, ops=None) -> ModelRunner:
+    """Read config.json, build the model its architecture names, load the tensors and make a cache
+    for `max_tokens` positions."""
+    from ..config import load_config
+    from ..weights import load_tensors
+    tdtype = parse_dtype(dtype)
+    if ops is None:
+        from ..kernels import ops as cuda_ops
+        ops = cuda_ops
+        ops.require()
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device()) if ops.device_type == "cuda" else torch.device("cpu")
+    device = torch.device(device)
+    cfg = load_config(model_dir)
+    model = build_model(cfg)
+    tensors = load_tensors(model_dir, model.param_decls(), tdtype, device)
+    model.bind(tensors, tdtype)
+    num_pages = max(-(-int(max_tokens) // page_size), 1)
+    cache = CacheManager(model.cache_needs(), page_size, num_pages, max_requests, tdtype, device)
+    runner = ModelRunner(model, cache, ops, tdtype, device)
+    runner.config = cfg
+    return runner
+
+
+def parse_dtype(dtype) -> torch.dtype:
+    if isinstance(dtype, torch.dtype):
+        if dtype in (torch.bfloat16, torch.float32):
+            return dtype
+        raise ValueError(f"dtype {dtype} is not supported; use bfloat16 or float32")
+    names = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+             "f32": torch.float32}
+    if dtype not in names:
+        raise ValueError(f"dtype {dtype!r} is not supported; use bfloat16 or float32")
+    return names[dtype]
