@@ -34,6 +34,6 @@ def tiny_models(tmp_path_factory):
     out = {}
     for name, (cfg_dict, seed) in TINY.items():
         d = str(root / name)
-        write_random_model(config_from_dict(cfg_dict), seed, d)
+        write_random_model(config_from_dict(cfg_dict), seed, d, matrix_std="fan_in")
         out[name] = d
     return out

@@ -1,0 +1,239 @@
+"""Each CUDA kernel alone against its plain PyTorch version (tests/ref_ops.py), in 32-bit and in
+bfloat16, at sizes other than the models': head sizes 16..80, odd head counts, widths and
+vocabularies that are no power of two, page sizes 4..32, spans that start and end inside pages."""
+import random
+
+import pytest
+import torch
+
+import ref_ops
+from zig_ai_b200.cache.manager import CacheView
+from zig_ai_b200.engine.batch import pack_step
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def ops():
+    from zig_ai_b200.kernels import ops as o
+    o.require()
+    return o
+
+
+def tol(dtype):
+    return dict(atol=2e-5, rtol=2e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+def make_step(o, dtype, ctx_lens, q_lens, page_size, num_pages, seed, device="cuda", slots=None):
+    """A step over fresh random block tables: request s holds ctx_lens[s] cached positions and
+    brings q_lens[s] new ones."""
+    g = random.Random(seed)
+    free = list(range(1, num_pages))
+    g.shuffle(free)
+    spans, tables = [], []
+    width = max(-(-(c + n) // page_size) for c, n in zip(ctx_lens, q_lens))
+    for s, (c, n) in enumerate(zip(ctx_lens, q_lens)):
+        need = -(-(c + n) // page_size)
+        row = [free.pop() for _ in range(need)]
+        tables.append(row + [0] * (width - need))
+        spans.append((s, c, [0] * n, [], (slots[s] if slots else s + 1)))
+    return pack_step(o, dtype, torch.device(device), spans, {0: tables})
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("N,H,V", [(7, 96, 517), (1, 1000, 33), (33, 2050, 129)])
+def test_embed_and_gather(dtype, N, H, V):
+    o = ops()
+    g = torch.Generator().manual_seed(1)
+    table = torch.randn(V, H, generator=g).to(dtype).cuda()
+    ids = torch.randint(0, V, (N,), generator=g, dtype=torch.int32).cuda()
+    h = o.embed(ids, table)
+    assert torch.equal(h, ref_ops.embed(ids, table))
+    pending = torch.randn(N, H, generator=g).to(dtype).cuda()
+    rows = torch.tensor([N - 1, 0, N // 2], dtype=torch.int32).cuda()
+    assert torch.equal(o.gather_add(h, pending, rows), ref_ops.gather_add(h, pending, rows))
+    assert torch.equal(o.gather_add(h, None, rows), ref_ops.gather_add(h, None, rows))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("N,H,eps", [(5, 96, 1e-6), (3, 1000, 1e-5), (17, 4104, 1e-3), (1, 64, 1e-5)])
+def test_add_rmsnorm(dtype, N, H, eps):
+    o = ops()
+    g = torch.Generator().manual_seed(2)
+    h = (torch.randn(N, H, generator=g) * 3).cuda()
+    delta = torch.randn(N, H, generator=g).to(dtype).cuda()
+    w = (1 + 0.1 * torch.randn(H, generator=g)).cuda()
+    h1, h2 = h.clone(), h.clone()
+    a = o.add_rmsnorm(h1, delta, w, eps, dtype)
+    b = ref_ops.add_rmsnorm(h2, delta, w, eps, dtype)
+    assert torch.equal(h1, h2)                       # the 32-bit residual sum is exact
+    assert torch.allclose(a.float(), b.float(), **tol(dtype))
+    a = o.add_rmsnorm(h1, None, w, eps, dtype)
+    b = ref_ops.add_rmsnorm(h2, None, w, eps, dtype)
+    assert torch.allclose(a.float(), b.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("N,F", [(3, 192), (9, 1000), (1, 4608)])
+def test_silu_mul(dtype, N, F):
+    o = ops()
+    gu = (torch.randn(N, 2 * F, generator=torch.Generator().manual_seed(3)) * 2).to(dtype).cuda()
+    assert torch.allclose(o.silu_mul(gu, F).float(), ref_ops.silu_mul(gu, F).float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("C,L,bias", [(96, 4, True), (64, 3, False), (200, 2, True), (48, 1, False), (130, 7, True)])
+def test_short_conv_spans_and_state(dtype, C, L, bias):
+    """Spans shorter than, equal to and longer than the state, beside single tokens; then a second
+    step that continues from the state the first one left; then a step of single tokens only."""
+    o = ops()
+    g = torch.Generator().manual_seed(4)
+    w = (torch.randn(C, L, generator=g) * 0.3).cuda()
+    b = (torch.randn(C, generator=g) * 0.3).cuda() if bias else None
+    rows = max(L - 1, 1)
+    state_a = torch.randn(6, rows, C, generator=g).cuda()
+    state_b = state_a.clone()
+    for q_lens in ([1, L - 1 if L > 1 else 1, L, 2 * L + 3, 1], [5, 1, 1, 2, 9], [1, 1, 1, 1, 1]):
+        step = make_step(o, dtype, [3] * 5, q_lens, 8, 64, 5)
+        bcx = torch.randn(sum(q_lens), 3 * C, generator=g).to(dtype).cuda()
+        za = o.short_conv(bcx, w, b, state_a, step, L, True)
+        zb = ref_ops.short_conv(bcx, w, b, state_b, step, L, True)
+        assert torch.allclose(za.float(), zb.float(), **tol(dtype)), q_lens
+        assert torch.allclose(state_a, state_b, atol=1e-6, rtol=1e-6), q_lens
+    assert torch.equal(state_a[0], state_b[0])       # the null slot was never touched
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("Hq,Hkv,D,rot,ps", [(4, 2, 16, 16, 16), (3, 1, 32, 32, 8), (5, 5, 48, 24, 4),
+                                              (6, 2, 80, 80, 32), (16, 8, 64, 64, 16)])
+def test_qk_norm_rope_and_page_write(dtype, Hq, Hkv, D, rot, ps):
+    o = ops()
+    g = torch.Generator().manual_seed(6)
+    ctx, q_lens = [0, ps - 1, 3 * ps, min(1000, 60 * ps)], [ps + 3, 2, 1, 5]
+    num_pages = 128
+    step = make_step(o, dtype, ctx, q_lens, ps, num_pages, 7)
+    N = sum(q_lens)
+    qkv = torch.randn(N, (Hq + 2 * Hkv) * D, generator=g).to(dtype).cuda()
+    qw = (1 + 0.1 * torch.randn(D, generator=g)).cuda()
+    kw = (1 + 0.1 * torch.randn(D, generator=g)).cuda()
+    pages_a = torch.zeros(num_pages, 2, Hkv, ps, D, dtype=dtype, device="cuda")
+    pages_b = pages_a.clone()
+    va = CacheView(0, pages_a, step.block_tables[0], ps)
+    vb = CacheView(0, pages_b, step.block_tables[0], ps)
+    qa, ka = o.qk_norm_rope(qkv, qw, kw, 1e-5, rot, 10000.0, step, va, Hq, Hkv, D, True, True, True)
+    qb, kb = ref_ops.qk_norm_rope(qkv, qw, kw, 1e-5, rot, 10000.0, step, vb, Hq, Hkv, D, True, True, True)
+    t = tol(dtype) if dtype == torch.bfloat16 else dict(atol=3e-4, rtol=1e-4)   # 32-bit angles of the plain version at position 1000
+    assert torch.allclose(qa.float(), qb.float(), **t)
+    assert torch.allclose(ka.float(), kb.float(), **t)
+    assert torch.allclose(pages_a.float(), pages_b.float(), **t)
+    assert pages_a[0].abs().sum() == 0                # nothing was written to the null page
+    # without norm and rotation, then written by the separate kernel
+    qa, ka = o.qk_norm_rope(qkv, None, None, 1e-5, 0, 1.0, step, va, Hq, Hkv, D, True, False, True)
+    assert torch.equal(qa, qkv[:, :Hq * D].contiguous())
+    assert torch.equal(ka, qkv[:, Hq * D:(Hq + Hkv) * D].contiguous())
+    pages_c = torch.zeros_like(pages_a)
+    vc = CacheView(0, pages_c, step.block_tables[0], ps)
+    o.kv_write(ka, qkv[:, (Hq + Hkv) * D:], step, vc, Hkv, D)
+    pages_d = torch.zeros_like(pages_a)
+    ref_ops.kv_write(ka, qkv[:, (Hq + Hkv) * D:], step, CacheView(0, pages_d, step.block_tables[0], ps), Hkv, D)
+    assert torch.equal(pages_c, pages_d)
+
+
+def fill_pages(step, ctx, q_lens, ps, Hkv, D, dtype, num_pages, g, boost=None):
+    """Random keys and values at every position the step's requests hold."""
+    pages = torch.zeros(num_pages, 2, Hkv, ps, D, dtype=dtype, device="cuda")
+    bt = step.block_tables[0].cpu()
+    for s, (c, n) in enumerate(zip(ctx, q_lens)):
+        for p in range(c + n):
+            pages[bt[s, p // ps], :, :, p % ps, :] = torch.randn(2, Hkv, D, generator=g).to(dtype).cuda()
+    return pages
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("Hq,Hkv,D,ps,window", [(4, 2, 16, 16, None), (3, 1, 32, 8, None), (6, 3, 48, 4, 7),
+                                                 (8, 2, 80, 32, None), (16, 8, 64, 16, None), (2, 2, 128, 16, 40)])
+def test_paged_attention(dtype, Hq, Hkv, D, ps, window):
+    o = ops()
+    g = torch.Generator().manual_seed(8)
+    ctx, q_lens = [0, ps - 1, 2 * ps, 301, 5], [2 * ps + 1, 2, 1, 1, 37]
+    num_pages = 128
+    step = make_step(o, dtype, ctx, q_lens, ps, num_pages, 9)
+    pages = fill_pages(step, ctx, q_lens, ps, Hkv, D, dtype, num_pages, g)
+    q = torch.randn(sum(q_lens), Hq * D, generator=g).to(dtype).cuda()
+    view = CacheView(0, pages, step.block_tables[0], ps)
+    a = o.paged_attention(q, step, view, Hq, Hkv, D, D ** -0.5, window)
+    b = ref_ops.paged_attention(q, step, view, Hq, Hkv, D, D ** -0.5, window)
+    assert torch.allclose(a.float(), b.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_one_far_key(dtype):
+    """One key among hundreds, at a page's first position far back, is made to stand out by scaling
+    it and the query; the output must be its value."""
+    o = ops()
+    Hq, Hkv, D, ps = 4, 2, 64, 16
+    g = torch.Generator().manual_seed(10)
+    ctx, q_lens = [700], [1]
+    step = make_step(o, dtype, ctx, q_lens, ps, 64, 11)
+    pages = fill_pages(step, ctx, q_lens, ps, Hkv, D, dtype, 64, g)
+    q = torch.randn(1, Hq * D, generator=g).to(dtype).cuda()
+    far = 5 * ps
+    bt = step.block_tables[0].cpu()
+    for h in range(Hkv):
+        pages[bt[0, far // ps], 0, h, 0, :] = (q[0, (h * 2) * D:(h * 2 + 1) * D].float() * 8).to(dtype)
+    view = CacheView(0, pages, step.block_tables[0], ps)
+    a = o.paged_attention(q, step, view, Hq, Hkv, D, D ** -0.5, None).float().view(Hq, D)
+    for h in (0, 2):
+        want = pages[bt[0, far // ps], 1, h // 2, 0, :].float()
+        assert torch.allclose(a[h], want, atol=2e-2), h
+
+
+@pytest.mark.parametrize("R,V", [(1, 517), (5, 65536), (3, 1000)])
+def test_argmax_first_maximum(R, V):
+    o = ops()
+    logits = torch.randn(R, V, generator=torch.Generator().manual_seed(12)).cuda()
+    logits[0, V // 3] = 50.0
+    logits[0, V // 3 + 7] = 50.0                     # a tie: the first index wins
+    assert torch.equal(o.argmax(logits), ref_ops.argmax(logits))
+    assert int(o.argmax(logits)[0]) == V // 3
+
+
+@pytest.mark.parametrize("V", [517, 65536])
+def test_sampling_matches_plain_version(V):
+    o = ops()
+    g = torch.Generator().manual_seed(13)
+    R = 12
+    logits = (torch.randn(R, V, generator=g) * 3).cuda()
+    temperature = torch.tensor([0.0, 1.0, 0.7, 1.5, 1.0, 1.0, 0.9, 1.0, 1.0, 2.0, 1.0, 0.5]).cuda()
+    top_k = torch.tensor([0, 0, 0, 0, 5, 1, 40, 0, 0, 50, 0, 3], dtype=torch.int32).cuda()
+    top_p = torch.tensor([1.0, 1.0, 1.0, 1.0, 1.0, 1.0, 1.0, 0.5, 0.9, 0.8, 0.01, 0.3]).cuda()
+    for trial in range(4):
+        u = torch.rand(R, generator=g).cuda()
+        a = o.sample(logits, temperature, top_k, top_p, u).cpu()
+        b = ref_ops.sample(logits.cpu(), temperature.cpu(), top_k.cpu(), top_p.cpu(), u.cpu())
+        # 32-bit sums may move a boundary by one token where u falls on it: allow it if the token is a neighbour
+        # in cumulative probability
+        for r in range(R):
+            if int(a[r]) != int(b[r]):
+                p = torch.softmax(logits[r].double().cpu() / float(temperature[r]), -1)
+                assert abs(float(p[:int(a[r])].sum()) - float(p[:int(b[r])].sum())) < 1e-3 or \
+                    p[int(a[r])] < 1e-4 or p[int(b[r])] < 1e-4, (trial, r, int(a[r]), int(b[r]))
+
+
+def test_repetition_penalty():
+    o = ops()
+    V = 300
+    logits = torch.randn(2, V, generator=torch.Generator().manual_seed(14)).cuda()
+    want = logits.clone()
+    tokens = torch.tensor([3, 7, 299, 5], dtype=torch.int32).cuda()
+    counts = torch.tensor([1, 3, 1, 2], dtype=torch.int32).cuda()
+    offsets = torch.tensor([0, 3, 4], dtype=torch.int32).cuda()
+    penalty = torch.tensor([1.3, 2.0]).cuda()
+    for r, (a, b) in enumerate([(0, 3), (3, 4)]):
+        for i in range(a, b):
+            for _ in range(int(counts[i])):
+                v = want[r, tokens[i]]
+                want[r, tokens[i]] = v / penalty[r] if v > 0 else v * penalty[r]
+    o.repetition_penalty(logits, tokens, counts, offsets, penalty)
+    assert torch.allclose(logits, want, atol=1e-6)

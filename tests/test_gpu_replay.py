@@ -1,0 +1,67 @@
+"""Whole-model checks through bin/trace_run: the same requests replayed whole, with the last 32
+tokens decoded one by one, in portions of changing size, and mixed with other requests in a pool
+so small that pages are used again; in 32-bit and in bfloat16; all compared with the plain
+implementation (tests/plain_lfm2.py)."""
+import numpy as np
+import pytest
+import torch
+
+import plain_lfm2
+import traces
+from tiny_configs import PAGE_SIZE, TINY
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": [70, 45, 128, 33, 7, 1, 2, 96], "B": [130, 61, 257, 40, 5, 1, 33, 90]}
+
+
+def tolerance(dtype):
+    # of the largest logit of the request: 32-bit rounding through a few hundred-term sums and a
+    # handful of layers; bfloat16 (8 bits of mantissa) rounding of every stored activation
+    return 5e-5 if dtype == "float32" else 3e-2
+
+
+@pytest.fixture(scope="module")
+def plain(tiny_models):
+    out = {}
+    for name, d in tiny_models.items():
+        c, W = plain_lfm2.read_config(d), plain_lfm2.read_weights(d)
+        reqs = traces.requests_for(c["vocab_size"], LENGTHS[name], 77)
+        out[name] = (reqs, {k: plain_lfm2.forward(c, W, t).numpy() for k, t in reqs.items()})
+    return out
+
+
+def compare(got, reqs, want, tag, dtype):
+    tol = tolerance(dtype)
+    for k, toks in reqs.items():
+        scale = max(float(np.abs(want[k]).max()), 1e-6)
+        for p in range(len(toks)):
+            row = got[(tag + k, p)]
+            err = float(np.abs(row - want[k][p]).max()) / scale
+            assert err < tol, f"{dtype} schedule '{tag}' request {k} position {p}: error {err:.3e} of the largest logit"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_schedules_agree_with_plain(tiny_models, plain, tmp_path, name, dtype):
+    reqs, want = plain[name]
+    vocab = TINY[name][0]["vocab_size"]
+    steps = traces.number(traces.whole(reqs) + traces.decode_tail(reqs) + traces.portions(reqs, 3))
+    got = traces.run_trace(tiny_models[name], dtype, steps, max_tokens=512, out_dir=str(tmp_path / "o"),
+                           vocab=vocab, page_size=PAGE_SIZE[name])
+    for tag in "wdp":
+        compare(got, reqs, want, tag, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_mixed_batches_in_a_small_pool(tiny_models, plain, tmp_path, name, dtype):
+    reqs, want = plain[name]
+    vocab = TINY[name][0]["vocab_size"]
+    longest = -(-max(len(t) for t in reqs.values()) // 64) * 64
+    max_tokens = longest + 128                       # a few requests at most: pages must be used again
+    steps = traces.number(traces.mixed(reqs, 5, max_tokens))
+    assert max(len(s["entries"]) for s in steps) >= 2
+    got = traces.run_trace(tiny_models[name], dtype, steps, max_tokens=max_tokens, out_dir=str(tmp_path / "o"),
+                           vocab=vocab, page_size=PAGE_SIZE[name])
+    compare(got, reqs, want, "m", dtype)

@@ -1,0 +1,121 @@
+// The ShortConv mixer between its two projections: u = B * x~, a causal depthwise convolution of u
+// over the request's conv state followed by this step's rows, and the gate z = C * y.
+//
+//   y[t, c] = sum_j w[c, j] * u_[i + j, c] (+ b[c]),   u_ = state rows 0..L-2 ++ u rows of the span
+//
+// with i the row's index inside its request's span, so tap L-1 multiplies the current token (the
+// indexing of the reference's conv1dSiluKernel, src/cuda/layer_kernels.cu:206-213, which adds a
+// SiLU that the LFM2 operator does not have).  The new state is the last L-1 rows of u_
+// (ibid. :216-221).  The reference passes one buffer as old and new state although its kernel
+// forbids that (src/transformer/short_conv.zig:408-415 against layer_kernels.cu:191); here the
+// rows are computed by one kernel that only reads the state, and the state is replaced by a second
+// kernel in which each thread first reads everything it needs and then writes.  When every span
+// is a single token both happen in one kernel, thread by thread.
+// The state is 32-bit and holds u exactly as the products of the stored B and x~, so a row's
+// result does not depend on whether its neighbours come from the state or from the same step.
+#include "common.cuh"
+
+#define ZAI_MAX_TAPS 16
+
+template <typename T>
+__global__ void conv_rows_kernel(T* __restrict__ z, const T* __restrict__ bcx, const float* __restrict__ w,
+                                 const float* __restrict__ bias, const float* __restrict__ state,
+                                 const int* __restrict__ seq_idx, const int* __restrict__ cu_q,
+                                 const int* __restrict__ slot_ids, int C, int L, int state_rows) {
+    const int t = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int s = seq_idx[t];
+    const int i = t - cu_q[s];
+    const float* st = state + ((size_t)slot_ids[s] * state_rows) * C;
+    float y = bias ? bias[c] : 0.f;
+    for (int j = 0; j < L; ++j) {
+        const int r = i + j - (L - 1);                    // row of the span, negative: from the state
+        float u;
+        if (r >= 0) {
+            const T* row = bcx + (size_t)(t - i + r) * 3 * C;
+            u = to_float(row[c]) * to_float(row[2 * C + c]);
+        } else {
+            u = st[(size_t)(i + j) * C + c];
+        }
+        y += w[(size_t)c * L + j] * u;
+    }
+    const float gate = to_float(bcx[(size_t)t * 3 * C + C + c]);
+    z[(size_t)t * C + c] = from_float<T>(gate * y);
+}
+
+template <typename T>
+__global__ void conv_state_kernel(const T* __restrict__ bcx, float* __restrict__ state,
+                                  const int* __restrict__ cu_q, const int* __restrict__ slot_ids,
+                                  int C, int L, int state_rows) {
+    const int s = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int a = cu_q[s], n = cu_q[s + 1] - a;
+    float* st = state + ((size_t)slot_ids[s] * state_rows) * C;
+    float keep[ZAI_MAX_TAPS];
+#pragma unroll
+    for (int r = 0; r < ZAI_MAX_TAPS; ++r) {
+        if (r < L - 1) {
+            const int src = n + r;                         // index into u_ = state ++ u
+            if (src < L - 1) {
+                keep[r] = st[(size_t)src * C + c];
+            } else {
+                const T* row = bcx + (size_t)(a + src - (L - 1)) * 3 * C;
+                keep[r] = to_float(row[c]) * to_float(row[2 * C + c]);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < ZAI_MAX_TAPS; ++r)
+        if (r < L - 1) st[(size_t)r * C + c] = keep[r];
+}
+
+// Every span is one token: row s belongs to request s.
+template <typename T>
+__global__ void conv_decode_kernel(T* __restrict__ z, const T* __restrict__ bcx, const float* __restrict__ w,
+                                   const float* __restrict__ bias, float* __restrict__ state,
+                                   const int* __restrict__ slot_ids, int C, int L, int state_rows, int write_state) {
+    const int s = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    float* st = state + ((size_t)slot_ids[s] * state_rows) * C;
+    const T* row = bcx + (size_t)s * 3 * C;
+    const float u = to_float(row[c]) * to_float(row[2 * C + c]);
+    float y = bias ? bias[c] : 0.f;
+    float prev[ZAI_MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < ZAI_MAX_TAPS; ++j)
+        if (j < L - 1) {
+            prev[j] = st[(size_t)j * C + c];
+            y += w[(size_t)c * L + j] * prev[j];
+        }
+    y += w[(size_t)c * L + (L - 1)] * u;
+    z[(size_t)s * C + c] = from_float<T>(to_float(row[C + c]) * y);
+    if (write_state) {
+#pragma unroll
+        for (int j = 0; j < ZAI_MAX_TAPS; ++j)
+            if (j < L - 1) st[(size_t)j * C + c] = (j + 1 < L - 1) ? prev[j + 1] : u;
+    }
+}
+
+ZAI_API int zai_short_conv(void* z, const void* bcx, int dtype, const float* w, const float* bias, float* state,
+                           const int* seq_idx, const int* cu_q, const int* slot_ids, int N, int S, int C, int L,
+                           int state_rows, int decode_only, int write_state, cudaStream_t stream) {
+    if (N <= 0) return ZAI_OK;
+    if (L < 1 || L > ZAI_MAX_TAPS || state_rows < L - 1) return ZAI_BAD_SIZE;
+    const int threads = 128;
+    const unsigned bx = (unsigned)((C + threads - 1) / threads);
+    if (decode_only) {
+        ZAI_DISPATCH(dtype, conv_decode_kernel<T><<<dim3(S, bx), threads, 0, stream>>>(
+            (T*)z, (const T*)bcx, w, bias, state, slot_ids, C, L, state_rows, write_state));
+        return launch_status();
+    }
+    ZAI_DISPATCH(dtype, conv_rows_kernel<T><<<dim3(N, bx), threads, 0, stream>>>(
+        (T*)z, (const T*)bcx, w, bias, state, seq_idx, cu_q, slot_ids, C, L, state_rows));
+    int e = launch_status();
+    if (e || !write_state || L == 1) return e;
+    ZAI_DISPATCH(dtype, conv_state_kernel<T><<<dim3(S, bx), threads, 0, stream>>>(
+        (const T*)bcx, state, cu_q, slot_ids, C, L, state_rows));
+    return launch_status();
+}

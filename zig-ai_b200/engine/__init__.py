@@ -1,0 +1,3 @@
+"""The step function, the scheduler above it, generation and trace replay."""
+from .batch import StepBatch, pack_step
+from .runner import ModelRunner, StepError, load_runner, parse_dtype

@@ -1,0 +1,253 @@
+"""The kernels as functions on torch CUDA tensors.
+
+One function per kernel (or per small group launched together); every function launches on the
+current CUDA stream and allocates its outputs with torch.  There is no CPU path: calling any of
+these without the compiled libraries or without a CUDA device raises.  Plain matrix products go to
+cuBLAS through `torch.matmul`, as the reference sends every projection to `cublasSgemm_v2`
+(src/matmul/cublas.zig:515-548); the 32-bit mode runs them as true 32-bit products (TF32 off).
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+from . import build
+
+device_type = "cuda"
+
+_F32, _BF16 = 0, 1
+_P, _I, _F = c_void_p, c_int, c_float
+
+_SIGNATURES = {
+    "embed": {
+        "zai_embed": [_P, _P, _I, _P, _I, _I, _I, _P],
+        "zai_gather_add": [_P, _P, _P, _I, _P, _I, _I, _P],
+    },
+    "norm": {"zai_add_rmsnorm": [_P, _P, _P, _P, _I, _F, _I, _I, _P]},
+    "activation": {"zai_silu_mul": [_P, _P, _I, _I, _I, _P]},
+    "shortconv": {"zai_short_conv": [_P, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P]},
+    "rope_kv": {
+        "zai_qk_norm_rope": [_P, _I, _I, _P, _P, _F, _P, _I, _P, _P, _P, _I, _P, _I, _P, _P,
+                             _I, _I, _I, _I, _I, _I, _P],
+        "zai_kv_write": [_P, _I, _P, _I, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P],
+    },
+    "attention": {
+        "zai_paged_attention_general": [_P, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
+    },
+    "sampling": {
+        "zai_argmax": [_P, _P, _I, _I, _P],
+        "zai_repetition_penalty": [_P, _P, _P, _P, _P, _I, _I, _P],
+        "zai_sample": [_P, _P, _P, _P, _P, _P, _I, _I, _P],
+    },
+}
+
+_fns = {}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _fn(lib_name: str, fn_name: str):
+    f = _fns.get(fn_name)
+    if f is None:
+        lib = build.load(lib_name)
+        f = getattr(lib, fn_name)
+        f.argtypes = _SIGNATURES[lib_name][fn_name]
+        f.restype = c_int
+        _fns[fn_name] = f
+    return f
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code == -1:
+        raise KernelError(f"{what}: element type not supported by the kernel")
+    if code == -2:
+        raise KernelError(f"{what}: a size is outside what the kernel supports")
+    raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+def require() -> None:
+    """Fail loudly unless a CUDA device is present and the core libraries load."""
+    if not torch.cuda.is_available():
+        raise KernelError("no CUDA device: this engine has no CPU path")
+    for lib in ("embed", "norm", "activation", "shortconv", "rope_kv", "attention", "sampling"):
+        build.load(lib)
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return _F32
+    if t.dtype == torch.bfloat16:
+        return _BF16
+    raise KernelError(f"element type {t.dtype} is not supported")
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _cuda(*tensors):
+    for t in tensors:
+        if t is not None and (not t.is_cuda or not t.is_contiguous()):
+            raise KernelError("kernels take contiguous CUDA tensors")
+
+
+# ----------------------------------------------------------------------------- kernels
+def has_fused_decode(w, x):
+    return False
+
+
+def embed(ids, table):
+    _cuda(ids, table)
+    N, (V, H) = ids.numel(), table.shape
+    out = torch.empty((N, H), dtype=torch.float32, device=table.device)
+    _check(_fn("embed", "zai_embed")(_ptr(out), _ptr(table), _dt(table), _ptr(ids), N, H, V, _stream()), "embed")
+    return out
+
+
+def gather_add(h, pending, rows):
+    _cuda(h, pending, rows)
+    R, H = rows.numel(), h.shape[1]
+    out = torch.empty((R, H), dtype=torch.float32, device=h.device)
+    pd = _dt(pending) if pending is not None else _F32
+    _check(_fn("embed", "zai_gather_add")(_ptr(out), _ptr(h), _ptr(pending), pd, _ptr(rows), R, H, _stream()),
+           "gather_add")
+    return out
+
+
+def add_rmsnorm(h, delta, w, eps, out_dtype):
+    _cuda(h, delta, w)
+    if h.dtype != torch.float32 or w.dtype != torch.float32:
+        raise KernelError("the residual stream and norm weights are 32-bit")
+    N, H = h.shape
+    out = torch.empty((N, H), dtype=out_dtype, device=h.device)
+    if delta is not None and delta.dtype != out_dtype:
+        raise KernelError("the pending term should have the model's dtype")
+    _check(_fn("norm", "zai_add_rmsnorm")(_ptr(h), _ptr(delta), _ptr(w), _ptr(out), _dt(out), float(eps), N, H,
+                                          _stream()), "add_rmsnorm")
+    return out
+
+
+def linear(x, w, out_dtype=None):
+    """x [N, K] times w [O, K] transposed.  A matrix kept in 32-bit is multiplied in 32-bit."""
+    out_dtype = out_dtype or x.dtype
+    if x.dtype == torch.float32 or w.dtype == torch.float32 or out_dtype == torch.float32:
+        if torch.backends.cuda.matmul.allow_tf32:
+            torch.backends.cuda.matmul.allow_tf32 = False
+        if x.dtype == w.dtype == torch.bfloat16:
+            # 32-bit logits from 16-bit operands: the product itself accumulates in 32-bit
+            return torch.mm(x, w.t(), out_dtype=torch.float32)
+        return torch.matmul(x.float(), w.float().t()).to(out_dtype)
+    return torch.matmul(x, w.t())
+
+
+def silu_mul(gu, ff_dim):
+    _cuda(gu)
+    N = gu.shape[0]
+    out = torch.empty((N, ff_dim), dtype=gu.dtype, device=gu.device)
+    _check(_fn("activation", "zai_silu_mul")(_ptr(out), _ptr(gu), _dt(gu), N, ff_dim, _stream()), "silu_mul")
+    return out
+
+
+def short_conv(bcx, conv_w, conv_b, state, step, taps, write_state=True):
+    _cuda(bcx, conv_w, conv_b, state)
+    N, C = bcx.shape[0], bcx.shape[1] // 3
+    z = torch.empty((N, C), dtype=bcx.dtype, device=bcx.device)
+    if state.dtype != torch.float32 or state.shape[-1] != C:
+        raise KernelError("the conv state is 32-bit [slots, rows, channels]")
+    _check(_fn("shortconv", "zai_short_conv")(
+        _ptr(z), _ptr(bcx), _dt(bcx), _ptr(conv_w), _ptr(conv_b), _ptr(state), _ptr(step.seq_idx), _ptr(step.cu_q),
+        _ptr(step.slot_ids), N, step.n_seqs, C, int(taps), state.shape[1], int(step.decode_only),
+        int(write_state), _stream()), "short_conv")
+    return z
+
+
+_inv_freq_cache = {}
+
+
+def inverse_frequencies(rotary_dim: int, theta: float, device) -> torch.Tensor:
+    """theta^(-2i/n) for i < n/2, computed in 64-bit."""
+    key = (rotary_dim, float(theta), str(device))
+    t = _inv_freq_cache.get(key)
+    if t is None:
+        i = torch.arange(rotary_dim // 2, dtype=torch.float64)
+        t = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -2.0 * i / rotary_dim).to(device)
+        _inv_freq_cache[key] = t
+    return t
+
+
+def qk_norm_rope(qkv, q_w, k_w, eps, rotary_dim, theta, step, cache, heads, kv_heads, head_dim,
+                 has_kv=True, write=True, return_k=False):
+    _cuda(qkv, q_w, k_w)
+    N, cols = qkv.shape
+    q = torch.empty((N, heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    k_out = torch.empty((N, kv_heads * head_dim), dtype=qkv.dtype, device=qkv.device) if (return_k and has_kv) else None
+    inv = inverse_frequencies(rotary_dim, theta, qkv.device) if rotary_dim else None
+    do_write = bool(write and has_kv)
+    pages, bt = cache.pages, cache.block_table
+    if do_write and pages.dtype != qkv.dtype:
+        raise KernelError("the pages and the activations should have one dtype")
+    _check(_fn("rope_kv", "zai_qk_norm_rope")(
+        _ptr(qkv), cols, _dt(qkv), _ptr(q_w), _ptr(k_w), float(eps), _ptr(inv), int(rotary_dim),
+        _ptr(step.positions), _ptr(step.seq_idx), _ptr(bt) if do_write else None,
+        bt.shape[1] if do_write else 0, _ptr(pages) if do_write else None, cache.page_size, _ptr(q), _ptr(k_out),
+        N, heads, kv_heads, head_dim, int(has_kv), int(do_write), _stream()), "qk_norm_rope")
+    return q, k_out
+
+
+def kv_write(k, v, step, cache, kv_heads, head_dim):
+    if k.stride(-1) != 1 or v.stride(-1) != 1:
+        raise KernelError("k and v rows should be contiguous")
+    N = k.shape[0]
+    _check(_fn("rope_kv", "zai_kv_write")(
+        _ptr(k), k.stride(0), _ptr(v), v.stride(0), _dt(k), _ptr(step.positions), _ptr(step.seq_idx),
+        _ptr(cache.block_table), cache.block_table.shape[1], _ptr(cache.pages), cache.page_size, N, kv_heads,
+        head_dim, _stream()), "kv_write")
+
+
+def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=None):
+    _cuda(q)
+    N = q.shape[0]
+    out = torch.empty((N, heads * head_dim), dtype=q.dtype, device=q.device)
+    if cache.pages.dtype != q.dtype:
+        raise KernelError("the pages and the queries should have one dtype")
+    _check(_fn("attention", "zai_paged_attention_general")(
+        _ptr(out), _ptr(q), _ptr(cache.pages), _dt(q), _ptr(cache.block_table), cache.block_table.shape[1],
+        _ptr(step.positions), _ptr(step.seq_idx), cache.page_size, N, heads, kv_heads, head_dim, float(scale),
+        int(window or 0), _stream()), "paged_attention")
+    return out
+
+
+def argmax(logits):
+    _cuda(logits)
+    R, V = logits.shape
+    out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    _check(_fn("sampling", "zai_argmax")(_ptr(out), _ptr(logits), R, V, _stream()), "argmax")
+    return out
+
+
+def repetition_penalty(logits, tokens, counts, offsets, penalty):
+    """In place: logits[r, tokens[i]] is penalised counts[i] times for offsets[r] <= i < offsets[r+1]."""
+    _cuda(logits, tokens, counts, offsets, penalty)
+    R, V = logits.shape
+    _check(_fn("sampling", "zai_repetition_penalty")(_ptr(logits), _ptr(tokens), _ptr(counts), _ptr(offsets),
+                                                     _ptr(penalty), R, V, _stream()), "repetition_penalty")
+    return logits
+
+
+def sample(logits, temperature, top_k, top_p, u):
+    _cuda(logits, temperature, top_k, top_p, u)
+    R, V = logits.shape
+    out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    _check(_fn("sampling", "zai_sample")(_ptr(out), _ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p),
+                                         _ptr(u), R, V, _stream()), "sample")
+    return out
