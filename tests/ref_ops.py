@@ -208,3 +208,15 @@ def sample(logits, temperature, top_k, top_p, u):
         hit = (c >= target).nonzero()
         out[r] = int(hit[0]) if hit.numel() else V - 1
     return out
+
+
+def repetition_penalty(logits, tokens, counts, offsets, penalty):
+    off = offsets.tolist()
+    for r in range(logits.shape[0]):
+        p = float(penalty[r])
+        for i in range(off[r], off[r + 1]):
+            t = int(tokens[i])
+            for _ in range(int(counts[i])):
+                v = logits[r, t]
+                logits[r, t] = v / p if v > 0 else (v * p if v < 0 else v)
+    return logits

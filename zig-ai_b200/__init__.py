@@ -14,5 +14,9 @@ from . import config, parts, models, cache  # noqa: F401
 from .config import ConfigError, load_config, register_architecture
 from .parts import register_part
 from .models import build_model
+from .engine import Engine, generate, load_runner
+from .sampling import SamplingParams
+from .weights import write_random_model
 
-__all__ = ["ConfigError", "load_config", "register_architecture", "register_part", "build_model"]
+__all__ = ["ConfigError", "load_config", "register_architecture", "register_part", "build_model", "Engine",
+           "generate", "load_runner", "SamplingParams", "write_random_model"]

@@ -36,6 +36,11 @@ class ModelRunner:
         self.cache.admit(request_id)
         self.processed[request_id] = 0
 
+    admit = add_request
+
+    def release(self, request_id) -> None:
+        self.end_request(request_id)
+
     def has_request(self, request_id) -> bool:
         return request_id in self.processed
 
