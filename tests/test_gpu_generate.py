@@ -1,0 +1,96 @@
+"""Generation through the Python entry point on the GPU, long decoding, and the command line."""
+import os
+import random
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_lfm2
+import traces
+from tiny_configs import PAGE_SIZE, TINY
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def plain_greedy(model_dir, prompt, n):
+    c, W = plain_lfm2.read_config(model_dir), plain_lfm2.read_weights(model_dir)
+    toks = list(prompt)
+    for _ in range(n):
+        toks.append(plain_lfm2.greedy(plain_lfm2.forward(c, W, toks)[-1]))
+    return toks[len(prompt):]
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_float32_matches_plain(tiny_models, name):
+    import zig_ai_b200 as z
+    g = random.Random(3)
+    V = TINY[name][0]["vocab_size"]
+    prompts = [[g.randrange(V) for _ in range(n)] for n in (7, 13, 1)]
+    eng = z.Engine(tiny_models[name], "float32", max_num_seqs=3, max_batched_tokens=6, max_model_len=64,
+                   page_size=PAGE_SIZE[name])
+    got = eng.generate(prompts, max_new_tokens=8, temperature=0.0)
+    for p, out in zip(prompts, got):
+        assert out == plain_greedy(tiny_models[name], p, 8)
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_bfloat16_picks_a_plain_maximum(tiny_models, name):
+    """In bfloat16 a near-tie may fall the other way: every generated token must be within the
+    bfloat16 tolerance of the plain implementation's best logit at its place."""
+    import zig_ai_b200 as z
+    g = random.Random(4)
+    V = TINY[name][0]["vocab_size"]
+    prompts = [[g.randrange(V) for _ in range(n)] for n in (5, 17, 33, 1)]
+    eng = z.Engine(tiny_models[name], "bfloat16", max_num_seqs=4, max_batched_tokens=10, max_model_len=96,
+                   page_size=PAGE_SIZE[name])
+    got = eng.generate(prompts, max_new_tokens=10, temperature=0.0)
+    c, W = plain_lfm2.read_config(tiny_models[name]), plain_lfm2.read_weights(tiny_models[name])
+    for p, out in zip(prompts, got):
+        assert len(out) == 10
+        logits = plain_lfm2.forward(c, W, p + out)
+        for i, tok in enumerate(out):
+            row = logits[len(p) + i - 1]
+            assert float(row.max() - row[tok]) <= 8e-2 * float(row.abs().max()), (i, tok)
+
+
+def test_sampled_generation_is_fixed_by_the_seed_and_not_by_batching(tiny_models):
+    import zig_ai_b200 as z
+    g = random.Random(5)
+    prompts = [[g.randrange(517) for _ in range(n)] for n in (1, 5, 17, 33)]
+    kw = dict(max_new_tokens=10, temperature=1.0, seed=7)
+    together = z.Engine(tiny_models["B"], "float32", max_num_seqs=4, max_batched_tokens=10, max_model_len=64,
+                        page_size=8).generate(prompts, **kw)
+    alone = [z.Engine(tiny_models["B"], "float32", max_num_seqs=1, max_batched_tokens=64, max_model_len=64,
+                      page_size=8).generate([p], **dict(kw, seed=7 + i))[0] for i, p in enumerate(prompts)]
+    assert together == alone
+    tight = z.Engine(tiny_models["B"], "float32", max_num_seqs=4, max_batched_tokens=16, max_model_len=64,
+                     max_tokens=56, page_size=8)
+    assert tight.generate(prompts, **kw) == alone and tight.stats()["preemptions"] > 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(tiny_models, tmp_path, dtype):
+    """One request decoded token by token from its first token for 600 positions."""
+    d = tiny_models["B"]
+    c, W = plain_lfm2.read_config(d), plain_lfm2.read_weights(d)
+    toks = traces.requests_for(c["vocab_size"], [600], 9)["q0"]
+    want = plain_lfm2.forward(c, W, toks).numpy()
+    steps = traces.number(traces.decode_tail({"q0": toks}, tail=600))
+    got = traces.run_trace(d, dtype, steps, max_tokens=640, out_dir=str(tmp_path / "o"), vocab=c["vocab_size"], page_size=8)
+    for p in range(600):
+        traces.check_row(got[("dq0", p)], want[p], dtype, f"{dtype} position {p}")
+
+
+def test_command_line(tiny_models):
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "zig-ai-engine"), "-m", tiny_models["A"],
+                          "--prompt", "5,17,3", "-n", "6", "--temperature", "0", "--dtype", "float32"],
+                         capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr
+    line = next(l for l in out.stdout.splitlines() if l.startswith("[0]"))
+    ids = [int(x) for x in line.split(")")[1].split()]
+    assert ids == plain_greedy(tiny_models["A"], [5, 17, 3], 6)
+    assert "decode:" in out.stdout and "prefill:" in out.stdout

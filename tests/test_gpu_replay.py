@@ -15,12 +15,6 @@ pytestmark = pytest.mark.gpu
 LENGTHS = {"A": [70, 45, 128, 33, 7, 1, 2, 96], "B": [130, 61, 257, 40, 5, 1, 33, 90]}
 
 
-def tolerance(dtype):
-    # of the largest logit of the request: 32-bit rounding through a few hundred-term sums and a
-    # handful of layers; bfloat16 (8 bits of mantissa) rounding of every stored activation
-    return 5e-5 if dtype == "float32" else 3e-2
-
-
 @pytest.fixture(scope="module")
 def plain(tiny_models):
     out = {}
@@ -32,13 +26,16 @@ def plain(tiny_models):
 
 
 def compare(got, reqs, want, tag, dtype):
-    tol = tolerance(dtype)
     for k, toks in reqs.items():
-        scale = max(float(np.abs(want[k]).max()), 1e-6)
         for p in range(len(toks)):
-            row = got[(tag + k, p)]
-            err = float(np.abs(row - want[k][p]).max()) / scale
-            assert err < tol, f"{dtype} schedule '{tag}' request {k} position {p}: error {err:.3e} of the largest logit"
+            traces.check_row(got[(tag + k, p)], want[k][p], dtype, f"{dtype} schedule '{tag}' request {k} position {p}")
+
+
+def compare_schedules(got, reqs, tag_a, tag_b, dtype):
+    for k, toks in reqs.items():
+        for p in range(len(toks)):
+            traces.check_same(got[(tag_a + k, p)], got[(tag_b + k, p)], dtype,
+                              f"{dtype} schedules '{tag_a}'/'{tag_b}' request {k} position {p}")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -51,6 +48,8 @@ def test_schedules_agree_with_plain(tiny_models, plain, tmp_path, name, dtype):
                            vocab=vocab, page_size=PAGE_SIZE[name])
     for tag in "wdp":
         compare(got, reqs, want, tag, dtype)
+    compare_schedules(got, reqs, "w", "d", dtype)
+    compare_schedules(got, reqs, "w", "p", dtype)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -127,3 +127,33 @@ def run_trace(model_dir, dtype, steps, max_tokens, out_dir, vocab, page_size=16,
         if p.poll() is None:
             p.kill()
     return got
+
+
+# How far logits may be from the plain implementation's, per row of logits.
+#   float32: rounding of sums of a few hundred terms through a handful of layers, far below 5e-5 of
+#   the largest logit.
+#   bfloat16: every stored activation is rounded to 8 bits of mantissa (relative 2^-9); over the
+#   layers this adds up to a relative error of the row (L2) near 2 % on average with a tail to 5 %
+#   among 600 rows, the same whether the request runs whole or token by token.  A fault of the
+#   cache or the batch moves a row by tens of per cent; faults smaller than this noise are the 32-bit
+#   path's to show.  Rows of different ways of cutting the same request are also compared with each
+#   other, more tightly.
+def row_error(got, want):
+    """(relative L2 error of the row, largest absolute error over the row's largest |logit|)"""
+    err = np.abs(got.astype(np.float64) - want)
+    return float(np.linalg.norm(err) / max(np.linalg.norm(want), 1e-30)), float(err.max() / max(np.abs(want).max(), 1e-30))
+
+
+def check_row(got, want, dtype, where):
+    l2, mx = row_error(got, want)
+    if dtype == "float32":
+        assert mx < 5e-5, f"{where}: error {mx:.3e} of the row's largest logit"
+    else:
+        assert l2 < 6e-2 and mx < 8e-2, f"{where}: relative L2 error {l2:.3e}, largest {mx:.3e}"
+
+
+def check_same(a, b, dtype, where):
+    """Two ways of running the same position."""
+    l2, mx = row_error(a, b.astype(np.float64))
+    lim = 2e-5 if dtype == "float32" else 2.5e-2
+    assert l2 < lim and mx < lim, f"{where}: two ways of cutting differ by L2 {l2:.3e}, largest {mx:.3e}"
