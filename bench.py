@@ -1,0 +1,261 @@
+#!/usr/bin/env python3
+"""Benchmark: decode tokens per second of the LFM2-350M shape on one B200, with prefill, roofline
+and end-to-end figures on the same JSON line.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one decode step of a batch of 8 requests whose contexts lie between 2048 and 4096
+tokens; weights are random (seeded), token ids are random: there is no dataset.  `value` times the
+step function and the sampling kernel on the device with CUDA events; `e2e` times the same steps
+through `Engine.step()`, the call a user makes, with host token lists in and out.  The decode step
+reads about 0.7 GB of weights, more than the 126 MB L2, so consecutive steps cannot be served from L2.
+"""
+import argparse
+import json
+import os
+import random
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LFM2_350M = {
+    "architectures": ["Lfm2ForCausalLM"], "hidden_size": 1024, "num_hidden_layers": 16,
+    "full_attn_idxs": [2, 5, 8, 10, 12, 14], "num_attention_heads": 16, "num_key_value_heads": 8, "head_dim": 64,
+    "block_ff_dim": 6656, "block_auto_adjust_ff_dim": True, "block_multiple_of": 256, "vocab_size": 65536,
+    "rope_theta": 1000000.0, "conv_L_cache": 3, "conv_bias": False, "use_qk_norm": True, "norm_eps": 1e-5,
+    "tie_embedding": True, "max_position_embeddings": 128000,
+}
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    hbm, flops, src = 6650.0, 1590.0, "fallback"
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        hbm = float(d.get("hbm_gbs", hbm))
+        flops = float(d.get("bf16_tflops", flops))
+        src = "measured"
+    except (OSError, ValueError):
+        pass
+    return hbm, flops, src
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 6 for n, v in zip(names, r[2:6]) if v.lower().startswith("active")})
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+def model_numbers(cfg):
+    """Matrix parameters read once per decode step, their flops per token, KV bytes per token."""
+    H, F, V = cfg.hidden_size, cfg.ff_dim, cfg.vocab_size
+    D, Hq, Hkv = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
+    n_attn = len(cfg.attention_layers)
+    n_conv = cfg.num_hidden_layers - n_attn
+    per_layer_ff = 3 * H * F
+    conv = 3 * H * H + H * H
+    attn = (Hq + 2 * Hkv) * D * H + Hq * D * H
+    layer_params = cfg.num_hidden_layers * per_layer_ff + n_conv * conv + n_attn * attn
+    head = V * H
+    kv_bytes_per_token = n_attn * 2 * Hkv * D * 2
+    state_bytes = n_conv * (cfg.conv_L_cache - 1) * H * 4
+    return dict(layer_params=layer_params, head_params=head, kv_bytes_per_token=kv_bytes_per_token,
+                state_bytes=state_bytes, n_attn=n_attn, attn_dims=(Hq, D))
+
+
+def decode_requests(eng, B, steps_needed, seed):
+    """Add B requests with contexts spread over 2048..CONTEXT and run until all of them decode."""
+    from zig_ai_b200.sampling import SamplingParams
+    g = random.Random(seed)
+    hi = CONTEXT - steps_needed - 160          # room for the tokens decoded while later requests still prefill
+    lens = [2048 + (hi - 2048) * i // max(B - 1, 1) for i in range(B)] if B > 1 else [(2048 + hi) // 2]
+    V = eng.config.vocab_size
+    ids = [eng.add_request([g.randrange(V) for _ in range(n)],
+                           SamplingParams(temperature=0.0, max_new_tokens=CONTEXT - n)) for n in lens]
+    while any(eng.requests[i].computed < len(eng.requests[i].prompt) or not eng.requests[i].output for i in ids):
+        eng.step()
+    return ids
+
+
+def time_decode(eng, B, steps, warmup, clocks=None):
+    """Device-timed decode steps of batch B (step function + sampling kernel, no host read-back),
+    then the same number of steps through Engine.step().  Returns (ms/step device, ms/step e2e,
+    context tokens read per step, launches per step, h2d bytes, d2h bytes)."""
+    import torch
+    from zig_ai_b200.kernels import ops
+    ids = decode_requests(eng, B, 2 * (steps + warmup) + 4, seed=B)
+    reqs = [eng.requests[i] for i in ids]
+    runner = eng.runner
+    ctx_tokens = sum(r.computed for r in reqs)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def device_step(k):
+        entries = [(r.request_id, [(7 * k + j) % 1000], [0]) for j, r in enumerate(reqs)]
+        return ops.argmax(runner.step(entries))
+    for k in range(warmup):
+        device_step(k)
+    torch.cuda.synchronize()
+    launches0 = ops.launches
+    if clocks:
+        clocks.start()
+    start.record()
+    for k in range(steps):
+        device_step(warmup + k)
+    stop.record()
+    torch.cuda.synchronize()
+    dev_ms = start.elapsed_time(stop) / steps
+    launches = (ops.launches - launches0) / steps
+    # the scheduler's view has to follow what was run behind its back
+    for r in reqs:
+        r.computed = runner.processed[r.request_id]
+        r.output += [0] * (r.computed + 1 - len(r.prompt) - len(r.output))
+    for _ in range(warmup):
+        eng.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        eng.step()
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / steps
+    clock_info = clocks.stop() if clocks else None
+    for r in list(reqs):
+        if r.request_id in eng.requests:
+            eng.scheduler.running.remove(r)
+            runner.end_request(r.request_id)
+            eng.requests.pop(r.request_id)
+    width = next(iter(runner.graphs.widths.values())) if runner.graphs else 0
+    bucket = runner.graphs.bucket(B) if runner.graphs else B
+    h2d = 4 * (3 * bucket + (bucket + 1) + 3 * bucket + bucket * width)
+    d2h = 4 * B
+    return dev_ms, e2e_ms, ctx_tokens, launches, h2d, d2h, clock_info
+
+
+def time_prefill(eng, reps=5):
+    import torch
+    g = random.Random(99)
+    V = eng.config.vocab_size
+    runner = eng.runner
+    times = []
+    for i in range(reps + 2):
+        toks = [g.randrange(V) for _ in range(PREFILL_TOKENS)]
+        rid = f"prefill{i}"
+        runner.add_request(rid)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        runner.step([(rid, toks, [PREFILL_TOKENS - 1])])
+        stop.record()
+        torch.cuda.synchronize()
+        runner.end_request(rid)
+        if i >= 2:
+            times.append(start.elapsed_time(stop))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def run_ours(args):
+    import torch
+    import zig_ai_b200 as z
+    from zig_ai_b200.config import config_from_dict
+    from zig_ai_b200.kernels import build
+    build.build_all(verbose=False)
+    hbm_peak, flops_peak, peak_src = peaks()
+    cfg = config_from_dict(LFM2_350M)
+    nums = model_numbers(cfg)
+    with tempfile.TemporaryDirectory(prefix="lfm2_350m_") as d:
+        z.write_random_model(cfg, 0, d)
+        eng = z.Engine(d, "bfloat16", max_num_seqs=64, max_batched_tokens=2048 + 64, max_model_len=CONTEXT,
+                       max_tokens=64 * CONTEXT)
+        prefill_ms = time_prefill(eng)
+        clocks = ClockSampler()
+        dev_ms, e2e_ms, ctx_tokens, launches, h2d, d2h, clock_info = time_decode(eng, 8, args.steps, args.warmup, clocks)
+        points = {}
+        for B in (1, 64):
+            ms, _, _, _, _, _, _ = time_decode(eng, B, max(args.steps // 2, 5), args.warmup)
+            points[f"decode_b{B}"] = round(B / ms * 1e3, 1)
+    weight_bytes = 2 * (nums["layer_params"] + nums["head_params"])
+    step_bytes = weight_bytes + ctx_tokens * nums["kv_bytes_per_token"] + 8 * nums["state_bytes"]
+    achieved = step_bytes / (dev_ms * 1e-3) / 1e9
+    Hq, D = nums["attn_dims"]
+    T = PREFILL_TOKENS
+    prefill_flops = 2 * T * nums["layer_params"] + 2 * 1 * nums["head_params"] + nums["n_attn"] * 2 * T * T * Hq * D
+    out = {
+        "metric": "decode tok/s @ batch 8 (LFM2-350M shape, context 2048-4096)",
+        "value": round(8 / dev_ms * 1e3, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(dev_ms, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded random weights and token ids)",
+        "impl": "ours",
+        "config": {"model": "LFM2-350M shape", "layers": cfg.num_hidden_layers, "layers_of_config": 16,
+                   "attn_layers": nums["n_attn"], "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads,
+                   "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim, "ff_dim": cfg.ff_dim,
+                   "vocab": cfg.vocab_size, "conv_taps": cfg.conv_L_cache, "global_batch": 8, "seq_len": CONTEXT,
+                   "mean_context": round(ctx_tokens / 8), "page_size": 16, "parallelism": "single GPU",
+                   "l2": "step reads 0.7 GB of weights (> 126 MB L2)", "peaks": peak_src},
+        "e2e": {"value": round(8 / e2e_ms * 1e3, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": int(round(launches * args.steps)),
+        "prefill": {"value": round(T / prefill_ms * 1e3, 1), "tokens": T, "ms": round(prefill_ms, 3),
+                    "frac": round(prefill_flops / (prefill_ms * 1e-3) / (flops_peak * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_peak, "unit": "GB/s",
+                     "frac": round(achieved / hbm_peak, 4)},
+        "points": points,
+        "clocks": clock_info,
+    }
+    print(json.dumps(out))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a Zig 0.16 program (build.zig); no Zig compiler exists in this image and it "
+                          "has no Python package to install, and it publishes no LFM2 figures"}))
+        return 0
+    if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported, run with --gpus 1")
+        return 2
+    args.warmup = max(args.warmup, 3)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -32,7 +32,8 @@ class Engine:
         if max_tokens is None:
             max_tokens = min(self.max_model_len * max_num_seqs, 1 << 20)
         self.runner: ModelRunner = load_runner(model_dir, dtype, max_tokens=max_tokens, max_requests=max_num_seqs,
-                                               page_size=page_size, device=device, ops=ops)
+                                               page_size=page_size, device=device, ops=ops,
+                                               max_positions=self.max_model_len)
         self.config = self.runner.config
         self.scheduler = Scheduler(self.runner.cache, max_num_seqs, max_batched_tokens, self.max_model_len,
                                    owner=self.runner)

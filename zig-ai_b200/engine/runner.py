@@ -30,6 +30,20 @@ class ModelRunner:
         self.processed: Dict[object, int] = {}      # request -> tokens in the cache
         self.steps = 0
         self.tokens_run = 0
+        self.graphs = None
+        self.use_graphs = False
+
+    def enable_graphs(self, max_positions: int) -> bool:
+        """Run decode-only steps as CUDA graphs, if the device is CUDA and every part says its
+        forward can be captured (no host reads of device data)."""
+        parts = [p for b in self.model.blocks for p in (b, b.mixer, b.feed_forward, b.mixer_norm, b.ff_norm)]
+        if self.device.type != "cuda" or not all(getattr(p, "graph_safe", False) for p in parts + [self.model.final_norm]):
+            return False
+        from .graph import DecodeGraphs
+        self.graphs = DecodeGraphs(self.model, self.cache, self.ops, self.dtype, self.device,
+                                   min(max_positions, self.cache.num_pages * self.cache.page_size))
+        self.use_graphs = True
+        return True
 
     # ------------------------------------------------------------------ requests
     def add_request(self, request_id) -> None:
@@ -49,9 +63,9 @@ class ModelRunner:
         del self.processed[request_id]
 
     # ------------------------------------------------------------------ the step
-    def prepare(self, entries: Sequence[Tuple[object, Sequence[int], Sequence[int]]]) -> StepBatch:
-        """Check the entries, reserve pages and build the batch description.  Nothing is reserved
-        if any entry is refused."""
+    def _reserve(self, entries: Sequence[Tuple[object, Sequence[int], Sequence[int]]]):
+        """Check the entries and reserve their pages (all or none).  Returns the spans
+        (request, ctx_len, tokens, wanted, slot) and the requests' block tables by group."""
         if not entries:
             raise StepError("a step needs at least one entry")
         seen = set()
@@ -88,22 +102,39 @@ class ModelRunner:
         for g in self.cache.paged_groups():
             width = max(max(len(self.cache.requests[r].tables[g]) for r in rids), 1)
             tables[g] = self.cache.table_rows(rids, g, width)
+        return spans, tables
+
+    def prepare(self, entries) -> StepBatch:
+        spans, tables = self._reserve(entries)
         return pack_step(self.ops, self.dtype, self.device, spans, tables, pin=True)
 
     def step(self, entries) -> torch.Tensor:
         """entries: (request, its next tokens, wanted places among them).  Returns 32-bit logits
         [wanted, vocab] in the order of the entries and of their wanted places."""
-        batch = self.prepare(entries)
-        logits = self.model.forward(batch, self.cache)
+        spans, tables = self._reserve(entries)
+        n_tokens = sum(len(e[1]) for e in entries)
+        graphed = (self.use_graphs and n_tokens == len(entries) and self.graphs.bucket(len(entries)) is not None
+                   and all(len(e[2]) <= 1 for e in entries))
+        if graphed:
+            full = self.graphs.run(spans, tables)            # logits of every row
+            keep = [i for i, e in enumerate(entries) if len(e[2]) == 1]
+            if len(keep) == len(entries):
+                logits = full
+            else:
+                logits = full[torch.tensor(keep, dtype=torch.long, device=self.device)] if keep else full[:0]
+        else:
+            batch = pack_step(self.ops, self.dtype, self.device, spans, tables, pin=True)
+            logits = self.model.forward(batch, self.cache)
         for rid, tokens, _ in entries:
             self.processed[rid] += len(tokens)
         self.steps += 1
-        self.tokens_run += batch.n_tokens
+        self.tokens_run += n_tokens
         return logits
 
 
 def load_runner(model_dir: str, dtype="bfloat16", max_tokens: int = 4096, max_requests: int = 64,
-                page_size: int = 16, device=None, ops=None) -> ModelRunner:
+                page_size: int = 16, device=None, ops=None, graphs: bool = True,
+                max_positions: Optional[int] = None) -> ModelRunner:
     """Read config.json, build the model its architecture names, load the tensors and make a cache
     for `max_tokens` positions."""
     from ..config import load_config
@@ -124,6 +155,8 @@ def load_runner(model_dir: str, dtype="bfloat16", max_tokens: int = 4096, max_re
     cache = CacheManager(model.cache_needs(), page_size, num_pages, max_requests, tdtype, device)
     runner = ModelRunner(model, cache, ops, tdtype, device)
     runner.config = cfg
+    if graphs:
+        runner.enable_graphs(min(max_positions or model.spec.max_positions, model.spec.max_positions))
     return runner
 
 

@@ -30,6 +30,7 @@ EXTRA_LIBS: Dict[str, List[str]] = {}
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
+_dir_lock = threading.Lock()
 
 
 class KernelBuildError(RuntimeError):
@@ -49,7 +50,18 @@ def find_nvcc() -> str:
                            "the CUDA kernels cannot be compiled")
 
 
+_lib_dir = None
+
+
 def lib_dir() -> str:
+    global _lib_dir
+    with _dir_lock:
+        if _lib_dir is None:
+            _lib_dir = _find_lib_dir()
+        return _lib_dir
+
+
+def _find_lib_dir() -> str:
     d = os.path.join(CSRC, "_build")
     try:
         os.makedirs(d, exist_ok=True)

@@ -61,8 +61,13 @@ def _fn(lib_name: str, fn_name: str):
     return f
 
 
-def _check(code: int, what: str) -> None:
+launches = 0        # kernels of this package launched so far (a count of launcher calls that ran)
+
+
+def _check(code: int, what: str, n: int = 1) -> None:
+    global launches
     if code == 0:
+        launches += n
         return
     if code == -1:
         raise KernelError(f"{what}: element type not supported by the kernel")
@@ -167,7 +172,7 @@ def short_conv(bcx, conv_w, conv_b, state, step, taps, write_state=True):
     _check(_fn("shortconv", "zai_short_conv")(
         _ptr(z), _ptr(bcx), _dt(bcx), _ptr(conv_w), _ptr(conv_b), _ptr(state), _ptr(step.seq_idx), _ptr(step.cu_q),
         _ptr(step.slot_ids), N, step.n_seqs, C, int(taps), state.shape[1], int(step.decode_only),
-        int(write_state), _stream()), "short_conv")
+        int(write_state), _stream()), "short_conv", 1 if (step.decode_only or taps == 1 or not write_state) else 2)
     return z
 
 

@@ -22,6 +22,8 @@ from .base import Mixer, PagedKVNeed, ParamDecl, make_part, register_part, PartS
 
 
 class Attention(Mixer):
+    graph_safe = True      # forward launches kernels only; nothing is read back to the host
+
     def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, qk_norm: bool, eps: float,
                  position: PartSpec, window=None, scale=None, kv_proj: bool = True):
         self.hidden, self.heads, self.kv_heads, self.head_dim = int(hidden), int(heads), int(kv_heads), int(head_dim)

@@ -13,6 +13,8 @@ from .base import Block, register_part
 
 
 class PreNormResidual(Block):
+    graph_safe = True      # forward launches kernels only; nothing is read back to the host
+
     def params(self):
         return {}
 

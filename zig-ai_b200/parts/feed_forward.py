@@ -11,6 +11,8 @@ from .base import FeedForward, ParamDecl, register_part
 
 
 class SwiGlu(FeedForward):
+    graph_safe = True      # forward launches kernels only; nothing is read back to the host
+
     def __init__(self, hidden: int, ff_dim: int):
         self.hidden, self.ff_dim = int(hidden), int(ff_dim)
 

@@ -11,6 +11,8 @@ from .base import Norm, ParamDecl, register_part
 
 
 class RmsNorm(Norm):
+    graph_safe = True      # forward launches kernels only; nothing is read back to the host
+
     def __init__(self, size: int, eps: float, weight: str):
         self.size, self.eps, self.weight_name = int(size), float(eps), weight
         self.weight = None

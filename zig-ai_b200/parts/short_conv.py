@@ -19,6 +19,8 @@ from .base import Mixer, ParamDecl, StateNeed, register_part
 
 
 class ShortConv(Mixer):
+    graph_safe = True      # forward launches kernels only; nothing is read back to the host
+
     def __init__(self, hidden: int, conv_dim: int, taps: int, bias: bool):
         self.hidden, self.conv_dim, self.taps, self.bias = int(hidden), int(conv_dim), int(taps), bool(bias)
         if self.taps < 1:
