@@ -150,40 +150,70 @@ def fill_pages(step, ctx, q_lens, ps, Hkv, D, dtype, num_pages, g, boost=None):
     return pages
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("Hq,Hkv,D,ps,window", [(4, 2, 16, 16, None), (3, 1, 32, 8, None), (6, 3, 48, 4, 7),
-                                                 (8, 2, 80, 32, None), (16, 8, 64, 16, None), (2, 2, 128, 16, 40)])
-def test_paged_attention(dtype, Hq, Hkv, D, ps, window):
+ATT_SHAPES = [(4, 2, 16, 16, None), (3, 1, 32, 8, None), (6, 3, 48, 4, 7), (8, 2, 80, 32, None),
+              (16, 8, 64, 16, None), (2, 2, 128, 16, 40), (32, 2, 96, 16, None), (5, 5, 112, 16, None)]
+
+
+@pytest.mark.parametrize("dtype,impl", [(torch.float32, None), (torch.bfloat16, None), (torch.bfloat16, "general")])
+@pytest.mark.parametrize("Hq,Hkv,D,ps,window", ATT_SHAPES)
+def test_paged_attention_mixed_spans(dtype, impl, Hq, Hkv, D, ps, window):
+    """Spans that start at 0, inside a page and far into a request, of 1 to 150 rows (more than two
+    query tiles), with and without a window."""
     o = ops()
     g = torch.Generator().manual_seed(8)
-    ctx, q_lens = [0, ps - 1, 2 * ps, 301, 5], [2 * ps + 1, 2, 1, 1, 37]
-    num_pages = 128
+    ctx, q_lens = [0, ps - 1, 2 * ps, 301, 5, 63], [150, 2, 1, 1, 37, 66]
+    num_pages = 256
     step = make_step(o, dtype, ctx, q_lens, ps, num_pages, 9)
     pages = fill_pages(step, ctx, q_lens, ps, Hkv, D, dtype, num_pages, g)
     q = torch.randn(sum(q_lens), Hq * D, generator=g).to(dtype).cuda()
     view = CacheView(0, pages, step.block_tables[0], ps)
-    a = o.paged_attention(q, step, view, Hq, Hkv, D, D ** -0.5, window)
+    a = o.paged_attention(q, step, view, Hq, Hkv, D, D ** -0.5, window, impl=impl)
     b = ref_ops.paged_attention(q, step, view, Hq, Hkv, D, D ** -0.5, window)
     assert torch.allclose(a.float(), b.float(), **tol(dtype))
 
 
+@pytest.mark.parametrize("Hq,Hkv,D,ps,window", ATT_SHAPES)
+def test_paged_attention_single_tokens(Hq, Hkv, D, ps, window):
+    """Every span one token (the split-key kernel in bfloat16): contexts of 0 keys, one short of
+    and exactly a chunk of 256, several chunks, and one that ends inside a tile."""
+    o = ops()
+    for dtype in DTYPES:
+        g = torch.Generator().manual_seed(18)
+        ctx = [0, 1, 254, 255, 256, 700, 63, 1029]
+        q_lens = [1] * len(ctx)
+        num_pages = 1024
+        step = make_step(o, dtype, ctx, q_lens, ps, num_pages, 19)
+        assert step.decode_only
+        pages = fill_pages(step, ctx, q_lens, ps, Hkv, D, dtype, num_pages, g)
+        q = torch.randn(len(ctx), Hq * D, generator=g).to(dtype).cuda()
+        view = CacheView(0, pages, step.block_tables[0], ps)
+        a = o.paged_attention(q, step, view, Hq, Hkv, D, D ** -0.5, window)
+        b = ref_ops.paged_attention(q, step, view, Hq, Hkv, D, D ** -0.5, window)
+        assert torch.allclose(a.float(), b.float(), **tol(dtype)), dtype
+        # more chunks than any request needs (a captured graph is sized for the longest request allowed)
+        step.max_kv_len = 3000
+        a2 = o.paged_attention(q, step, view, Hq, Hkv, D, D ** -0.5, window)
+        assert torch.equal(a, a2)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_attention_finds_one_far_key(dtype):
+@pytest.mark.parametrize("q_len", [1, 3])
+def test_attention_finds_one_far_key(dtype, q_len):
     """One key among hundreds, at a page's first position far back, is made to stand out by scaling
-    it and the query; the output must be its value."""
+    it and the query; the output must be its value (both the single-token and the span kernels)."""
     o = ops()
     Hq, Hkv, D, ps = 4, 2, 64, 16
     g = torch.Generator().manual_seed(10)
-    ctx, q_lens = [700], [1]
+    ctx, q_lens = [700], [q_len]
     step = make_step(o, dtype, ctx, q_lens, ps, 64, 11)
     pages = fill_pages(step, ctx, q_lens, ps, Hkv, D, dtype, 64, g)
-    q = torch.randn(1, Hq * D, generator=g).to(dtype).cuda()
+    q = torch.randn(q_len, Hq * D, generator=g).to(dtype).cuda()
     far = 5 * ps
     bt = step.block_tables[0].cpu()
     for h in range(Hkv):
         pages[bt[0, far // ps], 0, h, 0, :] = (q[0, (h * 2) * D:(h * 2 + 1) * D].float() * 8).to(dtype)
     view = CacheView(0, pages, step.block_tables[0], ps)
-    a = o.paged_attention(q, step, view, Hq, Hkv, D, D ** -0.5, None).float().view(Hq, D)
+    a = o.paged_attention(q, step, view, Hq, Hkv, D, D ** -0.5, None).float()[0].view(Hq, D)
     for h in (0, 2):
         want = pages[bt[0, far // ps], 1, h // 2, 0, :].float()
         assert torch.allclose(a[h], want, atol=2e-2), h

@@ -137,7 +137,10 @@ def run_trace(model_dir, dtype, steps, max_tokens, out_dir, vocab, page_size=16,
 #   among 600 rows, the same whether the request runs whole or token by token.  A fault of the
 #   cache or the batch moves a row by tens of per cent; faults smaller than this noise are the 32-bit
 #   path's to show.  Rows of different ways of cutting the same request are also compared with each
-#   other, more tightly.
+#   other: in 32-bit they agree to rounding of the sums; in bfloat16 a span and a single token run
+#   through different attention kernels (other orders of summation, probabilities rounded to
+#   bfloat16 at other places), so two runs differ like two independent roundings of the same row and
+#   get the same limit as a run against the plain implementation.
 def row_error(got, want):
     """(relative L2 error of the row, largest absolute error over the row's largest |logit|)"""
     err = np.abs(got.astype(np.float64) - want)
@@ -155,5 +158,5 @@ def check_row(got, want, dtype, where):
 def check_same(a, b, dtype, where):
     """Two ways of running the same position."""
     l2, mx = row_error(a, b.astype(np.float64))
-    lim = 2e-5 if dtype == "float32" else 2.5e-2
-    assert l2 < lim and mx < lim, f"{where}: two ways of cutting differ by L2 {l2:.3e}, largest {mx:.3e}"
+    lim_l2, lim_mx = (2e-5, 2e-5) if dtype == "float32" else (6e-2, 8e-2)
+    assert l2 < lim_l2 and mx < lim_mx, f"{where}: two ways of cutting differ by L2 {l2:.3e}, largest {mx:.3e}"

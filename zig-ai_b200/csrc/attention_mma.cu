@@ -1,0 +1,516 @@
+// Paged attention on the tensor cores (bfloat16 operands, 32-bit accumulation and softmax):
+//
+//   * prefill: a flash-style kernel over block tables.  One block takes 64 consecutive query rows
+//     of one request and one query head; it walks the request's cached keys in tiles of 64 (the
+//     cached prefix and the rows of this very step, which are already in the pages), keeps the
+//     running maximum, the running sum and the unnormalised output of each row in registers and
+//     never writes scores to memory.  Spans of one token are handled too, so a mixed step needs no
+//     second kernel.
+//   * decode: every row is one token.  One block takes one request, one key/value head and one
+//     chunk of 256 keys; the query heads that share the key/value head are the rows of one 16-row
+//     tile, so keys and values are read once per group.  Each of the four warps takes 16 keys of
+//     every 64-key tile.  Blocks write unnormalised partial outputs with their maximum and sum to
+//     scratch memory and a second kernel combines the chunks (no block waits on another).
+//
+// The reference's kernels give one warp to each (token, head) and walk all keys serially
+// (src/cuda/paged_attention.cu:121-225 decode, :230-337 prefill).  Same mathematics: scores
+// q.k/sqrt(D) (src/transformer/hybrid_attn.zig:571), causal bound on the absolute position (:587),
+// max-subtracted softmax (:578-600), query head h reads key/value head h / (Hq/Hkv)
+// (src/cuda/paged_attention.cu:142).
+//
+// Key tiles start at multiples of 64 counted from position 0 and chunks at multiples of 256, so a
+// row's sums are formed in the same order however the request was cut into steps and whatever
+// else is in the batch.  Pages: [num_pages, 2, Hkv, page_size, D].
+#include "common.cuh"
+
+#define TILE 64              // keys per tile, query rows per prefill block
+#define CHUNK 256            // keys per decode block
+#define NTHREADS 128
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+    const int bytes = valid ? 16 : 0;        // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(smem)), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+// d += a (16x16, row) * b (16x8, col)
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Rows t0 .. t0+63 of the keys (kv = 0) or values (kv = 1) of one head into shared memory, row
+// stride D + 8 elements; rows outside [kstart, kend) are filled with zeros.
+template <int D>
+__device__ __forceinline__ void load_kv_tile(bf16* dst, const bf16* __restrict__ pages, const int* __restrict__ table,
+                                             int t0, int kstart, int kend, int page_size, size_t page_stride,
+                                             size_t head_off, int tid) {
+    constexpr int CH = D / 8;
+    for (int idx = tid; idx < TILE * CH; idx += NTHREADS) {
+        const int r = idx / CH, c = idx % CH;
+        const int j = t0 + r;
+        const bool valid = j >= kstart && j < kend;
+        const bf16* src = pages;
+        if (valid) {
+            const int page = table[j / page_size];
+            src = pages + (size_t)page * page_stride + head_off + (size_t)(j % page_size) * D + c * 8;
+        }
+        cp_async16(dst + r * (D + 8) + c * 8, src, valid);
+    }
+}
+
+// S[16 x 16 keys] += Q (A fragments of all D/16 steps) . K^T for the 16 keys at `krows` (shared, stride D+8)
+template <int D>
+__device__ __forceinline__ void qk_16keys(float (&s0)[4], float (&s1)[4], const uint32_t (&qf)[D / 16][4],
+                                          const bf16* krows, int lane) {
+    const int key = ((lane >> 4) << 3) + (lane & 7);       // matrices 0,1: keys 0-7; 2,3: keys 8-15
+    const int dof = ((lane >> 3) & 1) << 3;                // matrices 1,3: dims +8
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+        uint32_t b[4];
+        ldmatrix_x4(b, krows + key * (D + 8) + ks * 16 + dof);
+        mma_bf16(s0, qf[ks], b[0], b[1]);
+        mma_bf16(s1, qf[ks], b[2], b[3]);
+    }
+}
+
+// O[16 x D] += P (one A fragment: 16 rows x 16 keys) . V for the 16 keys at `vrows`
+template <int D>
+__device__ __forceinline__ void pv_16keys(float (&o)[D / 8][4], const uint32_t (&pf)[4], const bf16* vrows, int lane) {
+    const int key = (((lane >> 3) & 1) << 3) + (lane & 7);  // matrices 1,3: keys 8-15
+    const int dof = (lane >> 4) << 3;                       // matrices 2,3: dims +8
+#pragma unroll
+    for (int dp = 0; dp < D / 16; ++dp) {
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, vrows + key * (D + 8) + dp * 16 + dof);
+        mma_bf16(o[2 * dp], pf, b[0], b[1]);
+        mma_bf16(o[2 * dp + 1], pf, b[2], b[3]);
+    }
+}
+
+// ------------------------------------------------------------------------------------------ prefill
+template <int D>
+__global__ void __launch_bounds__(NTHREADS) prefill_mma_kernel(
+    bf16* __restrict__ out, const bf16* __restrict__ q, const bf16* __restrict__ pages,
+    const int* __restrict__ block_table, int table_width, const int* __restrict__ cu_q,
+    const int* __restrict__ ctx_lens, int S, int page_size, int Hq, int Hkv, float scale_log2, int window) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int ST = D + 8;
+    bf16* sq = reinterpret_cast<bf16*>(smem_raw);           // [64][ST]
+    bf16* sk = sq + TILE * ST;                              // [2][64][ST]
+    bf16* sv = sk + 2 * TILE * ST;                          // [2][64][ST]
+    __shared__ int s_seq, s_i0;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) {
+        int t = blockIdx.x, s = 0;
+        for (; s < S; ++s) {
+            const int nt = (cu_q[s + 1] - cu_q[s] + TILE - 1) / TILE;
+            if (t < nt) break;
+            t -= nt;
+        }
+        s_seq = s;
+        s_i0 = t * TILE;
+    }
+    __syncthreads();
+    const int s = s_seq, i0 = s_i0;
+    if (s >= S) return;
+    const int h = blockIdx.y, hk = h / (Hq / Hkv);
+    const int row0 = cu_q[s], q_len = cu_q[s + 1] - row0, ctx = ctx_lens[s];
+    const int rows = min(TILE, q_len - i0);                 // valid query rows of this block
+    const int* table = block_table + (size_t)s * table_width;
+    const size_t page_stride = (size_t)2 * Hkv * page_size * D;
+    const size_t k_off = (size_t)hk * page_size * D, v_off = ((size_t)Hkv + hk) * page_size * D;
+    const int kend = ctx + i0 + rows;                       // one past the last visible key of the block
+    int kbeg = 0;
+    if (window > 0) kbeg = max(ctx + i0 - window + 1, 0);
+    const int tile0 = kbeg / TILE, tile1 = (kend + TILE - 1) / TILE;
+
+    // queries of the block: rows beyond the span are zeros
+    for (int idx = tid; idx < TILE * (D / 8); idx += NTHREADS) {
+        const int r = idx / (D / 8), c = idx % (D / 8);
+        const bool valid = r < rows;
+        const bf16* src = valid ? q + ((size_t)(row0 + i0 + r) * Hq + h) * D + c * 8 : q;
+        cp_async16(sq + r * ST + c * 8, src, valid);
+    }
+    load_kv_tile<D>(sk, pages, table, tile0 * TILE, kbeg, kend, page_size, page_stride, k_off, tid);
+    load_kv_tile<D>(sv, pages, table, tile0 * TILE, kbeg, kend, page_size, page_stride, v_off, tid);
+    cp_async_commit();
+
+    uint32_t qf[D / 16][4];
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;       // rows g and g+8 of the warp's 16
+    const int g = lane >> 2, tq = lane & 3;
+    const int p0 = ctx + i0 + warp * 16 + g, p1 = p0 + 8;          // positions of the two rows
+    const int lo0 = window > 0 ? p0 - window + 1 : 0, lo1 = window > 0 ? p1 - window + 1 : 0;
+
+    for (int t = tile0; t < tile1; ++t) {
+        const int buf = (t - tile0) & 1;
+        if (t + 1 < tile1) {
+            load_kv_tile<D>(sk + (buf ^ 1) * TILE * ST, pages, table, (t + 1) * TILE, kbeg, kend, page_size,
+                            page_stride, k_off, tid);
+            load_kv_tile<D>(sv + (buf ^ 1) * TILE * ST, pages, table, (t + 1) * TILE, kbeg, kend, page_size,
+                            page_stride, v_off, tid);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (t == tile0) {
+            const int r = warp * 16 + (((lane >> 3) & 1) << 3) + (lane & 7);
+            const int dof = (lane >> 4) << 3;
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) ldmatrix_x4(qf[ks], sq + r * ST + ks * 16 + dof);
+        }
+        const bf16* kt = sk + buf * TILE * ST;
+        const bf16* vt = sv + buf * TILE * ST;
+        // a warp whose rows all lie before this tile's first key has nothing to do in it
+        const int warp_last_pos = ctx + i0 + warp * 16 + 15;
+        if (t * TILE <= warp_last_pos) {
+            float sc[8][4];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
+#pragma unroll
+            for (int kb = 0; kb < 4; ++kb) qk_16keys<D>(sc[2 * kb], sc[2 * kb + 1], qf, kt + kb * 16 * ST, lane);
+            float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int j = t * TILE + nt * 8 + 2 * tq + e;
+                    if (j > p0 || j < lo0) sc[nt][e] = -INFINITY;
+                    if (j > p1 || j < lo1) sc[nt][2 + e] = -INFINITY;
+                    mx0 = fmaxf(mx0, sc[nt][e]);
+                    mx1 = fmaxf(mx1, sc[nt][2 + e]);
+                }
+            }
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+            const float u0 = n0 == -INFINITY ? 0.f : n0 * scale_log2;    // a row with nothing visible yet
+            const float u1 = n1 == -INFINITY ? 0.f : n1 * scale_log2;
+            const float c0 = exp2f(m0 * scale_log2 - u0), c1 = exp2f(m1 * scale_log2 - u1);
+            m0 = n0;
+            m1 = n1;
+            l0 *= c0;
+            l1 *= c1;
+#pragma unroll
+            for (int i = 0; i < D / 8; ++i) {
+                o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1;
+            }
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+                sc[nt][0] = exp2f(sc[nt][0] * scale_log2 - u0);
+                sc[nt][1] = exp2f(sc[nt][1] * scale_log2 - u0);
+                sc[nt][2] = exp2f(sc[nt][2] * scale_log2 - u1);
+                sc[nt][3] = exp2f(sc[nt][3] * scale_log2 - u1);
+                l0 += sc[nt][0] + sc[nt][1];
+                l1 += sc[nt][2] + sc[nt][3];
+            }
+#pragma unroll
+            for (int kb = 0; kb < 4; ++kb) {
+                uint32_t pf[4];
+                pf[0] = pack_bf16(sc[2 * kb][0], sc[2 * kb][1]);
+                pf[1] = pack_bf16(sc[2 * kb][2], sc[2 * kb][3]);
+                pf[2] = pack_bf16(sc[2 * kb + 1][0], sc[2 * kb + 1][1]);
+                pf[3] = pack_bf16(sc[2 * kb + 1][2], sc[2 * kb + 1][3]);
+                pv_16keys<D>(o, pf, vt + kb * 16 * ST, lane);
+            }
+        }
+        __syncthreads();                                    // the buffer is loaded again two tiles on
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const int r0 = warp * 16 + g, r1 = r0 + 8;
+    const float inv0 = 1.f / l0, inv1 = 1.f / l1;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+        const int d = i * 8 + 2 * tq;
+        if (r0 < rows)
+            *reinterpret_cast<uint32_t*>(out + ((size_t)(row0 + i0 + r0) * Hq + h) * D + d) = pack_bf16(o[i][0] * inv0, o[i][1] * inv0);
+        if (r1 < rows)
+            *reinterpret_cast<uint32_t*>(out + ((size_t)(row0 + i0 + r1) * Hq + h) * D + d) = pack_bf16(o[i][2] * inv1, o[i][3] * inv1);
+    }
+}
+
+// ------------------------------------------------------------------------------------------ decode
+// part_o [B, Hq, n_chunks, D] unnormalised outputs; part_ml [B, Hq, n_chunks, 2]: maximum (in log2
+// units, already scaled) and sum.  A chunk with no visible key writes (-inf, 0).
+template <int D>
+__global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
+    float* __restrict__ part_o, float* __restrict__ part_ml, const bf16* __restrict__ q,
+    const bf16* __restrict__ pages, const int* __restrict__ block_table, int table_width,
+    const int* __restrict__ positions, int page_size, int Hq, int Hkv, float scale_log2, int window) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int ST = D + 8;
+    bf16* sq = reinterpret_cast<bf16*>(smem_raw);           // [16][ST]
+    bf16* sk = sq + 16 * ST;                                // [2][64][ST]
+    bf16* sv = sk + 2 * TILE * ST;                          // [2][64][ST]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int chunk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z, n_chunks = gridDim.x;
+    const int G = Hq / Hkv;
+    const int pos = positions[b];
+    const int kend = pos + 1;
+    const int kstart = window > 0 ? max(pos - window + 1, 0) : 0;
+    const int lo = max(chunk * CHUNK, kstart), hi = min((chunk + 1) * CHUNK, kend);
+    if (lo >= hi) {
+        if (tid < G) {
+            float* ml = part_ml + (((size_t)b * Hq + hk * G + tid) * n_chunks + chunk) * 2;
+            ml[0] = -INFINITY;
+            ml[1] = 0.f;
+        }
+        return;
+    }
+    const int* table = block_table + (size_t)b * table_width;
+    const size_t page_stride = (size_t)2 * Hkv * page_size * D;
+    const size_t k_off = (size_t)hk * page_size * D, v_off = ((size_t)Hkv + hk) * page_size * D;
+    const int tile0 = lo / TILE, tile1 = (hi + TILE - 1) / TILE;
+
+    for (int idx = tid; idx < 16 * (D / 8); idx += NTHREADS) {
+        const int r = idx / (D / 8), c = idx % (D / 8);
+        const bool valid = r < G;
+        const bf16* src = valid ? q + ((size_t)b * Hq + hk * G + r) * D + c * 8 : q;
+        cp_async16(sq + r * ST + c * 8, src, valid);
+    }
+    load_kv_tile<D>(sk, pages, table, tile0 * TILE, lo, hi, page_size, page_stride, k_off, tid);
+    load_kv_tile<D>(sv, pages, table, tile0 * TILE, lo, hi, page_size, page_stride, v_off, tid);
+    cp_async_commit();
+
+    uint32_t qf[D / 16][4];
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    const int g = lane >> 2, tq = lane & 3;
+
+    for (int t = tile0; t < tile1; ++t) {
+        const int buf = (t - tile0) & 1;
+        if (t + 1 < tile1) {
+            load_kv_tile<D>(sk + (buf ^ 1) * TILE * ST, pages, table, (t + 1) * TILE, lo, hi, page_size, page_stride,
+                            k_off, tid);
+            load_kv_tile<D>(sv + (buf ^ 1) * TILE * ST, pages, table, (t + 1) * TILE, lo, hi, page_size, page_stride,
+                            v_off, tid);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (t == tile0) {
+            const int r = (((lane >> 3) & 1) << 3) + (lane & 7);
+            const int dof = (lane >> 4) << 3;
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) ldmatrix_x4(qf[ks], sq + r * ST + ks * 16 + dof);
+        }
+        const int j0 = t * TILE + warp * 16;                // this warp's 16 keys of the tile
+        if (j0 < hi && j0 + 16 > lo) {
+            float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+            qk_16keys<D>(s0, s1, qf, sk + (buf * TILE + warp * 16) * ST, lane);
+            float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int ja = j0 + 2 * tq + e, jb = ja + 8;
+                if (ja < lo || ja >= hi) { s0[e] = -INFINITY; s0[2 + e] = -INFINITY; }
+                if (jb < lo || jb >= hi) { s1[e] = -INFINITY; s1[2 + e] = -INFINITY; }
+                mx0 = fmaxf(mx0, fmaxf(s0[e], s1[e]));
+                mx1 = fmaxf(mx1, fmaxf(s0[2 + e], s1[2 + e]));
+            }
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);   // finite: the warp has a visible key
+            const float u0 = n0 * scale_log2, u1 = n1 * scale_log2;
+            const float c0 = exp2f(m0 * scale_log2 - u0), c1 = exp2f(m1 * scale_log2 - u1);
+            m0 = n0;
+            m1 = n1;
+#pragma unroll
+            for (int i = 0; i < D / 8; ++i) {
+                o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1;
+            }
+            s0[0] = exp2f(s0[0] * scale_log2 - u0); s0[1] = exp2f(s0[1] * scale_log2 - u0);
+            s0[2] = exp2f(s0[2] * scale_log2 - u1); s0[3] = exp2f(s0[3] * scale_log2 - u1);
+            s1[0] = exp2f(s1[0] * scale_log2 - u0); s1[1] = exp2f(s1[1] * scale_log2 - u0);
+            s1[2] = exp2f(s1[2] * scale_log2 - u1); s1[3] = exp2f(s1[3] * scale_log2 - u1);
+            l0 = l0 * c0 + s0[0] + s0[1] + s1[0] + s1[1];
+            l1 = l1 * c1 + s0[2] + s0[3] + s1[2] + s1[3];
+            uint32_t pf[4];
+            pf[0] = pack_bf16(s0[0], s0[1]);
+            pf[1] = pack_bf16(s0[2], s0[3]);
+            pf[2] = pack_bf16(s1[0], s1[1]);
+            pf[3] = pack_bf16(s1[2], s1[3]);
+            pv_16keys<D>(o, pf, sv + (buf * TILE + warp * 16) * ST, lane);
+        }
+        __syncthreads();
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+    // combine the four warps through shared memory (the tiles are no longer needed)
+    float* wo = reinterpret_cast<float*>(sk);               // [4][16][D]
+    float* wm = wo + 4 * 16 * D;                            // [4][16] maxima (log2 units)
+    float* wl = wm + 4 * 16;                                // [4][16] sums
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+        const int d = i * 8 + 2 * tq;
+        wo[(warp * 16 + g) * D + d] = o[i][0];
+        wo[(warp * 16 + g) * D + d + 1] = o[i][1];
+        wo[(warp * 16 + g + 8) * D + d] = o[i][2];
+        wo[(warp * 16 + g + 8) * D + d + 1] = o[i][3];
+    }
+    if (tq == 0) {
+        wm[warp * 16 + g] = m0 == -INFINITY ? -INFINITY : m0 * scale_log2;
+        wm[warp * 16 + g + 8] = m1 == -INFINITY ? -INFINITY : m1 * scale_log2;
+        wl[warp * 16 + g] = l0;
+        wl[warp * 16 + g + 8] = l1;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < G * D; idx += NTHREADS) {
+        const int r = idx / D, d = idx % D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, wm[w * 16 + r]);
+        float acc = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = wm[w * 16 + r];
+            const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+            acc += wo[(w * 16 + r) * D + d] * f;
+            L += wl[w * 16 + r] * f;
+        }
+        const size_t base = ((size_t)b * Hq + hk * G + r) * n_chunks + chunk;
+        part_o[base * D + d] = acc;
+        if (d == 0) {
+            part_ml[base * 2] = M;
+            part_ml[base * 2 + 1] = L;
+        }
+    }
+}
+
+template <int D>
+__global__ void decode_combine_kernel(bf16* __restrict__ out, const float* __restrict__ part_o,
+                                      const float* __restrict__ part_ml, int n_chunks) {
+    const size_t bh = blockIdx.x;                           // b * Hq + h
+    const float* ml = part_ml + bh * n_chunks * 2;
+    float M = -INFINITY;
+    for (int c = 0; c < n_chunks; ++c) M = fmaxf(M, ml[2 * c]);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float acc = 0.f, L = 0.f;
+        for (int c = 0; c < n_chunks; ++c) {
+            const float mc = ml[2 * c];
+            if (mc == -INFINITY) continue;
+            const float f = exp2f(mc - M);
+            acc += part_o[(bh * n_chunks + c) * D + d] * f;
+            L += ml[2 * c + 1] * f;
+        }
+        out[bh * D + d] = __float2bfloat16_rn(acc / L);
+    }
+}
+
+template <int D> static size_t prefill_smem() { return (size_t)5 * TILE * (D + 8) * sizeof(bf16); }
+template <int D> static size_t decode_smem() {
+    const size_t tiles = (size_t)(16 + 4 * TILE) * (D + 8) * sizeof(bf16);
+    const size_t comb = 16 * (D + 8) * sizeof(bf16) + (size_t)(4 * 16 * D + 2 * 4 * 16) * sizeof(float);
+    return tiles > comb ? tiles : comb;
+}
+
+template <int D>
+static int launch_prefill(bf16* out, const bf16* q, const bf16* pages, const int* block_table, int table_width,
+                          const int* cu_q, const int* ctx_lens, int S, int n_tiles, int page_size, int Hq, int Hkv,
+                          float scale, int window, cudaStream_t stream) {
+    const size_t smem = prefill_smem<D>();
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(prefill_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    prefill_mma_kernel<D><<<dim3(n_tiles, Hq), NTHREADS, smem, stream>>>(
+        out, q, pages, block_table, table_width, cu_q, ctx_lens, S, page_size, Hq, Hkv, scale * 1.4426950408889634f, window);
+    return launch_status();
+}
+
+template <int D>
+static int launch_decode(bf16* out, float* part_o, float* part_ml, const bf16* q, const bf16* pages,
+                         const int* block_table, int table_width, const int* positions, int B, int n_chunks,
+                         int page_size, int Hq, int Hkv, float scale, int window, cudaStream_t stream) {
+    const size_t smem = decode_smem<D>();
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    decode_mma_kernel<D><<<dim3(n_chunks, Hkv, B), NTHREADS, smem, stream>>>(
+        part_o, part_ml, q, pages, block_table, table_width, positions, page_size, Hq, Hkv,
+        scale * 1.4426950408889634f, window);
+    int e = launch_status();
+    if (e) return e;
+    decode_combine_kernel<D><<<B * Hq, D <= 64 ? 64 : 128, 0, stream>>>(out, part_o, part_ml, n_chunks);
+    return launch_status();
+}
+
+#define ZAI_HEAD_DIMS(X) X(16) X(32) X(48) X(64) X(80) X(96) X(128)
+
+// 1 if the tensor-core kernels take this head size (bfloat16 only; others use the general kernel)
+ZAI_API int zai_attention_mma_supports(int D, int Hq, int Hkv) {
+    if (Hkv < 1 || Hq % Hkv != 0 || Hq / Hkv > 16) return 0;
+#define X(d) if (D == d) return 1;
+    ZAI_HEAD_DIMS(X)
+#undef X
+    return 0;
+}
+
+ZAI_API int zai_prefill_attention_mma(void* out, const void* q, const void* pages, const int* block_table,
+                                      int table_width, const int* cu_q, const int* ctx_lens, int S, int n_tiles,
+                                      int page_size, int Hq, int Hkv, int D, float scale, int window,
+                                      cudaStream_t stream) {
+    if (S <= 0 || n_tiles <= 0) return ZAI_OK;
+    if (Hq > 65535) return ZAI_BAD_SIZE;
+#define X(d) if (D == d) return launch_prefill<d>((bf16*)out, (const bf16*)q, (const bf16*)pages, block_table, table_width, \
+                                                  cu_q, ctx_lens, S, n_tiles, page_size, Hq, Hkv, scale, window, stream);
+    ZAI_HEAD_DIMS(X)
+#undef X
+    return ZAI_BAD_SIZE;
+}
+
+// Scratch: part_o holds B*Hq*n_chunks*D floats, part_ml B*Hq*n_chunks*2 floats; n_chunks covers the
+// longest request, ceil(max(pos + 1) / 256).
+ZAI_API int zai_decode_attention_mma(void* out, float* part_o, float* part_ml, const void* q, const void* pages,
+                                     const int* block_table, int table_width, const int* positions, int B,
+                                     int n_chunks, int page_size, int Hq, int Hkv, int D, float scale, int window,
+                                     cudaStream_t stream) {
+    if (B <= 0) return ZAI_OK;
+    if (n_chunks < 1 || Hkv > 65535 || B > 65535 || Hq % Hkv != 0 || Hq / Hkv > 16) return ZAI_BAD_SIZE;
+#define X(d) if (D == d) return launch_decode<d>((bf16*)out, part_o, part_ml, (const bf16*)q, (const bf16*)pages, block_table, \
+                                                 table_width, positions, B, n_chunks, page_size, Hq, Hkv, scale, window, stream);
+    ZAI_HEAD_DIMS(X)
+#undef X
+    return ZAI_BAD_SIZE;
+}
+
+ZAI_API int zai_decode_chunk_keys() { return CHUNK; }

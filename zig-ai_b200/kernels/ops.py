@@ -36,6 +36,12 @@ _SIGNATURES = {
     "attention": {
         "zai_paged_attention_general": [_P, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     },
+    "attention_mma": {
+        "zai_attention_mma_supports": [_I, _I, _I],
+        "zai_prefill_attention_mma": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+        "zai_decode_attention_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+        "zai_decode_chunk_keys": [],
+    },
     "sampling": {
         "zai_argmax": [_P, _P, _I, _I, _P],
         "zai_repetition_penalty": [_P, _P, _P, _P, _P, _I, _I, _P],
@@ -80,7 +86,7 @@ def require() -> None:
     """Fail loudly unless a CUDA device is present and the core libraries load."""
     if not torch.cuda.is_available():
         raise KernelError("no CUDA device: this engine has no CPU path")
-    for lib in ("embed", "norm", "activation", "shortconv", "rope_kv", "attention", "sampling"):
+    for lib in ("embed", "norm", "activation", "shortconv", "rope_kv", "attention", "attention_mma", "sampling"):
         build.load(lib)
 
 
@@ -219,14 +225,37 @@ def kv_write(k, v, step, cache, kv_heads, head_dim):
         head_dim, _stream()), "kv_write")
 
 
-def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=None):
+def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=None, impl=None):
+    """Causal attention of the step's rows over their requests' pages.  bfloat16 runs on the
+    tensor cores (a split-key kernel when every span is one token, else the flash-style kernel)
+    for the head sizes those kernels have; everything else, and `impl="general"`, runs the
+    general kernel."""
     _cuda(q)
     N = q.shape[0]
     out = torch.empty((N, heads * head_dim), dtype=q.dtype, device=q.device)
     if cache.pages.dtype != q.dtype:
         raise KernelError("the pages and the queries should have one dtype")
+    bt = cache.block_table
+    if (impl != "general" and q.dtype == torch.bfloat16
+            and _fn("attention_mma", "zai_attention_mma_supports")(head_dim, heads, kv_heads)):
+        if step.decode_only:
+            chunk = _fn("attention_mma", "zai_decode_chunk_keys")()
+            n_chunks = max(-(-int(step.max_kv_len) // chunk), 1)
+            part_o = torch.empty((N, heads, n_chunks, head_dim), dtype=torch.float32, device=q.device)
+            part_ml = torch.empty((N, heads, n_chunks, 2), dtype=torch.float32, device=q.device)
+            _check(_fn("attention_mma", "zai_decode_attention_mma")(
+                _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(q), _ptr(cache.pages), _ptr(bt), bt.shape[1],
+                _ptr(step.positions), N, n_chunks, cache.page_size, heads, kv_heads, head_dim, float(scale),
+                int(window or 0), _stream()), "decode attention", 2)
+        else:
+            n_tiles = sum(-(-n // 64) for n in step.q_lens)
+            _check(_fn("attention_mma", "zai_prefill_attention_mma")(
+                _ptr(out), _ptr(q), _ptr(cache.pages), _ptr(bt), bt.shape[1], _ptr(step.cu_q), _ptr(step.ctx_lens),
+                step.n_seqs, n_tiles, cache.page_size, heads, kv_heads, head_dim, float(scale), int(window or 0),
+                _stream()), "prefill attention")
+        return out
     _check(_fn("attention", "zai_paged_attention_general")(
-        _ptr(out), _ptr(q), _ptr(cache.pages), _dt(q), _ptr(cache.block_table), cache.block_table.shape[1],
+        _ptr(out), _ptr(q), _ptr(cache.pages), _dt(q), _ptr(bt), bt.shape[1],
         _ptr(step.positions), _ptr(step.seq_idx), cache.page_size, N, heads, kv_heads, head_dim, float(scale),
         int(window or 0), _stream()), "paged_attention")
     return out
