@@ -514,3 +514,59 @@ ZAI_API int zai_decode_attention_mma(void* out, float* part_o, float* part_ml, c
 }
 
 ZAI_API int zai_decode_chunk_keys() { return CHUNK; }
+
+// ------------------------------------------------------------------------------------------ no allocation
+// The same two kernels with their scratch in a static device array; see attention_no_alloc.h for
+// who needs this, its cost and its limits.
+#include "attention_no_alloc.h"
+
+static __device__ __align__(256) float zai_static_scratch[ZAI_STATIC_SCRATCH_FLOATS];
+
+#define ZAI_MAX_DEVICES 64
+static float* zai_static_scratch_ptr[ZAI_MAX_DEVICES];   // device address of the array, per device
+
+// In host code the array's name is only a handle; its device address has to be asked for, once per
+// device, with that device current.
+static int static_scratch_address(float** ptr) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= ZAI_MAX_DEVICES) return ZAI_SCRATCH_SETUP_FAILED;
+    if (zai_static_scratch_ptr[dev] == nullptr) {
+        float* p = nullptr;
+        if (cudaGetSymbolAddress((void**)&p, zai_static_scratch) != cudaSuccess || p == nullptr) {
+            cudaGetLastError();
+            return ZAI_SCRATCH_SETUP_FAILED;
+        }
+        zai_static_scratch_ptr[dev] = p;
+    }
+    *ptr = zai_static_scratch_ptr[dev];
+    return ZAI_OK;
+}
+
+ZAI_API int zai_decode_attention_static(void* out, const void* q, const void* pages, const int* block_table,
+                                        int table_width, const int* positions, int B, int n_chunks, int page_size,
+                                        int Hq, int Hkv, int D, float scale, int window, cudaStream_t stream) {
+    if (B <= 0) return ZAI_OK;
+    if (n_chunks < 1 || Hq < 1 || D < 1) return ZAI_BAD_SIZE;
+    const unsigned long long rows = (unsigned long long)B * Hq * n_chunks;
+    if (rows * (unsigned long long)(D + 2) > (unsigned long long)ZAI_STATIC_SCRATCH_FLOATS) return ZAI_SCRATCH_TOO_SMALL;
+    float* scratch = nullptr;
+    const int e = static_scratch_address(&scratch);
+    if (e != ZAI_OK) return e;
+    float* part_o = scratch;                              // [B, Hq, n_chunks, D]
+    float* part_ml = scratch + rows * D;                  // [B, Hq, n_chunks, 2]
+    return zai_decode_attention_mma(out, part_o, part_ml, q, pages, block_table, table_width, positions, B, n_chunks,
+                                    page_size, Hq, Hkv, D, scale, window, stream);
+}
+
+ZAI_API const char* zai_decode_attention_static_error(int code) {
+    switch (code) {
+        case ZAI_OK: return "ok";
+        case ZAI_BAD_DTYPE: return "element type not supported";
+        case ZAI_BAD_SIZE: return "a size is outside what the kernel supports";
+        case ZAI_SCRATCH_TOO_SMALL:
+            return "B * Hq * n_chunks * (D + 2) floats of scratch are needed, more than the static array of "
+                   "1048576 floats holds; use zai_decode_attention_mma with scratch of your own";
+        case ZAI_SCRATCH_SETUP_FAILED: return "the device address of the static scratch array could not be obtained";
+        default: return "CUDA error at launch";
+    }
+}
