@@ -199,6 +199,14 @@ def run_ours(args):
         z.write_random_model(cfg, 0, d)
         eng = z.Engine(d, "bfloat16", max_num_seqs=64, max_batched_tokens=2048 + 64, max_model_len=CONTEXT,
                        max_tokens=64 * CONTEXT)
+        if args.only == "prefill":
+            print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "ms": round(time_prefill(eng, reps=args.steps), 3)}))
+            return 0
+        if args.only == "decode":
+            ms, e2e, ctx, launches, _, _, _ = time_decode(eng, args.batch, args.steps, args.warmup)
+            print(json.dumps({"only": "decode", "batch": args.batch, "ms_per_step": round(ms, 4),
+                              "e2e_ms_per_step": round(e2e, 4), "launches_per_step": launches}))
+            return 0
         prefill_ms = time_prefill(eng)
         clocks = ClockSampler()
         dev_ms, e2e_ms, ctx_tokens, launches, h2d, d2h, clock_info = time_decode(eng, 8, args.steps, args.warmup, clocks)
@@ -244,6 +252,9 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+                    help="profiling aid: run only the batch-8 decode steps or only the prefill (prints a short line)")
+    ap.add_argument("--batch", type=int, default=8, help="with --only decode: the batch size")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

@@ -17,8 +17,7 @@ def require():
     return None
 
 
-def has_fused_decode(w, x):
-    return False
+fuses_norm = False      # norms run on their own here
 
 
 def _f(x):
@@ -41,6 +40,10 @@ def linear(x, w, out_dtype=None):
     if x.dtype == w.dtype and x.dtype != torch.float32 and x.device.type == "cuda":
         return (x @ w.T).to(out_dtype)
     return (_f(x) @ _f(w).T).to(out_dtype)
+
+
+def linear_swiglu(x, w_gate_up, ff_dim):
+    return silu_mul(linear(x, w_gate_up), ff_dim)
 
 
 def silu_mul(gu, ff_dim):

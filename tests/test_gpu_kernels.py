@@ -267,3 +267,73 @@ def test_repetition_penalty():
                 want[r, tokens[i]] = v / penalty[r] if v > 0 else v * penalty[r]
     o.repetition_penalty(logits, tokens, counts, offsets, penalty)
     assert torch.allclose(logits, want, atol=1e-6)
+
+
+# ----------------------------------------------------------------------------- few-rows products
+def _lazy(h, delta, gamma, eps, rows=None):
+    from zig_ai_b200.parts.base import LazyNorm, Residual
+    return LazyNorm(Residual(h), delta, gamma, eps, torch.bfloat16, rows)
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 13, 16, 40, 64])
+@pytest.mark.parametrize("O,K", [(96, 96), (517, 1000), (1024, 1024), (3072, 1024), (1024, 4608), (130, 8)])
+def test_skinny_gemm_plain_input(M, O, K):
+    o = ops()
+    g = torch.Generator().manual_seed(20)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(O, K, generator=g) * K ** -0.5).to(torch.bfloat16).cuda()
+    want = x.float() @ w.float().t()
+    if M * (K + 8) * 2 <= 200 * 1024:
+        before = o.launches
+        got = o.linear(x, w)
+        assert o.launches == before + 1                 # the fused kernel ran, not the library
+    else:
+        got = o.linear(x, w)
+    assert got.dtype == torch.bfloat16 and torch.allclose(got.float(), want, atol=2e-2, rtol=2e-2)
+    got32 = o.linear(x, w, out_dtype=torch.float32)
+    assert got32.dtype == torch.float32 and torch.allclose(got32, want, atol=2e-3, rtol=2e-3)
+
+
+@pytest.mark.parametrize("M", [1, 8, 11, 64])
+@pytest.mark.parametrize("F,K", [(192, 64), (256, 96), (4608, 1024), (100, 1000)])
+def test_skinny_gemm_swiglu(M, F, K):
+    o = ops()
+    g = torch.Generator().manual_seed(21)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(2 * F, K, generator=g) * K ** -0.5).to(torch.bfloat16).cuda()
+    gu = x.float() @ w.float().t()
+    want = torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]
+    got = o.linear_swiglu(x, w, F)
+    assert got.shape == (M, F) and torch.allclose(got.float(), want, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 24, 64])
+@pytest.mark.parametrize("O,K,eps", [(3072, 1024, 1e-5), (288, 96, 1e-6), (517, 1000, 1e-3)])
+def test_skinny_gemm_with_norm_residual_and_gathered_rows(M, O, K, eps):
+    o = ops()
+    g = torch.Generator().manual_seed(22)
+    h = (torch.randn(M, K, generator=g) * 3).cuda()
+    delta = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    gamma = (1 + 0.1 * torch.randn(K, generator=g)).cuda()
+    w = (torch.randn(O, K, generator=g) * K ** -0.5).to(torch.bfloat16).cuda()
+    hsum = h + delta.float()
+    xn = (hsum * torch.rsqrt((hsum * hsum).mean(-1, keepdim=True) + eps) * gamma).to(torch.bfloat16)
+    want = xn.float() @ w.float().t()
+    lazy = _lazy(h.clone(), delta, gamma, eps)
+    old = lazy.residual.data
+    got = o.linear(lazy, w)
+    assert torch.allclose(got.float(), want, atol=3e-2, rtol=3e-2)
+    assert lazy.residual.data is not old and torch.equal(lazy.residual.data, hsum)    # the new residual stream
+    assert torch.equal(old, h)                                                        # the old one is untouched
+    # without a pending term the stream stays where it is
+    lazy = _lazy(h.clone(), None, gamma, eps)
+    old = lazy.residual.data
+    xn0 = (h * torch.rsqrt((h * h).mean(-1, keepdim=True) + eps) * gamma).to(torch.bfloat16)
+    assert torch.allclose(o.linear(lazy, w).float(), xn0.float() @ w.float().t(), atol=3e-2, rtol=3e-2)
+    assert lazy.residual.data is old
+    # gathered rows, 32-bit result (the head)
+    rows = torch.tensor([M - 1, 0, M // 2][:min(3, M)], dtype=torch.int32).cuda()
+    lazy = _lazy(h.clone(), delta, gamma, eps, rows)
+    got = o.linear(lazy, w, out_dtype=torch.float32)
+    assert got.dtype == torch.float32 and torch.allclose(got, want[rows.long()], atol=3e-2, rtol=3e-2)
+    assert torch.equal(lazy.residual.data, h)

@@ -9,10 +9,12 @@ cuBLAS through `torch.matmul`, as the reference sends every projection to `cubla
 from __future__ import annotations
 
 import ctypes
+import sys
 from ctypes import c_float, c_int, c_void_p
 
 import torch
 
+from ..parts.base import LazyNorm
 from . import build
 
 device_type = "cuda"
@@ -41,6 +43,10 @@ _SIGNATURES = {
         "zai_prefill_attention_mma": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
         "zai_decode_attention_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
         "zai_decode_chunk_keys": [],
+    },
+    "decode_gemm": {
+        "zai_skinny_gemm_supports": [_I, _I, _I, _I],
+        "zai_skinny_gemm": [_P, _P, _P, _P, _P, _P, _P, _P, _F, _I, _I, _I, _I, _P],
     },
     "sampling": {
         "zai_argmax": [_P, _P, _I, _I, _P],
@@ -86,7 +92,7 @@ def require() -> None:
     """Fail loudly unless a CUDA device is present and the core libraries load."""
     if not torch.cuda.is_available():
         raise KernelError("no CUDA device: this engine has no CPU path")
-    for lib in ("embed", "norm", "activation", "shortconv", "rope_kv", "attention", "attention_mma", "sampling"):
+    for lib in ("embed", "norm", "activation", "shortconv", "rope_kv", "attention", "attention_mma", "decode_gemm", "sampling"):
         build.load(lib)
 
 
@@ -113,8 +119,9 @@ def _cuda(*tensors):
 
 
 # ----------------------------------------------------------------------------- kernels
-def has_fused_decode(w, x):
-    return False
+fuses_norm = True       # `linear` and `linear_swiglu` take a LazyNorm and apply it inside the product kernel
+
+_EPI_BF16, _EPI_F32, _EPI_SWIGLU = 0, 1, 2
 
 
 def embed(ids, table):
@@ -148,9 +155,43 @@ def add_rmsnorm(h, delta, w, eps, out_dtype):
     return out
 
 
+def _skinny(x, w, epilogue, out_cols, out_dtype):
+    """The few-rows product kernel, if it takes these operands; else None."""
+    lazy = isinstance(x, LazyNorm)
+    M = (x.rows.numel() if x.rows is not None else x.residual.data.shape[0]) if lazy else x.shape[0]
+    O, K = w.shape
+    if w.dtype != torch.bfloat16 or (not lazy and x.dtype != torch.bfloat16) or (lazy and x.dtype != torch.bfloat16):
+        return None
+    if not _fn("decode_gemm", "zai_skinny_gemm_supports")(M, O, K, epilogue):
+        return None
+    y = torch.empty((M, out_cols), dtype=out_dtype, device=w.device)
+    if lazy:
+        res = x.residual
+        _cuda(res.data, x.delta, x.gamma, x.rows)
+        h_out = torch.empty_like(res.data) if (x.rows is None and x.delta is not None) else None
+        _check(_fn("decode_gemm", "zai_skinny_gemm")(
+            _ptr(y), _ptr(w), None, _ptr(res.data), _ptr(x.delta), _ptr(x.gamma), _ptr(x.rows), _ptr(h_out),
+            float(x.eps), M, O, K, epilogue, _stream()), "skinny_gemm")
+        if h_out is not None:
+            res.data = h_out
+    else:
+        _cuda(x)
+        _check(_fn("decode_gemm", "zai_skinny_gemm")(
+            _ptr(y), _ptr(w), _ptr(x), None, None, None, None, None, 0.0, M, O, K, epilogue, _stream()), "skinny_gemm")
+    return y
+
+
 def linear(x, w, out_dtype=None):
-    """x [N, K] times w [O, K] transposed.  A matrix kept in 32-bit is multiplied in 32-bit."""
-    out_dtype = out_dtype or x.dtype
+    """x [N, K] times w [O, K] transposed.  x may be a LazyNorm.  Few rows in bfloat16 go to the
+    fused kernel; a matrix kept in 32-bit is multiplied in 32-bit; the rest is the library's."""
+    in_dtype = x.dtype
+    out_dtype = out_dtype or in_dtype
+    if in_dtype == torch.bfloat16 and out_dtype in (torch.bfloat16, torch.float32):
+        y = _skinny(x, w, _EPI_F32 if out_dtype == torch.float32 else _EPI_BF16, w.shape[0], out_dtype)
+        if y is not None:
+            return y
+    if isinstance(x, LazyNorm):
+        x = x.materialize(sys.modules[__name__])
     if x.dtype == torch.float32 or w.dtype == torch.float32 or out_dtype == torch.float32:
         if torch.backends.cuda.matmul.allow_tf32:
             torch.backends.cuda.matmul.allow_tf32 = False
@@ -159,6 +200,15 @@ def linear(x, w, out_dtype=None):
             return torch.mm(x, w.t(), out_dtype=torch.float32)
         return torch.matmul(x.float(), w.float().t()).to(out_dtype)
     return torch.matmul(x, w.t())
+
+
+def linear_swiglu(x, w_gate_up, ff_dim):
+    """silu(x . Wgate^T) * (x . Wup^T) with the two matrices stacked as [2F, K]."""
+    if x.dtype == torch.bfloat16:
+        y = _skinny(x, w_gate_up, _EPI_SWIGLU, ff_dim, torch.bfloat16)
+        if y is not None:
+            return y
+    return silu_mul(linear(x, w_gate_up), ff_dim)
 
 
 def silu_mul(gu, ff_dim):

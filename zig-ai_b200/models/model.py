@@ -12,7 +12,7 @@ from typing import Dict, List
 
 import torch
 
-from ..parts.base import ModelSpec, ParamDecl, make_part
+from ..parts.base import ModelSpec, ParamDecl, Residual, make_part
 
 
 class Model:
@@ -89,13 +89,12 @@ class Model:
     def forward(self, step, cache) -> torch.Tensor:
         """Run the step's tokens through the layers; return 32-bit logits [wanted, vocab]."""
         ops = step.ops
-        h = ops.embed(step.token_ids, self.table)
+        h = Residual(ops.embed(step.token_ids, self.table))
         pending = None
         for k, call in enumerate(self.spec.order):
             view = cache.view(k, step)
             h, pending = self.blocks[call.layer].forward(h, pending, step, view, call.cache_of is None)
         if step.n_wanted == 0:
-            return torch.empty((0, self.vocab_size), dtype=torch.float32, device=h.device)
-        hr = ops.gather_add(h, pending, step.logit_rows)
-        n = self.final_norm.forward(hr, None, step)
+            return torch.empty((0, self.vocab_size), dtype=torch.float32, device=h.data.device)
+        n = self.final_norm.forward(h, pending, step, lazy=True, rows=step.logit_rows)
         return ops.linear(n, self.head_w, out_dtype=torch.float32)

@@ -22,6 +22,7 @@ from .base import Mixer, PagedKVNeed, ParamDecl, make_part, register_part, PartS
 
 
 class Attention(Mixer):
+    accepts_lazy_input = True     # x goes straight into a product
     graph_safe = True      # forward launches kernels only; nothing is read back to the host
 
     def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, qk_norm: bool, eps: float,

@@ -82,6 +82,35 @@ class StateNeed:
     shape: Tuple[int, ...]
 
 
+# --------------------------------------------------------------------------- the residual stream
+class Residual:
+    """The 32-bit residual stream of a step.  A holder, because a fused kernel writes the updated
+    stream into a fresh buffer (other blocks of that kernel still read the old one)."""
+
+    def __init__(self, data):
+        self.data = data
+
+
+class LazyNorm:
+    """A norm that has not run yet: `norm(residual + delta) * gamma`, optionally on gathered rows.
+    A product kernel that can apply it on the fly takes it as its input (`ops.linear`,
+    `ops.linear_swiglu`); anything else calls `materialize`."""
+
+    def __init__(self, residual: Residual, delta, gamma, eps: float, dtype, rows=None):
+        self.residual, self.delta, self.gamma, self.eps, self.dtype, self.rows = residual, delta, gamma, eps, dtype, rows
+
+    @property
+    def shape(self):
+        n = self.rows.numel() if self.rows is not None else self.residual.data.shape[0]
+        return (n, self.residual.data.shape[1])
+
+    def materialize(self, ops):
+        if self.rows is not None:
+            h = ops.gather_add(self.residual.data, self.delta, self.rows)
+            return ops.add_rmsnorm(h, None, self.gamma, self.eps, self.dtype)
+        return ops.add_rmsnorm(self.residual.data, self.delta, self.gamma, self.eps, self.dtype)
+
+
 # --------------------------------------------------------------------------- interfaces
 class Part:
     """Base of every part.  `params()` declares tensors by local name (the layer's prefix is put
@@ -97,7 +126,11 @@ class Part:
 
 class Mixer(Part):
     """Mixes information between positions of a request.
-    forward(x [N, hidden] in the model's dtype, step, cache, write_cache) -> [N, hidden]."""
+    forward(x [N, hidden] in the model's dtype, step, cache, write_cache) -> [N, hidden].
+    A mixer (or feed-forward) whose first operation on x is `ops.linear` / `ops.linear_swiglu` may
+    set `accepts_lazy_input = True`; it is then given a `LazyNorm` where a kernel can fuse the norm."""
+
+    accepts_lazy_input = False
 
     def cache_need(self):
         return None
@@ -109,15 +142,19 @@ class Mixer(Part):
 class FeedForward(Part):
     """forward(x [N, hidden], step) -> [N, hidden]"""
 
+    accepts_lazy_input = False
+
     def forward(self, x, step):
         raise NotImplementedError
 
 
 class Norm(Part):
-    """forward(h [N, hidden] 32-bit residual, delta or None, step) -> normed [N, hidden] in the
-    model's dtype; adds `delta` into `h` in place first (the residual sum is 32-bit)."""
+    """forward(h, delta or None, step) -> normed [N, hidden] in the model's dtype.  `h` is the
+    32-bit residual stream, a `Residual` (or a plain tensor); `delta` is added into it first (the
+    residual sum is 32-bit).  With `lazy=True` the norm may return a `LazyNorm` for a product
+    kernel to apply; with `rows` only those rows are normed (the stream is left as it is)."""
 
-    def forward(self, h, delta, step):
+    def forward(self, h, delta, step, lazy=False, rows=None):
         raise NotImplementedError
 
 
@@ -134,8 +171,8 @@ class PositionEncoding(Part):
 
 class Block(Part):
     """Arrangement of a layer's parts.  forward(h, pending, step, cache, write_cache) ->
-    (h, pending): `h` is the 32-bit residual stream and `pending` a term not yet added to it, so
-    that the addition can be fused with the next norm."""
+    (h, pending): `h` is the 32-bit residual stream (a `Residual`) and `pending` a term not yet
+    added to it, so that the addition can be fused with the next norm."""
 
     def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, ff_norm: Norm):
         self.mixer, self.feed_forward = mixer, feed_forward

@@ -19,9 +19,9 @@ class PreNormResidual(Block):
         return {}
 
     def forward(self, h, pending, step, cache, write_cache=True):
-        r = self.mixer_norm.forward(h, pending, step)
+        r = self.mixer_norm.forward(h, pending, step, lazy=self.mixer.accepts_lazy_input)
         m = self.mixer.forward(r, step, cache, write_cache)
-        r2 = self.ff_norm.forward(h, m, step)
+        r2 = self.ff_norm.forward(h, m, step, lazy=self.feed_forward.accepts_lazy_input)
         f = self.feed_forward.forward(r2, step)
         return h, f
 

@@ -11,6 +11,7 @@ from .base import FeedForward, ParamDecl, register_part
 
 
 class SwiGlu(FeedForward):
+    accepts_lazy_input = True     # x goes straight into a product
     graph_safe = True      # forward launches kernels only; nothing is read back to the host
 
     def __init__(self, hidden: int, ff_dim: int):
@@ -30,10 +31,7 @@ class SwiGlu(FeedForward):
 
     def forward(self, x, step):
         ops = step.ops
-        if step.decode_only and ops.has_fused_decode(self.w_gate_up, x):
-            a = ops.decode_linear_swiglu(x, self.w_gate_up, self.ff_dim)
-        else:
-            a = ops.silu_mul(ops.linear(x, self.w_gate_up), self.ff_dim)
+        a = ops.linear_swiglu(x, self.w_gate_up, self.ff_dim)
         return ops.linear(a, self.w_down)
 
 

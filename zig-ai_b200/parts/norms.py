@@ -7,7 +7,7 @@ stream by the same kernel that normalises it.
 """
 from __future__ import annotations
 
-from .base import Norm, ParamDecl, register_part
+from .base import LazyNorm, Norm, ParamDecl, Residual, register_part
 
 
 class RmsNorm(Norm):
@@ -24,8 +24,12 @@ class RmsNorm(Norm):
         self.weight = tensors[self.weight_name]
         self.dtype = dtype
 
-    def forward(self, h, delta, step):
-        return step.ops.add_rmsnorm(h, delta, self.weight, self.eps, self.dtype)
+    def forward(self, h, delta, step, lazy=False, rows=None):
+        res = h if isinstance(h, Residual) else Residual(h)
+        x = LazyNorm(res, delta, self.weight, self.eps, self.dtype, rows)
+        if lazy and getattr(step.ops, "fuses_norm", False):
+            return x
+        return x.materialize(step.ops)
 
 
 register_part("norm", "rmsnorm", RmsNorm)

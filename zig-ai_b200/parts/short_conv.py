@@ -19,6 +19,7 @@ from .base import Mixer, ParamDecl, StateNeed, register_part
 
 
 class ShortConv(Mixer):
+    accepts_lazy_input = True     # x goes straight into a product
     graph_safe = True      # forward launches kernels only; nothing is read back to the host
 
     def __init__(self, hidden: int, conv_dim: int, taps: int, bias: bool):
