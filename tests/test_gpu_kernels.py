@@ -283,7 +283,7 @@ def test_skinny_gemm_plain_input(M, O, K):
     x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
     w = (torch.randn(O, K, generator=g) * K ** -0.5).to(torch.bfloat16).cuda()
     want = x.float() @ w.float().t()
-    if M * (K + 8) * 2 <= 200 * 1024:
+    if M <= 16:
         before = o.launches
         got = o.linear(x, w)
         assert o.launches == before + 1                 # the fused kernel ran, not the library
@@ -323,8 +323,9 @@ def test_skinny_gemm_with_norm_residual_and_gathered_rows(M, O, K, eps):
     old = lazy.residual.data
     got = o.linear(lazy, w)
     assert torch.allclose(got.float(), want, atol=3e-2, rtol=3e-2)
-    assert lazy.residual.data is not old and torch.equal(lazy.residual.data, hsum)    # the new residual stream
-    assert torch.equal(old, h)                                                        # the old one is untouched
+    assert torch.equal(lazy.residual.data, hsum)                                      # the new residual stream
+    if M <= 16:                                                                       # the fused kernel: a fresh buffer,
+        assert lazy.residual.data is not old and torch.equal(old, h)                  # the old one is untouched
     # without a pending term the stream stays where it is
     lazy = _lazy(h.clone(), None, gamma, eps)
     old = lazy.residual.data

@@ -4,6 +4,8 @@
 
 template <typename T>
 __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int F, size_t total) {
+    pdl_trigger();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const size_t t = i / F, f = i % F;
@@ -17,6 +19,5 @@ ZAI_API int zai_silu_mul(void* out, const void* gu, int dtype, int N, int F, cud
     if (total == 0) return ZAI_OK;
     const int threads = 256;
     const unsigned blocks = (unsigned)((total + threads - 1) / threads);
-    ZAI_DISPATCH(dtype, silu_mul_kernel<T><<<blocks, threads, 0, stream>>>((T*)out, (const T*)gu, F, total));
-    return launch_status();
+    ZAI_DISPATCH(dtype, return launch_pdl(silu_mul_kernel<T>, dim3(blocks), dim3(threads), 0, stream, (T*)out, (const T*)gu, F, total));
 }

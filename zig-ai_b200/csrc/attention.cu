@@ -20,6 +20,8 @@ __global__ void paged_attention_warp_kernel(T* __restrict__ out, const T* __rest
                                             const int* __restrict__ positions, const int* __restrict__ seq_idx,
                                             int page_size, int Hq, int Hkv, int D, float scale, int window) {
     extern __shared__ float qs[];                 // [D]
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
     const int kvh = h / (Hq / Hkv);
     const int pos = positions[t];
@@ -84,11 +86,11 @@ ZAI_API int zai_paged_attention_general(void* out, const void* q, const void* pa
     const dim3 grid(N, Hq);
     const size_t smem = (size_t)D * sizeof(float);
     if (D <= 64) {
-        ZAI_DISPATCH(dtype, paged_attention_warp_kernel<T, 2><<<grid, 32, smem, stream>>>(
+        ZAI_DISPATCH(dtype, return launch_pdl(paged_attention_warp_kernel<T, 2>, grid, dim3(32), smem, stream,
             (T*)out, (const T*)q, (const T*)pages, block_table, table_width, positions, seq_idx, page_size, Hq, Hkv,
             D, scale, window));
     } else {
-        ZAI_DISPATCH(dtype, paged_attention_warp_kernel<T, 8><<<grid, 32, smem, stream>>>(
+        ZAI_DISPATCH(dtype, return launch_pdl(paged_attention_warp_kernel<T, 8>, grid, dim3(32), smem, stream,
             (T*)out, (const T*)q, (const T*)pages, block_table, table_width, positions, seq_idx, page_size, Hq, Hkv,
             D, scale, window));
     }

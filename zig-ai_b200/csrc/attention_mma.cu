@@ -117,6 +117,8 @@ __global__ void __launch_bounds__(NTHREADS) prefill_mma_kernel(
     bf16* sv = sk + 2 * TILE * ST;                          // [2][64][ST]
     __shared__ int s_seq, s_i0;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_trigger();
+    pdl_wait();
     if (tid == 0) {
         int t = blockIdx.x, s = 0;
         for (; s < S; ++s) {
@@ -258,19 +260,23 @@ __global__ void __launch_bounds__(NTHREADS) prefill_mma_kernel(
 // ------------------------------------------------------------------------------------------ decode
 // part_o [B, Hq, n_chunks, D] unnormalised outputs; part_ml [B, Hq, n_chunks, 2]: maximum (in log2
 // units, already scaled) and sum.  A chunk with no visible key writes (-inf, 0).
+template <int D> struct DecodeStages { static constexpr int N = D <= 64 ? 4 : 3; };   // tiles in flight + 1
+
 template <int D>
 __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
     float* __restrict__ part_o, float* __restrict__ part_ml, const bf16* __restrict__ q,
     const bf16* __restrict__ pages, const int* __restrict__ block_table, int table_width,
     const int* __restrict__ positions, int page_size, int Hq, int Hkv, float scale_log2, int window) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    constexpr int ST = D + 8;
+    constexpr int ST = D + 8, NS = DecodeStages<D>::N;
     bf16* sq = reinterpret_cast<bf16*>(smem_raw);           // [16][ST]
-    bf16* sk = sq + 16 * ST;                                // [2][64][ST]
-    bf16* sv = sk + 2 * TILE * ST;                          // [2][64][ST]
+    bf16* sk = sq + 16 * ST;                                // [NS][64][ST]
+    bf16* sv = sk + NS * TILE * ST;                         // [NS][64][ST]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int chunk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z, n_chunks = gridDim.x;
     const int G = Hq / Hkv;
+    pdl_trigger();
+    pdl_wait();
     const int pos = positions[b];
     const int kend = pos + 1;
     const int kstart = window > 0 ? max(pos - window + 1, 0) : 0;
@@ -294,9 +300,15 @@ __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
         const bf16* src = valid ? q + ((size_t)b * Hq + hk * G + r) * D + c * 8 : q;
         cp_async16(sq + r * ST + c * 8, src, valid);
     }
-    load_kv_tile<D>(sk, pages, table, tile0 * TILE, lo, hi, page_size, page_stride, k_off, tid);
-    load_kv_tile<D>(sv, pages, table, tile0 * TILE, lo, hi, page_size, page_stride, v_off, tid);
-    cp_async_commit();
+    // the first NS-1 tiles start moving at once; one group is committed per tile slot, used or not
+#pragma unroll
+    for (int s = 0; s < NS - 1; ++s) {
+        if (tile0 + s < tile1) {
+            load_kv_tile<D>(sk + s * TILE * ST, pages, table, (tile0 + s) * TILE, lo, hi, page_size, page_stride, k_off, tid);
+            load_kv_tile<D>(sv + s * TILE * ST, pages, table, (tile0 + s) * TILE, lo, hi, page_size, page_stride, v_off, tid);
+        }
+        cp_async_commit();
+    }
 
     uint32_t qf[D / 16][4];
     float o[D / 8][4];
@@ -306,18 +318,18 @@ __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
     const int g = lane >> 2, tq = lane & 3;
 
     for (int t = tile0; t < tile1; ++t) {
-        const int buf = (t - tile0) & 1;
-        if (t + 1 < tile1) {
-            load_kv_tile<D>(sk + (buf ^ 1) * TILE * ST, pages, table, (t + 1) * TILE, lo, hi, page_size, page_stride,
-                            k_off, tid);
-            load_kv_tile<D>(sv + (buf ^ 1) * TILE * ST, pages, table, (t + 1) * TILE, lo, hi, page_size, page_stride,
-                            v_off, tid);
+        const int buf = (t - tile0) % NS;
+        cp_async_wait<NS - 2>();                            // tile t has arrived
+        __syncthreads();                                    // and everyone is done with tile t-1
+        {
+            const int nxt = t + NS - 1;
+            if (nxt < tile1) {
+                const int nb = (nxt - tile0) % NS;
+                load_kv_tile<D>(sk + nb * TILE * ST, pages, table, nxt * TILE, lo, hi, page_size, page_stride, k_off, tid);
+                load_kv_tile<D>(sv + nb * TILE * ST, pages, table, nxt * TILE, lo, hi, page_size, page_stride, v_off, tid);
+            }
             cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
         }
-        __syncthreads();
         if (t == tile0) {
             const int r = (((lane >> 3) & 1) << 3) + (lane & 7);
             const int dof = (lane >> 4) << 3;
@@ -363,8 +375,9 @@ __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
             pf[3] = pack_bf16(s1[2], s1[3]);
             pv_16keys<D>(o, pf, sv + (buf * TILE + warp * 16) * ST, lane);
         }
-        __syncthreads();
     }
+    cp_async_wait<0>();
+    __syncthreads();                                        // the tiles are no longer needed
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
@@ -414,6 +427,8 @@ __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
 template <int D>
 __global__ void decode_combine_kernel(bf16* __restrict__ out, const float* __restrict__ part_o,
                                       const float* __restrict__ part_ml, int n_chunks) {
+    pdl_trigger();
+    pdl_wait();
     const size_t bh = blockIdx.x;                           // b * Hq + h
     const float* ml = part_ml + bh * n_chunks * 2;
     float M = -INFINITY;
@@ -433,7 +448,7 @@ __global__ void decode_combine_kernel(bf16* __restrict__ out, const float* __res
 
 template <int D> static size_t prefill_smem() { return (size_t)5 * TILE * (D + 8) * sizeof(bf16); }
 template <int D> static size_t decode_smem() {
-    const size_t tiles = (size_t)(16 + 4 * TILE) * (D + 8) * sizeof(bf16);
+    const size_t tiles = (size_t)(16 + 2 * DecodeStages<D>::N * TILE) * (D + 8) * sizeof(bf16);
     const size_t comb = 16 * (D + 8) * sizeof(bf16) + (size_t)(4 * 16 * D + 2 * 4 * 16) * sizeof(float);
     return tiles > comb ? tiles : comb;
 }
@@ -449,9 +464,9 @@ static int launch_prefill(bf16* out, const bf16* q, const bf16* pages, const int
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    prefill_mma_kernel<D><<<dim3(n_tiles, Hq), NTHREADS, smem, stream>>>(
-        out, q, pages, block_table, table_width, cu_q, ctx_lens, S, page_size, Hq, Hkv, scale * 1.4426950408889634f, window);
-    return launch_status();
+    return launch_pdl(prefill_mma_kernel<D>, dim3(n_tiles, Hq), dim3(NTHREADS), smem, stream,
+                      out, q, pages, block_table, table_width, cu_q, ctx_lens, S, page_size, Hq, Hkv,
+                      scale * 1.4426950408889634f, window);
 }
 
 template <int D>
@@ -465,13 +480,12 @@ static int launch_decode(bf16* out, float* part_o, float* part_ml, const bf16* q
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    decode_mma_kernel<D><<<dim3(n_chunks, Hkv, B), NTHREADS, smem, stream>>>(
-        part_o, part_ml, q, pages, block_table, table_width, positions, page_size, Hq, Hkv,
-        scale * 1.4426950408889634f, window);
-    int e = launch_status();
+    int e = launch_pdl(decode_mma_kernel<D>, dim3(n_chunks, Hkv, B), dim3(NTHREADS), smem, stream,
+                       part_o, part_ml, q, pages, block_table, table_width, positions, page_size, Hq, Hkv,
+                       scale * 1.4426950408889634f, window);
     if (e) return e;
-    decode_combine_kernel<D><<<B * Hq, D <= 64 ? 64 : 128, 0, stream>>>(out, part_o, part_ml, n_chunks);
-    return launch_status();
+    return launch_pdl(decode_combine_kernel<D>, dim3(B * Hq), dim3(D <= 64 ? 64 : 128), 0, stream,
+                      out, (const float*)part_o, (const float*)part_ml, n_chunks);
 }
 
 #define ZAI_HEAD_DIMS(X) X(16) X(32) X(48) X(64) X(80) X(96) X(128)

@@ -48,6 +48,41 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 
 static inline int launch_status() { return (int)cudaGetLastError(); }
 
+// ---- programmatic dependent launch: a kernel launched this way may start while the kernel before
+// it on the stream still runs.  It must call pdl_wait() before it reads anything an earlier kernel
+// wrote and before it writes anything an earlier kernel may still read (so: before its first global
+// write); what it does before that (address arithmetic, loads of weights) overlaps the predecessor.
+// pdl_trigger() lets the kernel after this one begin its own start-up.  Both are no-ops in a kernel
+// launched the ordinary way.  ZAI_PDL=0 in the environment launches everything the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#include <stdlib.h>
+static inline bool pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("ZAI_PDL");
+        on = (e && e[0] == '0') ? 0 : 1;
+    }
+    return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // Calls `expr` with T bound to the element type that `dtype` names.
 #define ZAI_DISPATCH(dtype, ...)                                   \
     do {                                                           \

@@ -7,6 +7,8 @@
 template <typename T>
 __global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ table,
                              const int* __restrict__ ids, int H, int V) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     int id = ids[t];
     id = id < 0 ? 0 : (id >= V ? V - 1 : id);       // never read outside the table
@@ -19,6 +21,8 @@ __global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ tabl
 template <typename T>
 __global__ void gather_add_kernel(float* __restrict__ out, const float* __restrict__ h,
                                   const T* __restrict__ pending, const int* __restrict__ rows, int H) {
+    pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.x;
     const size_t src = (size_t)rows[r] * H;
     float* o = out + (size_t)r * H;
@@ -32,14 +36,12 @@ __global__ void gather_add_kernel(float* __restrict__ out, const float* __restri
 ZAI_API int zai_embed(float* out, const void* table, int table_dtype, const int* ids, int N, int H, int V,
                       cudaStream_t stream) {
     if (N <= 0) return ZAI_OK;
-    ZAI_DISPATCH(table_dtype, embed_kernel<T><<<N, 256, 0, stream>>>(out, (const T*)table, ids, H, V));
-    return launch_status();
+    ZAI_DISPATCH(table_dtype, return launch_pdl(embed_kernel<T>, dim3(N), dim3(256), 0, stream, out, (const T*)table, ids, H, V));
 }
 
 ZAI_API int zai_gather_add(float* out, const float* h, const void* pending, int pending_dtype, const int* rows,
                            int R, int H, cudaStream_t stream) {
     if (R <= 0) return ZAI_OK;
     ZAI_DISPATCH(pending_dtype,
-                 gather_add_kernel<T><<<R, 256, 0, stream>>>(out, h, (const T*)pending, rows, H));
-    return launch_status();
+                 return launch_pdl(gather_add_kernel<T>, dim3(R), dim3(256), 0, stream, out, h, (const T*)pending, rows, H));
 }

@@ -10,6 +10,8 @@ template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ delta,
                                    const float* __restrict__ gamma, T* __restrict__ out, float eps, int H) {
     __shared__ float red[33];
+    pdl_trigger();
+    pdl_wait();
     const size_t base = (size_t)blockIdx.x * H;
     float ss = 0.f;
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
@@ -30,6 +32,5 @@ ZAI_API int zai_add_rmsnorm(float* h, const void* delta, const float* gamma, voi
                             int N, int H, cudaStream_t stream) {
     if (N <= 0) return ZAI_OK;
     const int threads = H >= 2048 ? 512 : 256;
-    ZAI_DISPATCH(dtype, add_rmsnorm_kernel<T><<<N, threads, 0, stream>>>(h, (const T*)delta, gamma, (T*)out, eps, H));
-    return launch_status();
+    ZAI_DISPATCH(dtype, return launch_pdl(add_rmsnorm_kernel<T>, dim3(N), dim3(threads), 0, stream, h, (const T*)delta, gamma, (T*)out, eps, H));
 }

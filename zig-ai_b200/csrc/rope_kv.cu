@@ -10,13 +10,27 @@
 // The position is the token's own absolute position (the reference's kernel takes `row % N`,
 // layer_kernels.cu:351).  v is neither normed nor rotated.  The norm is 32-bit; the angle is the
 // product of the position and a frequency table computed on the host in 64-bit, and its sine and
-// cosine are taken in 64-bit and rounded to 32-bit once per token, then shared by all heads.
+// cosine are taken in 64-bit and rounded to 32-bit once per token and step (rope_table_kernel),
+// then shared by all heads and all layers with the same rotation.
 // One block per token; each warp takes heads in turn.
 #include "common.cuh"
 
+// table[t][i] = (cos, sin) of positions[t] * inv_freq[i]
+__global__ void rope_table_kernel(float2* __restrict__ table, const int* __restrict__ positions,
+                                  const double* __restrict__ inv_freq, int N, int half) {
+    pdl_trigger();
+    pdl_wait();
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= N * half) return;
+    const int t = idx / half, i = idx % half;
+    double s, c;
+    sincos((double)positions[t] * inv_freq[i], &s, &c);
+    table[idx] = make_float2((float)c, (float)s);
+}
+
 template <typename T>
 __global__ void qk_norm_rope_kernel(const T* __restrict__ qkv, int qkv_cols, const float* __restrict__ q_gamma,
-                                    const float* __restrict__ k_gamma, float eps, const double* __restrict__ inv_freq,
+                                    const float* __restrict__ k_gamma, float eps, const float2* __restrict__ cs_table,
                                     int rot, const int* __restrict__ positions, const int* __restrict__ seq_idx,
                                     const int* __restrict__ block_table, int table_width, T* __restrict__ pages,
                                     int page_size, T* __restrict__ q_out, T* __restrict__ k_out, int Hq, int Hkv,
@@ -27,13 +41,14 @@ __global__ void qk_norm_rope_kernel(const T* __restrict__ qkv, int qkv_cols, con
     float* sn = smem + half;                // [half] sin
     const int nwarp = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* buf = smem + 2 * half + (size_t)warp * D;
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int pos = positions[t];
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
-        double s, c;
-        sincos((double)pos * inv_freq[i], &s, &c);
-        cs[i] = (float)c;
-        sn[i] = (float)s;
+        const float2 v = cs_table[(size_t)t * half + i];
+        cs[i] = v.x;
+        sn[i] = v.y;
     }
     __syncthreads();
     size_t page_base = 0;
@@ -95,6 +110,8 @@ __global__ void kv_write_kernel(const T* __restrict__ k, int k_stride, const T* 
                                 const int* __restrict__ positions, const int* __restrict__ seq_idx,
                                 const int* __restrict__ block_table, int table_width, T* __restrict__ pages,
                                 int page_size, int Hkv, int D) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int pos = positions[t];
     const int page = block_table[(size_t)seq_idx[t] * table_width + pos / page_size];
@@ -107,8 +124,15 @@ __global__ void kv_write_kernel(const T* __restrict__ k, int k_stride, const T* 
     }
 }
 
+ZAI_API int zai_rope_table(float2* table, const int* positions, const double* inv_freq, int N, int half,
+                           cudaStream_t stream) {
+    if (N <= 0 || half <= 0) return ZAI_OK;
+    const int total = N * half;
+    return launch_pdl(rope_table_kernel, dim3((total + 127) / 128), dim3(128), 0, stream, table, positions, inv_freq, N, half);
+}
+
 ZAI_API int zai_qk_norm_rope(const void* qkv, int qkv_cols, int dtype, const float* q_gamma, const float* k_gamma,
-                             float eps, const double* inv_freq, int rot, const int* positions, const int* seq_idx,
+                             float eps, const float2* cs_table, int rot, const int* positions, const int* seq_idx,
                              const int* block_table, int table_width, void* pages, int page_size, void* q_out,
                              void* k_out, int N, int Hq, int Hkv, int D, int has_kv, int write,
                              cudaStream_t stream) {
@@ -117,18 +141,16 @@ ZAI_API int zai_qk_norm_rope(const void* qkv, int qkv_cols, int dtype, const flo
     const int threads = 128;
     const size_t smem = (size_t)(rot + (threads / 32) * D) * sizeof(float);
     if (smem > 48 * 1024) return ZAI_BAD_SIZE;
-    ZAI_DISPATCH(dtype, qk_norm_rope_kernel<T><<<N, threads, smem, stream>>>(
-        (const T*)qkv, qkv_cols, q_gamma, k_gamma, eps, inv_freq, rot, positions, seq_idx, block_table,
+    ZAI_DISPATCH(dtype, return launch_pdl(qk_norm_rope_kernel<T>, dim3(N), dim3(threads), smem, stream,
+        (const T*)qkv, qkv_cols, q_gamma, k_gamma, eps, cs_table, rot, positions, seq_idx, block_table,
         table_width, (T*)pages, page_size, (T*)q_out, (T*)k_out, Hq, Hkv, D, has_kv, write));
-    return launch_status();
 }
 
 ZAI_API int zai_kv_write(const void* k, int k_stride, const void* v, int v_stride, int dtype, const int* positions,
                          const int* seq_idx, const int* block_table, int table_width, void* pages, int page_size,
                          int N, int Hkv, int D, cudaStream_t stream) {
     if (N <= 0) return ZAI_OK;
-    ZAI_DISPATCH(dtype, kv_write_kernel<T><<<N, 128, 0, stream>>>(
+    ZAI_DISPATCH(dtype, return launch_pdl(kv_write_kernel<T>, dim3(N), dim3(128), 0, stream,
         (const T*)k, k_stride, (const T*)v, v_stride, positions, seq_idx, block_table, table_width, (T*)pages,
         page_size, Hkv, D));
-    return launch_status();
 }

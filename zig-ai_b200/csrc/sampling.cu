@@ -53,14 +53,43 @@ __device__ MaxIdx block_argmax(MaxIdx x, MaxIdx* red) {
     return red[32];
 }
 
+// The thread's best (value, first index) over a row, scanned with 16-byte loads, several in flight.
+__device__ __forceinline__ MaxIdx scan_row(const float* __restrict__ row, int V) {
+    MaxIdx x{-INFINITY, 0x7fffffff};
+    if ((V & 3) == 0 && (reinterpret_cast<size_t>(row) & 15) == 0) {
+        const float4* r4 = reinterpret_cast<const float4*>(row);
+        const int n4 = V >> 2;
+        for (int i = threadIdx.x; i < n4; i += 4 * blockDim.x) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int j = i + u * blockDim.x;
+                v[u] = j < n4 ? r4[j] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {                   // indices rise with u, then within the float4
+                const int j = (i + u * blockDim.x) << 2;
+                if (v[u].x > x.v) { x.v = v[u].x; x.i = j; }
+                if (v[u].y > x.v) { x.v = v[u].y; x.i = j + 1; }
+                if (v[u].z > x.v) { x.v = v[u].z; x.i = j + 2; }
+                if (v[u].w > x.v) { x.v = v[u].w; x.i = j + 3; }
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < V; i += blockDim.x) {
+            const float v = row[i];
+            if (v > x.v) { x.v = v; x.i = i; }              // a strided scan visits indices in rising order
+        }
+    }
+    return x;
+}
+
 __global__ void argmax_kernel(int* __restrict__ out, const float* __restrict__ logits, int V) {
     __shared__ MaxIdx red[33];
+    pdl_trigger();
+    pdl_wait();
     const float* row = logits + (size_t)blockIdx.x * V;
-    MaxIdx x{-INFINITY, 0x7fffffff};
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float v = row[i];
-        if (v > x.v) { x.v = v; x.i = i; }          // strided scan visits indices in rising order
-    }
+    MaxIdx x = scan_row(row, V);
     x = block_argmax(x, red);
     if (threadIdx.x == 0) out[blockIdx.x] = x.i == 0x7fffffff ? 0 : x.i;
 }
@@ -89,14 +118,12 @@ __global__ void sample_kernel(int* __restrict__ out, const float* __restrict__ l
     __shared__ float red[33];
     __shared__ float scan[SAMPLE_THREADS];
     __shared__ int chosen;
+    pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.x, tid = threadIdx.x;
     const float* row = logits + (size_t)r * V;
     const float T = temperature[r];
-    MaxIdx x{-INFINITY, 0x7fffffff};
-    for (int i = tid; i < V; i += blockDim.x) {
-        const float v = row[i];
-        if (v > x.v) { x.v = v; x.i = i; }
-    }
+    MaxIdx x = scan_row(row, V);
     x = block_argmax(x, redm);
     if (T <= 0.f) {
         if (tid == 0) out[r] = x.i == 0x7fffffff ? 0 : x.i;
@@ -204,8 +231,7 @@ __global__ void sample_kernel(int* __restrict__ out, const float* __restrict__ l
 
 ZAI_API int zai_argmax(int* out, const float* logits, int R, int V, cudaStream_t stream) {
     if (R <= 0) return ZAI_OK;
-    argmax_kernel<<<R, 1024, 0, stream>>>(out, logits, V);
-    return launch_status();
+    return launch_pdl(argmax_kernel, dim3(R), dim3(1024), 0, stream, out, logits, V);
 }
 
 ZAI_API int zai_repetition_penalty(float* logits, const int* tokens, const int* counts, const int* offsets,
@@ -218,6 +244,5 @@ ZAI_API int zai_repetition_penalty(float* logits, const int* tokens, const int* 
 ZAI_API int zai_sample(int* out, const float* logits, const float* temperature, const int* top_k, const float* top_p,
                        const float* uniform, int R, int V, cudaStream_t stream) {
     if (R <= 0) return ZAI_OK;
-    sample_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(out, logits, temperature, top_k, top_p, uniform, V);
-    return launch_status();
+    return launch_pdl(sample_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, stream, out, logits, temperature, top_k, top_p, uniform, V);
 }

@@ -22,6 +22,8 @@ __global__ void conv_rows_kernel(T* __restrict__ z, const T* __restrict__ bcx, c
                                  const float* __restrict__ bias, const float* __restrict__ state,
                                  const int* __restrict__ seq_idx, const int* __restrict__ cu_q,
                                  const int* __restrict__ slot_ids, int C, int L, int state_rows) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= C) return;
@@ -48,6 +50,8 @@ template <typename T>
 __global__ void conv_state_kernel(const T* __restrict__ bcx, float* __restrict__ state,
                                   const int* __restrict__ cu_q, const int* __restrict__ slot_ids,
                                   int C, int L, int state_rows) {
+    pdl_trigger();
+    pdl_wait();
     const int s = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= C) return;
@@ -76,6 +80,8 @@ template <typename T>
 __global__ void conv_decode_kernel(T* __restrict__ z, const T* __restrict__ bcx, const float* __restrict__ w,
                                    const float* __restrict__ bias, float* __restrict__ state,
                                    const int* __restrict__ slot_ids, int C, int L, int state_rows, int write_state) {
+    pdl_trigger();
+    pdl_wait();
     const int s = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= C) return;
@@ -107,15 +113,13 @@ ZAI_API int zai_short_conv(void* z, const void* bcx, int dtype, const float* w, 
     const int threads = 128;
     const unsigned bx = (unsigned)((C + threads - 1) / threads);
     if (decode_only) {
-        ZAI_DISPATCH(dtype, conv_decode_kernel<T><<<dim3(S, bx), threads, 0, stream>>>(
+        ZAI_DISPATCH(dtype, return launch_pdl(conv_decode_kernel<T>, dim3(S, bx), dim3(threads), 0, stream,
             (T*)z, (const T*)bcx, w, bias, state, slot_ids, C, L, state_rows, write_state));
-        return launch_status();
     }
-    ZAI_DISPATCH(dtype, conv_rows_kernel<T><<<dim3(N, bx), threads, 0, stream>>>(
-        (T*)z, (const T*)bcx, w, bias, state, seq_idx, cu_q, slot_ids, C, L, state_rows));
-    int e = launch_status();
+    int e = 0;
+    ZAI_DISPATCH(dtype, e = launch_pdl(conv_rows_kernel<T>, dim3(N, bx), dim3(threads), 0, stream,
+        (T*)z, (const T*)bcx, w, bias, (const float*)state, seq_idx, cu_q, slot_ids, C, L, state_rows));
     if (e || !write_state || L == 1) return e;
-    ZAI_DISPATCH(dtype, conv_state_kernel<T><<<dim3(S, bx), threads, 0, stream>>>(
+    ZAI_DISPATCH(dtype, return launch_pdl(conv_state_kernel<T>, dim3(S, bx), dim3(threads), 0, stream,
         (const T*)bcx, state, cu_q, slot_ids, C, L, state_rows));
-    return launch_status();
 }

@@ -33,6 +33,7 @@ class StepBatch:
     decode_only: bool = False      # every span is one token
     q_lens: Sequence[int] = ()
     request_ids: Sequence = ()
+    scratch: Dict = field(default_factory=dict)   # what kernels compute once per step (rotation tables)
 
 
 def pack_step(ops, dtype, device, spans, tables: Dict[int, List[List[int]]], pin: bool = False,

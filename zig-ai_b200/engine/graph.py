@@ -37,9 +37,8 @@ class StaticDecodeStep:
         self.tok, self.pos, self.sidx = take(B), take(B), take(B)
         self.cu, self.ctx, self.slots, self.rows = take(B + 1), take(B), take(B), take(B)
         self.tables = {g: take(B * w) for g, w in widths.items()}
-        self.sidx[0][:] = torch.arange(B, dtype=torch.int32)
-        self.cu[0][:] = torch.arange(B + 1, dtype=torch.int32)
-        self.rows[0][:] = torch.arange(B, dtype=torch.int32)
+        self._sidx, self._cu, self._rows = list(range(B)), list(range(B + 1)), list(range(B))
+        self.n_ints = n
         self.batch = StepBatch(
             ops=ops, dtype=dtype, n_tokens=B, n_seqs=B, n_wanted=B, token_ids=self.tok[1], positions=self.pos[1],
             seq_idx=self.sidx[1], cu_q=self.cu[1], ctx_lens=self.ctx[1], slot_ids=self.slots[1],
@@ -47,21 +46,28 @@ class StaticDecodeStep:
             block_tables={g: self.tables[g][1].view(B, w) for g, w in widths.items()},
             max_q_len=1, max_kv_len=max(widths.values(), default=1) * page_size, decode_only=True, q_lens=[1] * B, request_ids=[None] * B)
 
-    def fill(self, spans, tables: Dict[int, List[List[int]]]) -> None:
-        """spans: (request, ctx_len, [token], wanted, slot) for the live rows; the rest is padding."""
-        n = len(spans)
-        B = self.B
-        tok = [int(s[2][0]) for s in spans] + [0] * (B - n)
-        ctx = [int(s[1]) for s in spans] + [0] * (B - n)
-        slots = [int(s[4]) for s in spans] + [NULL_SLOT] * (B - n)
-        self.tok[0][:] = torch.tensor(tok, dtype=torch.int32)
-        self.pos[0][:] = torch.tensor(ctx, dtype=torch.int32)
-        self.ctx[0][:] = self.pos[0]
-        self.slots[0][:] = torch.tensor(slots, dtype=torch.int32)
+    def pack(self, spans, tables: Dict[int, List[List[int]]], host: torch.Tensor = None) -> torch.Tensor:
+        """Write the description of the live rows (request, ctx_len, [token], wanted, slot) and padding
+        into a pinned host buffer (this step's own if none is given)."""
+        host = self.host if host is None else host
+        n, B = len(spans), self.B
+        pad = B - n
+        tok = [int(s[2][0]) for s in spans] + [0] * pad
+        ctx = [int(s[1]) for s in spans] + [0] * pad
+        slots = [int(s[4]) for s in spans] + [NULL_SLOT] * pad
+        flat = tok + ctx + self._sidx + self._cu + ctx + slots + self._rows
         for g, w in self.widths.items():
-            rows = [r[:w] + [NULL_PAGE] * (w - len(r)) for r in tables[g]] + [[NULL_PAGE] * w] * (B - n)
-            self.tables[g][0][:] = torch.tensor(rows, dtype=torch.int32).view(-1)
-        self.dev.copy_(self.host, non_blocking=True)
+            for r in tables[g]:
+                flat += r[:w] if len(r) >= w else r + [NULL_PAGE] * (w - len(r))
+            flat += [NULL_PAGE] * (w * pad)
+        host.copy_(torch.tensor(flat, dtype=torch.int32))
+        return host
+
+    def fill(self, spans, tables: Dict[int, List[List[int]]]) -> None:
+        self.upload(self.pack(spans, tables))
+
+    def upload(self, host: torch.Tensor) -> None:
+        self.dev.copy_(host, non_blocking=True)
 
 
 class DecodeGraphs:
@@ -97,6 +103,23 @@ class DecodeGraphs:
             self.ops.launches = before               # captured, not run
         self.graphs[B] = (graph, static, logits)
         return self.graphs[B]
+
+    def prepare(self, spans, tables):
+        """Pack a step's description into a pinned buffer of its own, to be run later by `run_prepared`."""
+        B = self.bucket(len(spans))
+        _, static, _ = self.graphs.get(B) or self._capture(B)
+        host = torch.empty(static.n_ints, dtype=torch.int32).pin_memory()
+        return B, len(spans), static.pack(spans, tables, host)
+
+    def run_prepared(self, prepared) -> torch.Tensor:
+        B, n, host = prepared
+        graph, static, logits = self.graphs[B]
+        static.upload(host)
+        graph.replay()
+        self.replays += 1
+        if hasattr(self.ops, "launches"):
+            self.ops.launches += self.launches_per_replay[B]
+        return logits[:n]
 
     def run(self, spans, tables) -> torch.Tensor:
         B = self.bucket(len(spans))

