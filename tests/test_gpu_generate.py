@@ -81,8 +81,7 @@ def test_long_decoding(tiny_models, tmp_path, dtype):
     want = plain_lfm2.forward(c, W, toks).numpy()
     steps = traces.number(traces.decode_tail({"q0": toks}, tail=600))
     got = traces.run_trace(d, dtype, steps, max_tokens=640, out_dir=str(tmp_path / "o"), vocab=c["vocab_size"], page_size=8)
-    for p in range(600):
-        traces.check_row(got[("dq0", p)], want[p], dtype, f"{dtype} position {p}")
+    traces.check_request(np.stack([got[("dq0", p)] for p in range(600)]), want, dtype, f"{dtype} long decoding")
 
 
 def test_command_line(tiny_models):
@@ -94,3 +93,27 @@ def test_command_line(tiny_models):
     ids = [int(x) for x in line.split(")")[1].split()]
     assert ids == plain_greedy(tiny_models["A"], [5, 17, 3], 6)
     assert "decode:" in out.stdout and "prefill:" in out.stdout
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_repeated_step_shapes_run_as_graphs_and_agree(tiny_models, dtype):
+    """The same span lengths again and again (here: five requests of 40 tokens, each cut 24 + 16):
+    from the third time on the step is a replayed graph; its logits equal the eager ones."""
+    from zig_ai_b200.engine.runner import load_runner
+    d = tiny_models["B"]
+    c, W = plain_lfm2.read_config(d), plain_lfm2.read_weights(d)
+    reqs = traces.requests_for(c["vocab_size"], [40] * 5, 21)
+    runner = load_runner(d, dtype, max_tokens=512, page_size=8)
+    eager = load_runner(d, dtype, max_tokens=512, page_size=8, graphs=False)
+    for k, toks in reqs.items():
+        want = plain_lfm2.forward(c, W, toks).numpy()
+        outs = []
+        for r in (runner, eager):
+            r.add_request(k)
+            a = r.step([(k, toks[:24], list(range(24)))]).cpu().numpy().copy()
+            b = r.step([(k, toks[24:], list(range(16)))]).cpu().numpy().copy()
+            r.end_request(k)
+            outs.append(np.concatenate([a, b]))
+        traces.check_request(outs[0], want, dtype, f"{dtype} graphed request {k}")
+        assert np.array_equal(outs[0], outs[1]) or dtype == "bfloat16" or np.abs(outs[0] - outs[1]).max() < 1e-5
+    assert runner.shape_graphs.replays >= 4 and len(runner.shape_graphs.graphs) == 2

@@ -25,17 +25,19 @@ def plain(tiny_models):
     return out
 
 
+def rows_of(got, tag, k, n):
+    return np.stack([got[(tag + k, p)] for p in range(n)])
+
+
 def compare(got, reqs, want, tag, dtype):
     for k, toks in reqs.items():
-        for p in range(len(toks)):
-            traces.check_row(got[(tag + k, p)], want[k][p], dtype, f"{dtype} schedule '{tag}' request {k} position {p}")
+        traces.check_request(rows_of(got, tag, k, len(toks)), want[k], dtype, f"{dtype} schedule '{tag}' request {k}")
 
 
 def compare_schedules(got, reqs, tag_a, tag_b, dtype):
     for k, toks in reqs.items():
-        for p in range(len(toks)):
-            traces.check_same(got[(tag_a + k, p)], got[(tag_b + k, p)], dtype,
-                              f"{dtype} schedules '{tag_a}'/'{tag_b}' request {k} position {p}")
+        traces.check_same(rows_of(got, tag_a, k, len(toks)), rows_of(got, tag_b, k, len(toks)), dtype,
+                          f"{dtype} schedules '{tag_a}'/'{tag_b}' request {k}")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

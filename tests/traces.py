@@ -129,34 +129,49 @@ def run_trace(model_dir, dtype, steps, max_tokens, out_dir, vocab, page_size=16,
     return got
 
 
-# How far logits may be from the plain implementation's, per row of logits.
-#   float32: rounding of sums of a few hundred terms through a handful of layers, far below 5e-5 of
-#   the largest logit.
-#   bfloat16: every stored activation is rounded to 8 bits of mantissa (relative 2^-9); over the
-#   layers this adds up to a relative error of the row (L2) near 2 % on average with a tail to 5 %
-#   among 600 rows, the same whether the request runs whole or token by token.  A fault of the
-#   cache or the batch moves a row by tens of per cent; faults smaller than this noise are the 32-bit
-#   path's to show.  Rows of different ways of cutting the same request are also compared with each
-#   other: in 32-bit they agree to rounding of the sums; in bfloat16 a span and a single token run
-#   through different attention kernels (other orders of summation, probabilities rounded to
-#   bfloat16 at other places), so two runs differ like two independent roundings of the same row and
-#   get the same limit as a run against the plain implementation.
-def row_error(got, want):
-    """(relative L2 error of the row, largest absolute error over the row's largest |logit|)"""
-    err = np.abs(got.astype(np.float64) - want)
-    return float(np.linalg.norm(err) / max(np.linalg.norm(want), 1e-30)), float(err.max() / max(np.abs(want).max(), 1e-30))
+# How far logits may be from the plain implementation's.
+#   float32: every row within 5e-5 of its largest logit (rounding of sums of a few hundred terms
+#   through a handful of layers stays far below that).  Two ways of cutting the same request agree
+#   within 2e-5.
+#   bfloat16: every stored activation is rounded to 8 bits of mantissa (relative 2^-9), and the
+#   absolute error that this leaves in a row of logits follows the size of the activations, not the
+#   size of that row's logits.  So a row's error is measured against the request's logit scale (the
+#   root mean square over all its rows).  Measured on the tiny models: 2 % on average, up to 5-6 %
+#   for single rows, the same whether the request runs whole, token by token or in portions, and
+#   moving by a per cent when another kernel takes a product.  Asserted: the mean over a request's
+#   rows below 3 %, every row below 10 %.  A fault of the cache or of the batch moves a row by tens
+#   of per cent; smaller faults are the 32-bit path's to show, which runs the same cache and batch
+#   code, and the tensor-core kernels have their own tests against plain versions with tight limits.
+def request_errors(got_rows, want_rows):
+    """Per row: root-mean-square error over the request's root-mean-square logit."""
+    want = np.asarray(want_rows, dtype=np.float64)
+    got = np.asarray(got_rows, dtype=np.float64)
+    scale = max(float(np.sqrt((want ** 2).mean())), 1e-30)
+    return np.sqrt(((got - want) ** 2).mean(axis=1)) / scale
 
 
-def check_row(got, want, dtype, where):
-    l2, mx = row_error(got, want)
+def check_request(got_rows, want_rows, dtype, where):
+    """All rows of one request against the plain implementation."""
+    want = np.asarray(want_rows, dtype=np.float64)
+    got = np.asarray(got_rows, dtype=np.float64)
     if dtype == "float32":
-        assert mx < 5e-5, f"{where}: error {mx:.3e} of the row's largest logit"
+        err = np.abs(got - want).max(axis=1) / np.maximum(np.abs(want).max(axis=1), 1e-30)
+        assert err.max() < 5e-5, f"{where}: position {int(err.argmax())} is off by {err.max():.3e} of its largest logit"
     else:
-        assert l2 < 6e-2 and mx < 8e-2, f"{where}: relative L2 error {l2:.3e}, largest {mx:.3e}"
+        e = request_errors(got, want)
+        assert e.max() < 1e-1, f"{where}: position {int(e.argmax())} is off by {e.max():.3e} of the request's logit scale"
+        assert e.mean() < 3e-2, f"{where}: rows are off by {e.mean():.3e} of the request's logit scale on average"
 
 
-def check_same(a, b, dtype, where):
-    """Two ways of running the same position."""
-    l2, mx = row_error(a, b.astype(np.float64))
-    lim_l2, lim_mx = (2e-5, 2e-5) if dtype == "float32" else (6e-2, 8e-2)
-    assert l2 < lim_l2 and mx < lim_mx, f"{where}: two ways of cutting differ by L2 {l2:.3e}, largest {mx:.3e}"
+def check_same(a_rows, b_rows, dtype, where):
+    """Two ways of running the same request.  In 32-bit they agree to the rounding of the sums.  In
+    bfloat16 the two runs may go through different kernels (library product or few-rows kernel,
+    span or single-token attention) and are two independent roundings; their distance is held to
+    twice the limit of one run."""
+    a, b = np.asarray(a_rows, dtype=np.float64), np.asarray(b_rows, dtype=np.float64)
+    if dtype == "float32":
+        err = np.abs(a - b).max(axis=1) / np.maximum(np.abs(b).max(axis=1), 1e-30)
+        assert err.max() < 2e-5, f"{where}: position {int(err.argmax())} differs by {err.max():.3e}"
+    else:
+        e = request_errors(a, b)
+        assert e.max() < 2e-1 and e.mean() < 6e-2, f"{where}: two ways of cutting differ by {e.max():.3e} (mean {e.mean():.3e})"

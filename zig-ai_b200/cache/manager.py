@@ -21,6 +21,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional
 
+import numpy as np
 import torch
 
 from ..parts.base import PagedKVNeed, StateNeed
@@ -99,6 +100,9 @@ class CacheManager:
             else:
                 raise TypeError(f"unknown cache need {grp.need!r}")
         self.slots = IdPool(self.max_requests, first=1, what="slot")
+        # host mirror of every block table, one row per slot, ready to be gathered into a step's batch
+        self._rows = {gi: np.zeros((self.max_requests + 1, 16), dtype=np.int32) for gi in self.paged_groups()}
+        self._has_window = any(g.paged and g.need.window is not None for g in self.groups)
         self.requests: Dict[object, RequestCache] = {}
         self.pages_reused = 0
         self._ever_used = [set() for _ in self.groups]
@@ -133,7 +137,25 @@ class CacheManager:
             out[gi] = takes - gives_back
         return out
 
+    def _fits_already(self, rc: RequestCache, total_tokens: int) -> bool:
+        """True if the pages the request holds already cover `total_tokens` positions and no window
+        has anything to give back (the common case of a decoded token inside its last page)."""
+        if self._has_window:
+            return False
+        n_logical = -(-total_tokens // self.page_size)
+        return all(len(t) >= n_logical for t in rc.tables.values())
+
+    def _set_row(self, gi: int, slot: int, j: int, page: int) -> None:
+        rows = self._rows[gi]
+        if j >= rows.shape[1]:
+            grown = np.zeros((rows.shape[0], max(2 * rows.shape[1], j + 1)), dtype=np.int32)
+            grown[:, :rows.shape[1]] = rows
+            self._rows[gi] = rows = grown
+        rows[slot, j] = page
+
     def can_reserve(self, request_id, total_tokens: int) -> bool:
+        if self._fits_already(self.requests[request_id], total_tokens):
+            return True
         need = self.pages_to_take(request_id, total_tokens)
         return all(self.groups[gi].pool.n_free >= n for gi, n in need.items())
 
@@ -159,6 +181,9 @@ class CacheManager:
         rc = self.requests[request_id]
         if total_tokens < rc.num_tokens:
             raise ValueError("a request's cache does not shrink")
+        if self._fits_already(rc, total_tokens):
+            rc.num_tokens = total_tokens
+            return
         if not self.can_reserve(request_id, total_tokens):
             raise OutOfPages(f"request {request_id!r} needs pages {self.pages_to_take(request_id, total_tokens)}, "
                              f"free {[self.groups[g].pool.n_free for g in self.paged_groups()]}")
@@ -170,6 +195,7 @@ class CacheManager:
                 if table[j] != RELEASED:
                     grp.pool.free(table[j])
                     table[j] = RELEASED
+                    self._set_row(gi, rc.slot, j, NULL_PAGE)
             while len(table) < n_logical:
                 if len(table) < first:
                     table.append(RELEASED)
@@ -178,6 +204,7 @@ class CacheManager:
                 if p in self._ever_used[gi]:
                     self.pages_reused += 1
                 self._ever_used[gi].add(p)
+                self._set_row(gi, rc.slot, len(table), p)
                 table.append(p)
         rc.num_tokens = total_tokens
 
@@ -188,6 +215,7 @@ class CacheManager:
             for p in table:
                 if p != RELEASED:
                     self.groups[gi].pool.free(p)
+            self._rows[gi][rc.slot, :] = NULL_PAGE
         self.slots.free(rc.slot)
 
     def check(self) -> None:
@@ -216,13 +244,15 @@ class CacheManager:
         return out
 
     # ------------------------------------------------------------------ what a step sees
-    def table_rows(self, request_ids, group: int, width: int) -> List[List[int]]:
-        rows = []
-        for rid in request_ids:
-            t = self.requests[rid].tables[group]
-            row = [p if p != RELEASED else NULL_PAGE for p in t[:width]]
-            rows.append(row + [NULL_PAGE] * (width - len(row)))
-        return rows
+    def table_rows(self, request_ids, group: int, width: int) -> np.ndarray:
+        """The block tables of these requests, [len(request_ids), width] int32, released and unused
+        entries as the null page."""
+        slots = [self.requests[rid].slot for rid in request_ids]
+        rows = self._rows[group]
+        if width > rows.shape[1]:
+            self._set_row(group, 0, width - 1, NULL_PAGE)
+            rows = self._rows[group]
+        return rows[slots, :width]
 
     def view(self, call_index: int, step) -> CacheView:
         w = self.where[call_index]

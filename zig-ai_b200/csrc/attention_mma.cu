@@ -1,7 +1,7 @@
 // Paged attention on the tensor cores (bfloat16 operands, 32-bit accumulation and softmax):
 //
-//   * prefill: a flash-style kernel over block tables.  One block takes 64 consecutive query rows
-//     of one request and one query head; it walks the request's cached keys in tiles of 64 (the
+//   * prefill: a flash-style kernel over block tables.  One block takes 128 consecutive query rows
+//     of one request and one query head (eight warps of 16 rows); it walks the request's cached keys in tiles of 64 (the
 //     cached prefix and the rows of this very step, which are already in the pages), keeps the
 //     running maximum, the running sum and the unnormalised output of each row in registers and
 //     never writes scores to memory.  Spans of one token are handled too, so a mixed step needs no
@@ -56,20 +56,28 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // Rows t0 .. t0+63 of the keys (kv = 0) or values (kv = 1) of one head into shared memory, row
-// stride D + 8 elements; rows outside [kstart, kend) are filled with zeros.
-template <int D>
+// stride D + 8 elements; rows outside [kstart, kend) are filled with zeros.  `page_shift` is
+// log2(page_size) if that is a power of two, else -1.
+template <int D, int NT>
 __device__ __forceinline__ void load_kv_tile(bf16* dst, const bf16* __restrict__ pages, const int* __restrict__ table,
-                                             int t0, int kstart, int kend, int page_size, size_t page_stride,
-                                             size_t head_off, int tid) {
+                                             int t0, int kstart, int kend, int page_size, int page_shift,
+                                             size_t page_stride, size_t head_off, int tid) {
     constexpr int CH = D / 8;
-    for (int idx = tid; idx < TILE * CH; idx += NTHREADS) {
+    for (int idx = tid; idx < TILE * CH; idx += NT) {
         const int r = idx / CH, c = idx % CH;
         const int j = t0 + r;
         const bool valid = j >= kstart && j < kend;
         const bf16* src = pages;
         if (valid) {
-            const int page = table[j / page_size];
-            src = pages + (size_t)page * page_stride + head_off + (size_t)(j % page_size) * D + c * 8;
+            int page, off;
+            if (page_shift >= 0) {
+                page = table[j >> page_shift];
+                off = j & (page_size - 1);
+            } else {
+                page = table[j / page_size];
+                off = j % page_size;
+            }
+            src = pages + (size_t)page * page_stride + head_off + (size_t)off * D + c * 8;
         }
         cp_async16(dst + r * (D + 8) + c * 8, src, valid);
     }
@@ -105,36 +113,42 @@ __device__ __forceinline__ void pv_16keys(float (&o)[D / 8][4], const uint32_t (
 }
 
 // ------------------------------------------------------------------------------------------ prefill
+#define PREFILL_WARPS 8
+#define PREFILL_ROWS (16 * PREFILL_WARPS)      // query rows per block
+
 template <int D>
-__global__ void __launch_bounds__(NTHREADS) prefill_mma_kernel(
+__global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_mma_kernel(
     bf16* __restrict__ out, const bf16* __restrict__ q, const bf16* __restrict__ pages,
     const int* __restrict__ block_table, int table_width, const int* __restrict__ cu_q,
     const int* __restrict__ ctx_lens, int S, int page_size, int Hq, int Hkv, float scale_log2, int window) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    constexpr int ST = D + 8;
-    bf16* sq = reinterpret_cast<bf16*>(smem_raw);           // [64][ST]
-    bf16* sk = sq + TILE * ST;                              // [2][64][ST]
+    constexpr int ST = D + 8, NT = PREFILL_WARPS * 32, QR = PREFILL_ROWS;
+    bf16* sq = reinterpret_cast<bf16*>(smem_raw);           // [QR][ST]
+    bf16* sk = sq + QR * ST;                                // [2][64][ST]
     bf16* sv = sk + 2 * TILE * ST;                          // [2][64][ST]
     __shared__ int s_seq, s_i0;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
     pdl_trigger();
     pdl_wait();
     if (tid == 0) {
-        int t = blockIdx.x, s = 0;
+        // blocks are numbered from the last rows of the last request backwards: under the causal
+        // mask later rows have more keys to walk, and the longest blocks should start first
+        int t = gridDim.x - 1 - blockIdx.x, s = 0;
         for (; s < S; ++s) {
-            const int nt = (cu_q[s + 1] - cu_q[s] + TILE - 1) / TILE;
+            const int nt = (cu_q[s + 1] - cu_q[s] + QR - 1) / QR;
             if (t < nt) break;
             t -= nt;
         }
         s_seq = s;
-        s_i0 = t * TILE;
+        s_i0 = t * QR;
     }
     __syncthreads();
     const int s = s_seq, i0 = s_i0;
     if (s >= S) return;
     const int h = blockIdx.y, hk = h / (Hq / Hkv);
     const int row0 = cu_q[s], q_len = cu_q[s + 1] - row0, ctx = ctx_lens[s];
-    const int rows = min(TILE, q_len - i0);                 // valid query rows of this block
+    const int rows = min(QR, q_len - i0);                   // valid query rows of this block
     const int* table = block_table + (size_t)s * table_width;
     const size_t page_stride = (size_t)2 * Hkv * page_size * D;
     const size_t k_off = (size_t)hk * page_size * D, v_off = ((size_t)Hkv + hk) * page_size * D;
@@ -144,14 +158,14 @@ __global__ void __launch_bounds__(NTHREADS) prefill_mma_kernel(
     const int tile0 = kbeg / TILE, tile1 = (kend + TILE - 1) / TILE;
 
     // queries of the block: rows beyond the span are zeros
-    for (int idx = tid; idx < TILE * (D / 8); idx += NTHREADS) {
+    for (int idx = tid; idx < QR * (D / 8); idx += NT) {
         const int r = idx / (D / 8), c = idx % (D / 8);
         const bool valid = r < rows;
         const bf16* src = valid ? q + ((size_t)(row0 + i0 + r) * Hq + h) * D + c * 8 : q;
         cp_async16(sq + r * ST + c * 8, src, valid);
     }
-    load_kv_tile<D>(sk, pages, table, tile0 * TILE, kbeg, kend, page_size, page_stride, k_off, tid);
-    load_kv_tile<D>(sv, pages, table, tile0 * TILE, kbeg, kend, page_size, page_stride, v_off, tid);
+    load_kv_tile<D, NT>(sk, pages, table, tile0 * TILE, kbeg, kend, page_size, page_shift, page_stride, k_off, tid);
+    load_kv_tile<D, NT>(sv, pages, table, tile0 * TILE, kbeg, kend, page_size, page_shift, page_stride, v_off, tid);
     cp_async_commit();
 
     uint32_t qf[D / 16][4];
@@ -162,14 +176,15 @@ __global__ void __launch_bounds__(NTHREADS) prefill_mma_kernel(
     const int g = lane >> 2, tq = lane & 3;
     const int p0 = ctx + i0 + warp * 16 + g, p1 = p0 + 8;          // positions of the two rows
     const int lo0 = window > 0 ? p0 - window + 1 : 0, lo1 = window > 0 ? p1 - window + 1 : 0;
+    const bool warp_has_rows = warp * 16 < rows;
 
     for (int t = tile0; t < tile1; ++t) {
         const int buf = (t - tile0) & 1;
         if (t + 1 < tile1) {
-            load_kv_tile<D>(sk + (buf ^ 1) * TILE * ST, pages, table, (t + 1) * TILE, kbeg, kend, page_size,
-                            page_stride, k_off, tid);
-            load_kv_tile<D>(sv + (buf ^ 1) * TILE * ST, pages, table, (t + 1) * TILE, kbeg, kend, page_size,
-                            page_stride, v_off, tid);
+            load_kv_tile<D, NT>(sk + (buf ^ 1) * TILE * ST, pages, table, (t + 1) * TILE, kbeg, kend, page_size,
+                                page_shift, page_stride, k_off, tid);
+            load_kv_tile<D, NT>(sv + (buf ^ 1) * TILE * ST, pages, table, (t + 1) * TILE, kbeg, kend, page_size,
+                                page_shift, page_stride, v_off, tid);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -184,25 +199,32 @@ __global__ void __launch_bounds__(NTHREADS) prefill_mma_kernel(
         }
         const bf16* kt = sk + buf * TILE * ST;
         const bf16* vt = sv + buf * TILE * ST;
-        // a warp whose rows all lie before this tile's first key has nothing to do in it
+        // a warp whose rows all lie before this tile's first key, or that has no rows, skips the tile
         const int warp_last_pos = ctx + i0 + warp * 16 + 15;
-        if (t * TILE <= warp_last_pos) {
+        const int warp_first_lo = window > 0 ? ctx + i0 + warp * 16 - window + 1 : 0;
+        if (warp_has_rows && t * TILE <= warp_last_pos && (t + 1) * TILE > warp_first_lo) {
             float sc[8][4];
 #pragma unroll
             for (int i = 0; i < 8; ++i) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
 #pragma unroll
             for (int kb = 0; kb < 4; ++kb) qk_16keys<D>(sc[2 * kb], sc[2 * kb + 1], qf, kt + kb * 16 * ST, lane);
             float mx0 = -INFINITY, mx1 = -INFINITY;
+            const bool diag = (t + 1) * TILE - 1 > ctx + i0 + warp * 16 || window > 0;   // some element may be masked
+            if (diag) {
+#pragma unroll
+                for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int j = t * TILE + nt * 8 + 2 * tq + e;
+                        if (j > p0 || j < lo0) sc[nt][e] = -INFINITY;
+                        if (j > p1 || j < lo1) sc[nt][2 + e] = -INFINITY;
+                    }
+                }
+            }
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt) {
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int j = t * TILE + nt * 8 + 2 * tq + e;
-                    if (j > p0 || j < lo0) sc[nt][e] = -INFINITY;
-                    if (j > p1 || j < lo1) sc[nt][2 + e] = -INFINITY;
-                    mx0 = fmaxf(mx0, sc[nt][e]);
-                    mx1 = fmaxf(mx1, sc[nt][2 + e]);
-                }
+                mx0 = fmaxf(mx0, fmaxf(sc[nt][0], sc[nt][1]));
+                mx1 = fmaxf(mx1, fmaxf(sc[nt][2], sc[nt][3]));
             }
             mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
             mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
@@ -275,6 +297,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int chunk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z, n_chunks = gridDim.x;
     const int G = Hq / Hkv;
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
     pdl_trigger();
     pdl_wait();
     const int pos = positions[b];
@@ -304,8 +327,8 @@ __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
 #pragma unroll
     for (int s = 0; s < NS - 1; ++s) {
         if (tile0 + s < tile1) {
-            load_kv_tile<D>(sk + s * TILE * ST, pages, table, (tile0 + s) * TILE, lo, hi, page_size, page_stride, k_off, tid);
-            load_kv_tile<D>(sv + s * TILE * ST, pages, table, (tile0 + s) * TILE, lo, hi, page_size, page_stride, v_off, tid);
+            load_kv_tile<D, NTHREADS>(sk + s * TILE * ST, pages, table, (tile0 + s) * TILE, lo, hi, page_size, page_shift, page_stride, k_off, tid);
+            load_kv_tile<D, NTHREADS>(sv + s * TILE * ST, pages, table, (tile0 + s) * TILE, lo, hi, page_size, page_shift, page_stride, v_off, tid);
         }
         cp_async_commit();
     }
@@ -325,8 +348,8 @@ __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
             const int nxt = t + NS - 1;
             if (nxt < tile1) {
                 const int nb = (nxt - tile0) % NS;
-                load_kv_tile<D>(sk + nb * TILE * ST, pages, table, nxt * TILE, lo, hi, page_size, page_stride, k_off, tid);
-                load_kv_tile<D>(sv + nb * TILE * ST, pages, table, nxt * TILE, lo, hi, page_size, page_stride, v_off, tid);
+                load_kv_tile<D, NTHREADS>(sk + nb * TILE * ST, pages, table, nxt * TILE, lo, hi, page_size, page_shift, page_stride, k_off, tid);
+                load_kv_tile<D, NTHREADS>(sv + nb * TILE * ST, pages, table, nxt * TILE, lo, hi, page_size, page_shift, page_stride, v_off, tid);
             }
             cp_async_commit();
         }
@@ -446,7 +469,7 @@ __global__ void decode_combine_kernel(bf16* __restrict__ out, const float* __res
     }
 }
 
-template <int D> static size_t prefill_smem() { return (size_t)5 * TILE * (D + 8) * sizeof(bf16); }
+template <int D> static size_t prefill_smem() { return (size_t)(PREFILL_ROWS + 4 * TILE) * (D + 8) * sizeof(bf16); }
 template <int D> static size_t decode_smem() {
     const size_t tiles = (size_t)(16 + 2 * DecodeStages<D>::N * TILE) * (D + 8) * sizeof(bf16);
     const size_t comb = 16 * (D + 8) * sizeof(bf16) + (size_t)(4 * 16 * D + 2 * 4 * 16) * sizeof(float);
@@ -464,7 +487,7 @@ static int launch_prefill(bf16* out, const bf16* q, const bf16* pages, const int
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    return launch_pdl(prefill_mma_kernel<D>, dim3(n_tiles, Hq), dim3(NTHREADS), smem, stream,
+    return launch_pdl(prefill_mma_kernel<D>, dim3(n_tiles, Hq), dim3(PREFILL_WARPS * 32), smem, stream,
                       out, q, pages, block_table, table_width, cu_q, ctx_lens, S, page_size, Hq, Hkv,
                       scale * 1.4426950408889634f, window);
 }
@@ -528,6 +551,7 @@ ZAI_API int zai_decode_attention_mma(void* out, float* part_o, float* part_ml, c
 }
 
 ZAI_API int zai_decode_chunk_keys() { return CHUNK; }
+ZAI_API int zai_prefill_block_rows() { return PREFILL_ROWS; }
 
 // ------------------------------------------------------------------------------------------ no allocation
 // The same two kernels with their scratch in a static device array; see attention_no_alloc.h for

@@ -46,6 +46,57 @@ __global__ void conv_rows_kernel(T* __restrict__ z, const T* __restrict__ bcx, c
     z[(size_t)t * C + c] = from_float<T>(gate * y);
 }
 
+// bfloat16, C a multiple of 8: one thread per (row, 8 channels), 16-byte loads of B, C and x~
+__global__ void conv_rows_bf16x8_kernel(bf16* __restrict__ z, const bf16* __restrict__ bcx, const float* __restrict__ w,
+                                        const float* __restrict__ bias, const float* __restrict__ state,
+                                        const int* __restrict__ seq_idx, const int* __restrict__ cu_q,
+                                        const int* __restrict__ slot_ids, int C, int L, int state_rows) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+    if (c >= C) return;
+    const int s = seq_idx[t];
+    const int i = t - cu_q[s];
+    const float* st = state + ((size_t)slot_ids[s] * state_rows) * C;
+    float y[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) y[e] = bias ? bias[c + e] : 0.f;
+    for (int j = 0; j < L; ++j) {
+        const int r = i + j - (L - 1);
+        float u[8];
+        if (r >= 0) {
+            const bf16* row = bcx + (size_t)(t - i + r) * 3 * C;
+            const uint4 b4 = *reinterpret_cast<const uint4*>(row + c);
+            const uint4 x4 = *reinterpret_cast<const uint4*>(row + 2 * C + c);
+            const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&b4);
+            const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&x4);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 b = __bfloat1622float2(bp[e]), x = __bfloat1622float2(xp[e]);
+                u[2 * e] = b.x * x.x;
+                u[2 * e + 1] = b.y * x.y;
+            }
+        } else {
+            const float4 a = *reinterpret_cast<const float4*>(st + (size_t)(i + j) * C + c);
+            const float4 b = *reinterpret_cast<const float4*>(st + (size_t)(i + j) * C + c + 4);
+            u[0] = a.x; u[1] = a.y; u[2] = a.z; u[3] = a.w; u[4] = b.x; u[5] = b.y; u[6] = b.z; u[7] = b.w;
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[e] += w[(size_t)(c + e) * L + j] * u[e];
+    }
+    const uint4 g4 = *reinterpret_cast<const uint4*>(bcx + (size_t)t * 3 * C + C + c);
+    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g4);
+    uint4 o4;
+    __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float2 gte = __bfloat1622float2(gp[e]);
+        op[e] = __floats2bfloat162_rn(gte.x * y[2 * e], gte.y * y[2 * e + 1]);
+    }
+    *reinterpret_cast<uint4*>(z + (size_t)t * C + c) = o4;
+}
+
 template <typename T>
 __global__ void conv_state_kernel(const T* __restrict__ bcx, float* __restrict__ state,
                                   const int* __restrict__ cu_q, const int* __restrict__ slot_ids,
@@ -117,6 +168,11 @@ ZAI_API int zai_short_conv(void* z, const void* bcx, int dtype, const float* w, 
             (T*)z, (const T*)bcx, w, bias, state, slot_ids, C, L, state_rows, write_state));
     }
     int e = 0;
+    if (dtype == ZAI_BF16 && (C & 7) == 0) {
+        const int c8 = C / 8, th = c8 < 128 ? ((c8 + 31) / 32) * 32 : 128;
+        e = launch_pdl(conv_rows_bf16x8_kernel, dim3(N, (c8 + th - 1) / th), dim3(th), 0, stream, (bf16*)z, (const bf16*)bcx, w,
+                       bias, (const float*)state, seq_idx, cu_q, slot_ids, C, L, state_rows);
+    } else
     ZAI_DISPATCH(dtype, e = launch_pdl(conv_rows_kernel<T>, dim3(N, bx), dim3(threads), 0, stream,
         (T*)z, (const T*)bcx, w, bias, (const float*)state, seq_idx, cu_q, slot_ids, C, L, state_rows));
     if (e || !write_state || L == 1) return e;

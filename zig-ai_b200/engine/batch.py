@@ -10,6 +10,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Sequence
 
+import numpy as np
 import torch
 
 
@@ -36,19 +37,33 @@ class StepBatch:
     scratch: Dict = field(default_factory=dict)   # what kernels compute once per step (rotation tables)
 
 
-def pack_step(ops, dtype, device, spans, tables: Dict[int, List[List[int]]], pin: bool = False,
-              pad_to: int = 0) -> StepBatch:
-    """Build the device-side description from host lists with one host-to-device copy.
-    `spans` is a list of (request_id, ctx_len, tokens, wanted offsets, slot)."""
+@dataclass
+class PackedLayout:
+    """Where the pieces of a packed step lie in its flat int32 buffer."""
+    N: int
+    S: int
+    R: int
+    tables: Dict[int, tuple]           # group -> (offset, width)
+    total: int
+    q_lens: List[int]
+    ctx: List[int]
+    request_ids: List
+
+
+def pack_host(spans, tables: Dict[int, "np.ndarray"], widths: Dict[int, int] = None):
+    """Flatten a step's description into one int32 array: tokens, positions, row->request, span
+    starts, context lengths, slots, wanted rows, then each group's block tables [S, width].
+    `spans` is a list of (request_id, ctx_len, tokens, wanted offsets, slot); `widths` fixes the
+    table widths (a captured graph needs them constant), default: as wide as the tables given."""
     S = len(spans)
     tok, pos, sidx, cu, ctx, slots, rows, q_lens, rids = [], [], [], [0], [], [], [], [], []
+    at = 0
     for s, (rid, c, tokens, want, slot) in enumerate(spans):
         n = len(tokens)
-        base = len(tok)
-        tok.extend(int(t) for t in tokens)
-        pos.extend(range(c, c + n))
-        sidx.extend([s] * n)
-        cu.append(base + n)
+        tok.append(np.asarray(tokens, dtype=np.int32))
+        pos.append(np.arange(c, c + n, dtype=np.int32))
+        sidx.append(np.full(n, s, dtype=np.int32))
+        cu.append(at + n)
         ctx.append(c)
         slots.append(slot)
         q_lens.append(n)
@@ -56,31 +71,50 @@ def pack_step(ops, dtype, device, spans, tables: Dict[int, List[List[int]]], pin
         for w in want:
             if not 0 <= w < n:
                 raise ValueError(f"wanted place {w} is outside the {n} tokens of request {rid!r}")
-            rows.append(base + w)
-    N, R = len(tok), len(rows)
-    parts = [tok, pos, sidx, cu, ctx, slots, rows]
-    widths = {}
+            rows.append(at + w)
+        at += n
+    parts = tok + pos + sidx + [np.array(cu + ctx + slots + rows, dtype=np.int32)]
+    N, R = at, len(rows)
+    off = 3 * N + (S + 1) + 2 * S + R
+    layout_tables = {}
     for g, t in tables.items():
-        widths[g] = len(t[0]) if t else 1
-        parts.append([p for row in t for p in row])
-    flat = [x for p in parts for x in p]
-    host = torch.tensor(flat, dtype=torch.int32)
-    if pin and device.type == "cuda":
-        host = host.pin_memory()
-    dev = host.to(device, non_blocking=True) if device.type == "cuda" else host
-    off = 0
-    views = []
-    for p in parts:
-        views.append(dev[off:off + len(p)])
-        off += len(p)
-    bt = {}
-    for i, g in enumerate(tables):
-        bt[g] = views[7 + i].view(S, widths[g]) if S else views[7 + i].view(0, 1)
+        m = np.asarray(t, dtype=np.int32).reshape(S, -1)
+        w = widths[g] if widths else max(m.shape[1], 1)
+        if m.shape[1] != w:
+            fixed = np.zeros((S, w), dtype=np.int32)
+            cols = min(w, m.shape[1])
+            fixed[:, :cols] = m[:, :cols]
+            m = fixed
+        parts.append(m.reshape(-1))
+        layout_tables[g] = (off, w)
+        off += S * w
+    flat = np.concatenate(parts) if parts else np.zeros(0, np.int32)
+    return flat, PackedLayout(N, S, R, layout_tables, off, q_lens, ctx, rids)
+
+
+def batch_views(ops, dtype, dev: torch.Tensor, lay: PackedLayout) -> StepBatch:
+    """A StepBatch whose tensors are views of the flat device buffer `dev`."""
+    N, S, R = lay.N, lay.S, lay.R
+    sizes = [N, N, N, S + 1, S, S, R]
+    views, at = [], 0
+    for n in sizes:
+        views.append(dev[at:at + n])
+        at += n
+    bt = {g: (dev[o:o + S * w].view(S, w) if S else dev[o:o].view(0, 1)) for g, (o, w) in lay.tables.items()}
     return StepBatch(
         ops=ops, dtype=dtype, n_tokens=N, n_seqs=S, n_wanted=R,
         token_ids=views[0], positions=views[1], seq_idx=views[2], cu_q=views[3], ctx_lens=views[4],
         slot_ids=views[5], logit_rows=views[6], block_tables=bt,
-        max_q_len=max(q_lens) if q_lens else 0,
-        max_kv_len=max((c + n for c, n in zip(ctx, q_lens)), default=0),
-        decode_only=all(n == 1 for n in q_lens) and S > 0,
-        q_lens=q_lens, request_ids=rids)
+        max_q_len=max(lay.q_lens) if lay.q_lens else 0,
+        max_kv_len=max((c + n for c, n in zip(lay.ctx, lay.q_lens)), default=0),
+        decode_only=all(n == 1 for n in lay.q_lens) and S > 0,
+        q_lens=lay.q_lens, request_ids=lay.request_ids)
+
+
+def pack_step(ops, dtype, device, spans, tables: Dict[int, "np.ndarray"], pin: bool = False) -> StepBatch:
+    """Build the device-side description from host data with one host-to-device copy."""
+    flat, lay = pack_host(spans, tables)
+    host = torch.empty(lay.total, dtype=torch.int32, pin_memory=bool(pin and device.type == "cuda"))
+    host.numpy()[:] = flat
+    dev = host.to(device, non_blocking=True) if device.type == "cuda" else host
+    return batch_views(ops, dtype, dev, lay)

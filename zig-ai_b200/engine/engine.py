@@ -70,15 +70,14 @@ class Engine:
         ended = list(plan.failed)
         if plan.entries:
             entries = [(e.request.request_id, e.tokens, [len(e.tokens) - 1] if e.sample else []) for e in plan.entries]
-            logits = self.runner.step(entries)
+            logits = self.runner.step(entries, trusted=True)
             wanting = [e.request for e in plan.entries if e.sample]
             ids = self.sampler.sample(logits, [r.params for r in wanting], [len(r.output) for r in wanting],
                                       [r.output for r in wanting])
             sampled = {r.request_id: t for r, t in zip(wanting, ids)}
             self.n_steps += 1
             self.n_generated += len(ids)
-            self.n_prompt_tokens += plan.n_tokens - sum(1 for e in plan.entries if len(e.tokens) == 1 and e.sample
-                                                        and e.request.computed >= len(e.request.prompt))
+            self.n_prompt_tokens += plan.n_tokens
             ended += self.scheduler.commit(plan, sampled)
         for r in ended:
             self.requests.pop(r.request_id, None)
@@ -108,7 +107,7 @@ class Engine:
 
     def stats(self) -> dict:
         out = dict(self.runner.cache.stats())
-        out.update(steps=self.n_steps, generated=self.n_generated, prompt_tokens=self.n_prompt_tokens,
+        out.update(steps=self.n_steps, generated=self.n_generated, tokens_run=self.n_prompt_tokens,
                    preemptions=self.scheduler.n_preemptions, running=len(self.scheduler.running),
                    waiting=len(self.scheduler.waiting))
         return out

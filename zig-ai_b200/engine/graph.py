@@ -11,6 +11,7 @@ from __future__ import annotations
 
 from typing import Dict, List
 
+import numpy as np
 import torch
 
 from ..cache.manager import NULL_PAGE, NULL_SLOT
@@ -37,8 +38,20 @@ class StaticDecodeStep:
         self.tok, self.pos, self.sidx = take(B), take(B), take(B)
         self.cu, self.ctx, self.slots, self.rows = take(B + 1), take(B), take(B), take(B)
         self.tables = {g: take(B * w) for g, w in widths.items()}
-        self._sidx, self._cu, self._rows = list(range(B)), list(range(B + 1)), list(range(B))
         self.n_ints = n
+        # layout: tok[B] pos[B] seq_idx[B] cu[B+1] ctx[B] slots[B] rows[B] tables...; constant parts and
+        # padding (token 0, position 0, null slot, null page) come from a template
+        t = np.zeros(n, dtype=np.int32)
+        t[2 * B:3 * B] = np.arange(B)
+        t[3 * B:4 * B + 1] = np.arange(B + 1)
+        t[5 * B + 1:6 * B + 1] = NULL_SLOT
+        t[6 * B + 1:7 * B + 1] = np.arange(B)
+        t[7 * B + 1:] = NULL_PAGE
+        self._template = t
+        self._table_off, o = {}, 7 * B + 1
+        for g, w in widths.items():
+            self._table_off[g] = o
+            o += B * w
         self.batch = StepBatch(
             ops=ops, dtype=dtype, n_tokens=B, n_seqs=B, n_wanted=B, token_ids=self.tok[1], positions=self.pos[1],
             seq_idx=self.sidx[1], cu_q=self.cu[1], ctx_lens=self.ctx[1], slot_ids=self.slots[1],
@@ -46,21 +59,27 @@ class StaticDecodeStep:
             block_tables={g: self.tables[g][1].view(B, w) for g, w in widths.items()},
             max_q_len=1, max_kv_len=max(widths.values(), default=1) * page_size, decode_only=True, q_lens=[1] * B, request_ids=[None] * B)
 
-    def pack(self, spans, tables: Dict[int, List[List[int]]], host: torch.Tensor = None) -> torch.Tensor:
+    def pack(self, spans, tables, host: torch.Tensor = None) -> torch.Tensor:
         """Write the description of the live rows (request, ctx_len, [token], wanted, slot) and padding
-        into a pinned host buffer (this step's own if none is given)."""
+        into a pinned host buffer (this step's own if none is given).  `tables[g]` is [n, >= width]."""
         host = self.host if host is None else host
+        hv = host.numpy()
         n, B = len(spans), self.B
-        pad = B - n
-        tok = [int(s[2][0]) for s in spans] + [0] * pad
-        ctx = [int(s[1]) for s in spans] + [0] * pad
-        slots = [int(s[4]) for s in spans] + [NULL_SLOT] * pad
-        flat = tok + ctx + self._sidx + self._cu + ctx + slots + self._rows
-        for g, w in self.widths.items():
-            for r in tables[g]:
-                flat += r[:w] if len(r) >= w else r + [NULL_PAGE] * (w - len(r))
-            flat += [NULL_PAGE] * (w * pad)
-        host.copy_(torch.tensor(flat, dtype=torch.int32))
+        hv[:] = self._template
+        if n:
+            tok = np.fromiter((s[2][0] for s in spans), dtype=np.int32, count=n)
+            ctx = np.fromiter((s[1] for s in spans), dtype=np.int32, count=n)
+            slots = np.fromiter((s[4] for s in spans), dtype=np.int32, count=n)
+            hv[0:n] = tok
+            hv[B:B + n] = ctx
+            hv[4 * B + 1:4 * B + 1 + n] = ctx
+            hv[5 * B + 1:5 * B + 1 + n] = slots
+            for g, w in self.widths.items():
+                off = self._table_off[g]
+                t = np.asarray(tables[g], dtype=np.int32)
+                cols = min(w, t.shape[1]) if t.ndim == 2 else 0
+                if cols:
+                    hv[off:off + B * w].reshape(B, w)[:n, :cols] = t[:, :cols]
         return host
 
     def fill(self, spans, tables: Dict[int, List[List[int]]]) -> None:
@@ -68,6 +87,88 @@ class StaticDecodeStep:
 
     def upload(self, host: torch.Tensor) -> None:
         self.dev.copy_(host, non_blocking=True)
+
+
+class ShapeGraphs:
+    """Graphs for steps that are not single-token steps but come again with exactly the same shape
+    (the same span lengths and wanted rows): a prompt cut into portions of the token budget, equal
+    prompts.  A shape is captured the third time it is seen; a few shapes are kept."""
+
+    KEEP = 6
+    SEEN_BEFORE_CAPTURE = 2
+
+    def __init__(self, model, cache, ops, dtype, device, widths: Dict[int, int]):
+        self.model, self.cache, self.ops, self.dtype, self.device, self.widths = model, cache, ops, dtype, device, widths
+        self.seen: Dict[tuple, int] = {}
+        self.graphs: Dict[tuple, tuple] = {}          # key -> (graph, host, dev, logits, launches)
+        self.replays = 0
+
+    @staticmethod
+    def key(spans) -> tuple:
+        return tuple((len(s[2]), tuple(s[3])) for s in spans)
+
+    def run(self, spans, tables):
+        """Logits if this shape has a graph or has earned one, else None (the caller runs it eagerly)."""
+        from .batch import batch_views, pack_host
+        k = self.key(spans)
+        entry = self.graphs.get(k)
+        if entry is None:
+            n = self.seen.get(k, 0)
+            self.seen[k] = n + 1
+            if len(self.seen) > 4096:
+                self.seen.clear()
+            if n < self.SEEN_BEFORE_CAPTURE:
+                return None
+            flat, lay = pack_host(spans, tables, self.widths)
+            host = torch.empty(lay.total, dtype=torch.int32).pin_memory()
+            host.numpy()[:] = flat
+            dev = host.to(self.device)
+            batch = batch_views(self.ops, self.dtype, dev, lay)
+            batch.max_kv_len = max(self.widths.values(), default=1) * self.cache.page_size
+            # the capture's own warm-up would run the step three times; state that a step changes in
+            # place (conv state, pages) must see it once.  So this step runs eagerly now, and the
+            # graph is captured from a dry run on the null request's slot and page afterwards.
+            return self._capture_later(k, spans, tables, lay, host, dev, batch)
+        graph, host, dev, logits, launches = entry
+        flat, _ = pack_host(spans, tables, self.widths)
+        host.numpy()[:] = flat
+        dev.copy_(host, non_blocking=True)
+        graph.replay()
+        self.replays += 1
+        if hasattr(self.ops, "launches"):
+            self.ops.launches += launches
+        self.graphs[k] = self.graphs.pop(k)           # most recently used last
+        return logits
+
+    def _capture_later(self, k, spans, tables, lay, host, dev, batch):
+        from .batch import pack_host
+        from ..cache.manager import NULL_PAGE, NULL_SLOT
+        # dry-run description: same shape, every span on the null slot and the null page at position 0
+        dry = [(None, 0, s[2], s[3], NULL_SLOT) for s in spans]
+        dry_tables = {g: np.zeros((len(spans), 1), dtype=np.int32) for g in tables}
+        flat, _ = pack_host(dry, dry_tables, self.widths)
+        # 1. the real step, eagerly, on the static buffers
+        logits_now = self.model.forward(batch, self.cache)
+        # 2. warm-up and capture on the dry description
+        host.numpy()[:] = flat
+        dev.copy_(host)
+        stream = torch.cuda.Stream(device=self.device)
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            self.model.forward(batch, self.cache)
+        torch.cuda.current_stream().wait_stream(stream)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        before = getattr(self.ops, "launches", 0)
+        with torch.cuda.graph(graph):
+            logits = self.model.forward(batch, self.cache)
+        launches = getattr(self.ops, "launches", 0) - before
+        if hasattr(self.ops, "launches"):
+            self.ops.launches = before
+        while len(self.graphs) >= self.KEEP:
+            self.graphs.pop(next(iter(self.graphs)))
+        self.graphs[k] = (graph, host, dev, logits, launches)
+        return logits_now
 
 
 class DecodeGraphs:

@@ -11,6 +11,7 @@ from __future__ import annotations
 
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..cache import CacheManager, OutOfPages
@@ -31,6 +32,7 @@ class ModelRunner:
         self.steps = 0
         self.tokens_run = 0
         self.graphs = None
+        self.shape_graphs = None
         self.use_graphs = False
 
     def enable_graphs(self, max_positions: int) -> bool:
@@ -39,9 +41,10 @@ class ModelRunner:
         parts = [p for b in self.model.blocks for p in (b, b.mixer, b.feed_forward, b.mixer_norm, b.ff_norm)]
         if self.device.type != "cuda" or not all(getattr(p, "graph_safe", False) for p in parts + [self.model.final_norm]):
             return False
-        from .graph import DecodeGraphs
+        from .graph import DecodeGraphs, ShapeGraphs
         self.graphs = DecodeGraphs(self.model, self.cache, self.ops, self.dtype, self.device,
                                    min(max_positions, self.cache.num_pages * self.cache.page_size))
+        self.shape_graphs = ShapeGraphs(self.model, self.cache, self.ops, self.dtype, self.device, self.graphs.widths)
         self.use_graphs = True
         return True
 
@@ -63,45 +66,50 @@ class ModelRunner:
         del self.processed[request_id]
 
     # ------------------------------------------------------------------ the step
-    def _reserve(self, entries: Sequence[Tuple[object, Sequence[int], Sequence[int]]]):
+    def _reserve(self, entries: Sequence[Tuple[object, Sequence[int], Sequence[int]]], trusted: bool = False):
         """Check the entries and reserve their pages (all or none).  Returns the spans
-        (request, ctx_len, tokens, wanted, slot) and the requests' block tables by group."""
+        (request, ctx_len, tokens, wanted, slot) and the requests' block tables by group.
+        `trusted`: the caller (the scheduler) has checked the tokens and reserved the pages."""
         if not entries:
             raise StepError("a step needs at least one entry")
-        seen = set()
-        V, max_pos = self.model.vocab_size, self.model.spec.max_positions
-        for rid, tokens, _want in entries:
-            if rid in seen:
-                raise StepError(f"request {rid!r} appears twice in one step")
-            seen.add(rid)
-            if rid not in self.processed:
-                raise StepError(f"request {rid!r} was not added")
-            if len(tokens) < 1:
-                raise StepError(f"request {rid!r} brings no tokens")
-            bad = [int(t) for t in tokens if not 0 <= int(t) < V]
-            if bad:
-                raise StepError(f"request {rid!r}: token ids {bad[:8]} are outside the vocabulary of {V}")
-            if self.processed[rid] + len(tokens) > max_pos:
-                raise StepError(f"request {rid!r} would reach {self.processed[rid] + len(tokens)} positions; "
-                                f"the model allows {max_pos}")
-        # all-or-nothing reservation over the whole step
-        demand: Dict[int, int] = {}
-        for rid, tokens, _want in entries:
-            for g, n in self.cache.pages_to_take(rid, self.processed[rid] + len(tokens)).items():
-                demand[g] = demand.get(g, 0) + n
-        for g, n in demand.items():
-            if n > self.cache.groups[g].pool.n_free:
-                raise OutOfPages(f"the step needs {n} more pages of group {g}; "
-                                 f"{self.cache.groups[g].pool.n_free} are free")
-        for rid, tokens, _want in entries:
-            self.cache.reserve(rid, self.processed[rid] + len(tokens))
-        spans = [(rid, self.processed[rid], tokens, want, self.cache.requests[rid].slot)
-                 for rid, tokens, want in entries]
+        if not trusted:
+            seen = set()
+            V, max_pos = self.model.vocab_size, self.model.spec.max_positions
+            for rid, tokens, _want in entries:
+                if rid in seen:
+                    raise StepError(f"request {rid!r} appears twice in one step")
+                seen.add(rid)
+                if rid not in self.processed:
+                    raise StepError(f"request {rid!r} was not added")
+                if len(tokens) < 1:
+                    raise StepError(f"request {rid!r} brings no tokens")
+                arr = np.asarray(tokens)
+                if arr.dtype.kind not in "iu" or arr.min() < 0 or arr.max() >= V:
+                    bad = [int(t) for t in tokens if not 0 <= int(t) < V]
+                    raise StepError(f"request {rid!r}: token ids {bad[:8]} are outside the vocabulary of {V}")
+                if self.processed[rid] + len(tokens) > max_pos:
+                    raise StepError(f"request {rid!r} would reach {self.processed[rid] + len(tokens)} positions; "
+                                    f"the model allows {max_pos}")
+            # all-or-nothing reservation over the whole step
+            demand: Dict[int, int] = {}
+            for rid, tokens, _want in entries:
+                if self.cache._fits_already(self.cache.requests[rid], self.processed[rid] + len(tokens)):
+                    continue
+                for g, n in self.cache.pages_to_take(rid, self.processed[rid] + len(tokens)).items():
+                    demand[g] = demand.get(g, 0) + n
+            for g, n in demand.items():
+                if n > self.cache.groups[g].pool.n_free:
+                    raise OutOfPages(f"the step needs {n} more pages of group {g}; "
+                                     f"{self.cache.groups[g].pool.n_free} are free")
+            for rid, tokens, _want in entries:
+                self.cache.reserve(rid, self.processed[rid] + len(tokens))
+        requests = self.cache.requests
+        spans = [(rid, self.processed[rid], tokens, want, requests[rid].slot) for rid, tokens, want in entries]
         rids = [e[0] for e in entries]
-        tables = {}
-        for g in self.cache.paged_groups():
-            width = max(max(len(self.cache.requests[r].tables[g]) for r in rids), 1)
-            tables[g] = self.cache.table_rows(rids, g, width)
+        ps = self.cache.page_size
+        longest = max(self.processed[rid] + len(tokens) for rid, tokens, _ in entries)
+        width = max(-(-longest // ps), 1)
+        tables = {g: self.cache.table_rows(rids, g, width) for g in self.cache.paged_groups()}
         return spans, tables
 
     def prepare(self, entries) -> StepBatch:
@@ -123,10 +131,11 @@ class ModelRunner:
         self.tokens_run += prepared[1]
         return self.graphs.run_prepared(prepared)
 
-    def step(self, entries) -> torch.Tensor:
+    def step(self, entries, trusted: bool = False) -> torch.Tensor:
         """entries: (request, its next tokens, wanted places among them).  Returns 32-bit logits
-        [wanted, vocab] in the order of the entries and of their wanted places."""
-        spans, tables = self._reserve(entries)
+        [wanted, vocab] in the order of the entries and of their wanted places.  (A step that ran
+        as a CUDA graph returns a view of that graph's output buffer, valid until the next such step.)"""
+        spans, tables = self._reserve(entries, trusted)
         n_tokens = sum(len(e[1]) for e in entries)
         graphed = (self.use_graphs and n_tokens == len(entries) and self.graphs.bucket(len(entries)) is not None
                    and all(len(e[2]) <= 1 for e in entries))
@@ -138,8 +147,10 @@ class ModelRunner:
             else:
                 logits = full[torch.tensor(keep, dtype=torch.long, device=self.device)] if keep else full[:0]
         else:
-            batch = pack_step(self.ops, self.dtype, self.device, spans, tables, pin=True)
-            logits = self.model.forward(batch, self.cache)
+            logits = self.shape_graphs.run(spans, tables) if self.use_graphs else None
+            if logits is None:
+                batch = pack_step(self.ops, self.dtype, self.device, spans, tables, pin=True)
+                logits = self.model.forward(batch, self.cache)
         for rid, tokens, _ in entries:
             self.processed[rid] += len(tokens)
         self.steps += 1

@@ -38,7 +38,7 @@ class RequestRefused(ValueError):
     pass
 
 
-@dataclass
+@dataclass(eq=False)
 class Request:
     request_id: object
     prompt: List[int]
@@ -55,12 +55,25 @@ class Request:
         return self.prompt + self.output
 
     @property
+    def last_token(self) -> int:
+        return self.output[-1] if self.output else self.prompt[-1]
+
+    def token_range(self, a: int, b: int) -> List[int]:
+        """Tokens a..b-1 of prompt followed by output."""
+        n = len(self.prompt)
+        if b <= n:
+            return self.prompt[a:b]
+        if a >= n:
+            return self.output[a - n:b - n]
+        return self.prompt[a:] + self.output[:b - n]
+
+    @property
     def remaining(self) -> int:
         """Tokens known but not yet run through the model."""
         return len(self.prompt) + len(self.output) - self.computed
 
 
-@dataclass
+@dataclass(eq=False)
 class PlanEntry:
     request: Request
     tokens: List[int]
@@ -154,24 +167,26 @@ class Scheduler:
         plan = StepPlan()
         budget = self.max_batched_tokens
         # 1. one token for every decoding request, oldest first
+        planned = set()
         for req in list(self.running):
-            if req not in self.running or req.remaining != 1 or req.computed < len(req.prompt):
+            if req.status != RUNNING or req.remaining != 1 or req.computed < len(req.prompt):
                 continue
             if budget < 1:
                 break
             if self._reserve_or_preempt(req, 1, plan):
-                plan.entries.append(PlanEntry(req, [req.tokens[-1]], True))
+                plan.entries.append(PlanEntry(req, [req.last_token], True))
+                planned.add(id(req))
                 budget -= 1
         # 2. prompt portions of running requests (also recomputation after a preemption)
         for req in list(self.running):
-            if req not in self.running or any(e.request is req for e in plan.entries):
+            if req.status != RUNNING or id(req) in planned:
                 continue
             if budget < 1:
                 break
             n = min(req.remaining, budget)
             if self._reserve_or_preempt(req, n, plan):
-                toks = req.tokens[req.computed:req.computed + n]
-                plan.entries.append(PlanEntry(req, toks, n == req.remaining))
+                plan.entries.append(PlanEntry(req, req.token_range(req.computed, req.computed + n), n == req.remaining))
+                planned.add(id(req))
                 budget -= n
         # 3. admissions, first come first served; never right after a preemption in the same plan
         while self.waiting and budget >= 1 and len(self.running) < self.max_num_seqs and not plan.preempted:
@@ -193,7 +208,7 @@ class Scheduler:
             self.waiting.popleft()
             req.status, req.computed = RUNNING, 0
             self.running.append(req)
-            plan.entries.append(PlanEntry(req, req.tokens[:n], n == req.remaining))
+            plan.entries.append(PlanEntry(req, req.token_range(0, n), n == req.remaining))
             budget -= n
         return plan
 

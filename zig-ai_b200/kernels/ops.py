@@ -44,6 +44,7 @@ _SIGNATURES = {
         "zai_prefill_attention_mma": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
         "zai_decode_attention_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
         "zai_decode_chunk_keys": [],
+        "zai_prefill_block_rows": [],
     },
     "decode_gemm": {
         "zai_skinny_gemm_supports": [_I, _I, _I, _I],
@@ -109,8 +110,23 @@ def _ptr(t):
     return None if t is None else t.data_ptr()
 
 
+_stream_handle = None
+
+
+def begin_forward() -> None:
+    """Called once at the start of a forward pass: the current stream is looked up here and reused by
+    every launch of the pass (the lookup costs about as much as a launch)."""
+    global _stream_handle
+    _stream_handle = torch.cuda.current_stream().cuda_stream
+
+
+def end_forward() -> None:
+    global _stream_handle
+    _stream_handle = None
+
+
 def _stream():
-    return torch.cuda.current_stream().cuda_stream
+    return _stream_handle if _stream_handle is not None else torch.cuda.current_stream().cuda_stream
 
 
 def _cuda(*tensors):
@@ -313,7 +329,8 @@ def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=Non
                 _ptr(step.positions), N, n_chunks, cache.page_size, heads, kv_heads, head_dim, float(scale),
                 int(window or 0), _stream()), "decode attention", 2)
         else:
-            n_tiles = sum(-(-n // 64) for n in step.q_lens)
+            block_rows = _fn("attention_mma", "zai_prefill_block_rows")()
+            n_tiles = sum(-(-n // block_rows) for n in step.q_lens)
             _check(_fn("attention_mma", "zai_prefill_attention_mma")(
                 _ptr(out), _ptr(q), _ptr(cache.pages), _ptr(bt), bt.shape[1], _ptr(step.cu_q), _ptr(step.ctx_lens),
                 step.n_seqs, n_tiles, cache.page_size, heads, kv_heads, head_dim, float(scale), int(window or 0),

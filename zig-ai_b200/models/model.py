@@ -89,6 +89,16 @@ class Model:
     def forward(self, step, cache) -> torch.Tensor:
         """Run the step's tokens through the layers; return 32-bit logits [wanted, vocab]."""
         ops = step.ops
+        begin = getattr(ops, "begin_forward", None)
+        if begin:
+            begin()
+        try:
+            return self._forward(step, cache, ops)
+        finally:
+            if begin:
+                ops.end_forward()
+
+    def _forward(self, step, cache, ops) -> torch.Tensor:
         step.scratch.clear()                # per-step tables are computed anew (also inside a graph capture)
         h = Residual(ops.embed(step.token_ids, self.table))
         pending = None
