@@ -94,6 +94,7 @@ def require() -> None:
     """Fail loudly unless a CUDA device is present and the core libraries load."""
     if not torch.cuda.is_available():
         raise KernelError("no CUDA device: this engine has no CPU path")
+    build.build_all(verbose=True)            # whatever is missing or out of date, several at a time
     for lib in ("embed", "norm", "activation", "shortconv", "rope_kv", "attention", "attention_mma", "decode_gemm", "sampling"):
         build.load(lib)
 
