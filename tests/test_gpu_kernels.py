@@ -338,3 +338,55 @@ def test_skinny_gemm_with_norm_residual_and_gathered_rows(M, O, K, eps):
     got = o.linear(lazy, w, out_dtype=torch.float32)
     assert got.dtype == torch.float32 and torch.allclose(got, want[rows.long()], atol=3e-2, rtol=3e-2)
     assert torch.equal(lazy.residual.data, h)
+
+
+# ----------------------------------------------------------------------------- many-rows products (tcgen05)
+def _tc_call(o, y, w, x, epilogue):
+    import ctypes
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    fn = o._fn("gemm_tc", "zai_gemm_tc")
+    code = fn(y.data_ptr(), w.data_ptr(), x.data_ptr(), status.data_ptr(), x.shape[0], w.shape[0], w.shape[1], epilogue,
+              torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert code == 0 and int(status.item()) == 0, (code, int(status.item()))
+
+
+@pytest.mark.parametrize("N,O,K", [(128, 128, 64), (256, 256, 1024), (300, 517, 1000), (2048, 1024, 1024),
+                                   (1000, 3072, 1024), (129, 96, 96), (4096, 256, 136), (640, 1536, 4608)])
+def test_tensor_core_gemm_bf16_and_f32(N, O, K):
+    """Tiles that end inside the matrix in every direction, K that is no multiple of 64, more tiles
+    than blocks (a block takes several), few tiles."""
+    o = ops()
+    g = torch.Generator().manual_seed(30)
+    x = torch.randn(N, K, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(O, K, generator=g) * K ** -0.5).to(torch.bfloat16).cuda()
+    want = x.float() @ w.float().t()
+    y = torch.full((N, O), float("nan"), dtype=torch.bfloat16, device="cuda")
+    _tc_call(o, y, w, x, 0)
+    assert torch.allclose(y.float(), want, atol=2e-2, rtol=2e-2)
+    y32 = torch.full((N, O), float("nan"), dtype=torch.float32, device="cuda")
+    _tc_call(o, y32, w, x, 1)
+    assert torch.allclose(y32, want, atol=2e-3, rtol=2e-3)
+
+
+@pytest.mark.parametrize("N,F,K", [(128, 128, 64), (2048, 4608, 1024), (130, 100, 96), (700, 1000, 520)])
+def test_tensor_core_gemm_swiglu(N, F, K):
+    o = ops()
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn(N, K, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(2 * F, K, generator=g) * K ** -0.5).to(torch.bfloat16).cuda()
+    gu = x.float() @ w.float().t()
+    want = torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]
+    y = torch.full((N, F), float("nan"), dtype=torch.bfloat16, device="cuda")
+    _tc_call(o, y, w, x, 2)
+    assert torch.allclose(y.float(), want, atol=3e-2, rtol=3e-2)
+    # and through the op the parts call, with the switch that sends products to this kernel
+    old, o.USE_TC_GEMM = o.USE_TC_GEMM, True
+    try:
+        before = o.launches
+        got = o.linear_swiglu(x, w, F)
+        assert o.launches == before + 1 and torch.allclose(got.float(), want, atol=3e-2, rtol=3e-2)
+        assert torch.allclose(o.linear(x, w).float(), gu, atol=3e-2, rtol=3e-2)
+    finally:
+        o.USE_TC_GEMM = old
+    assert o.tc_status() == 0

@@ -11,7 +11,7 @@
 // The reference runs these products as cublasSgemm followed by a separate activation kernel
 // (src/matmul/cublas.zig:515-548, src/transformer/hybrid_layer.zig:661-669, src/cuda/layer_kernels.cu:62-70).
 //
-// Structure of a block (192 threads), one output tile each:
+// Structure of a block (192 threads):
 //   warp 0, one lane   TMA producer: cp.async.bulk.tensor loads of 64-k slices of the weight and
 //                      token tiles into a ring of shared-memory stages (128-byte swizzle), each
 //                      stage signalled by an mbarrier with the expected byte count
@@ -20,6 +20,8 @@
 //                      tcgen05.commit frees the stage, and after the last slice signals the epilogue
 //   warps 2-5          read the accumulators with tcgen05.ld (each warp its quarter of the lanes),
 //                      apply the epilogue and store
+// Blocks are persistent (one per SM, tiles taken round robin) and TMEM holds the accumulators of two
+// tiles, so a tile's epilogue overlaps the next tile's products.
 // TMA loads are never multicast.  Every wait on an mbarrier is bounded: when it runs out the block
 // raises an error word in global memory, every role leaves its loop, TMEM is freed and the block
 // returns; the host reports the error.
@@ -87,24 +89,28 @@ struct TcArgs {
     int N, O, K, ldy;
     int F;                // SwiGLU: gate rows 0..F-1, up rows F..2F-1
     int stages;
+    int tiles_o, tiles;   // tiles along the weight rows; all tiles (tile t: o tile t % tiles_o, token tile t / tiles_o)
 };
 
-template <int BN, int EPI>
+// Blocks are persistent: block b takes tiles b, b + gridDim.x, ...  The accumulator memory holds two
+// tiles, so the epilogue of one tile runs while the products of the next are issued.
+template <int BN, int EPI, int ACC_BUFS>
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                              const __grid_constant__ CUtensorMap map_x, const TcArgs a) {
-    constexpr int NA = EPI == TC_EPI_SWIGLU ? 2 : 1;           // accumulators (weight tiles per stage)
+    constexpr int NA = EPI == TC_EPI_SWIGLU ? 2 : 1;           // accumulators per tile (weight tiles per stage)
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
     constexpr uint32_t STAGE_BYTES = NA * A_BYTES + B_BYTES;
-    constexpr uint32_t TMEM_COLS = NA * BN;                    // 128, 256 or 512: a power of two
+    constexpr uint32_t TILE_COLS = NA * BN;                    // TMEM columns of one tile's accumulators
+    constexpr uint32_t TMEM_COLS = ACC_BUFS * TILE_COLS;       // one or two tiles: 128..512, a power of two
+    static_assert(TMEM_COLS <= 512, "the accumulators must fit the 512 TMEM columns");
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    __shared__ uint64_t full_bar[8], empty_bar[8], tmem_full_bar;
+    __shared__ uint64_t full_bar[8], empty_bar[8], acc_full_bar[2], acc_empty_bar[2];
     __shared__ uint32_t tmem_base_holder;
     __shared__ int failed_flag;
     volatile int* failed = &failed_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int stages = a.stages;
-    const int o0 = blockIdx.x * TC_BM, n0 = blockIdx.y * BN;
     const int num_kb = (a.K + TC_BK - 1) / TC_BK;
 
     if (threadIdx.x == 0) {
@@ -113,7 +119,10 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
         }
-        mbar_init(&tmem_full_bar, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&acc_full_bar[i], 1);
+            mbar_init(&acc_empty_bar[i], 4);                   // one arrival per epilogue warp
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {                                           // one warp allocates the accumulator columns
@@ -130,28 +139,32 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
 
     if (warp == 0) {
         if (lane == 0) {
-            int issued = 0;
-            for (int kb = 0; kb < num_kb; ++kb) {
-                const int s = kb % stages;
-                const uint32_t ph = (kb / stages) & 1;
-                if (!mbar_wait(&empty_bar[s], ph ^ 1, failed)) break;
-                unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
-                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-                tma_load_2d(st, &map_w, kb * TC_BK, o0, &full_bar[s]);
-                if (NA == 2) tma_load_2d(st + A_BYTES, &map_w, kb * TC_BK, a.F + o0, &full_bar[s]);
-                tma_load_2d(st + NA * A_BYTES, &map_x, kb * TC_BK, n0, &full_bar[s]);
-                issued = kb + 1;
+            int issued = 0, it = 0;                            // `it` counts k-blocks over all of this block's tiles
+            bool ok = true;
+            for (int t = blockIdx.x; t < a.tiles && ok; t += gridDim.x) {
+                const int o0 = (t % a.tiles_o) * TC_BM, n0 = (t / a.tiles_o) * BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % stages;
+                    const uint32_t ph = (it / stages) & 1;
+                    if (!mbar_wait(&empty_bar[s], ph ^ 1, failed)) { ok = false; break; }
+                    unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
+                    mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+                    tma_load_2d(st, &map_w, kb * TC_BK, o0, &full_bar[s]);
+                    if (NA == 2) tma_load_2d(st + A_BYTES, &map_w, kb * TC_BK, a.F + o0, &full_bar[s]);
+                    tma_load_2d(st + NA * A_BYTES, &map_x, kb * TC_BK, n0, &full_bar[s]);
+                    issued = it + 1;
+                }
             }
             if (*failed) {
                 // copies already issued still land in this block's shared memory: wait for them (bounded)
-                for (int kb = max(issued - stages, 0); kb < issued; ++kb) {
-                    const uint32_t a_ = smem_addr(&full_bar[kb % stages]);
-                    const uint32_t ph = (kb / stages) & 1;
-                    for (int it = 0; it < TC_SPIN_LIMIT; ++it) {
-                        uint32_t ok;
+                for (int i = max(issued - stages, 0); i < issued; ++i) {
+                    const uint32_t a_ = smem_addr(&full_bar[i % stages]);
+                    const uint32_t ph = (i / stages) & 1;
+                    for (int spin = 0; spin < TC_SPIN_LIMIT; ++spin) {
+                        uint32_t done;
                         asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                                     : "=r"(ok) : "r"(a_), "r"(ph) : "memory");
-                        if (ok) break;
+                                     : "=r"(done) : "r"(a_), "r"(ph) : "memory");
+                        if (done) break;
                     }
                 }
             }
@@ -161,41 +174,55 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
             // instruction descriptor: D fp32, A and B bfloat16, both K-major, N = BN, M = 128
             constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
             bool ok = true;
-            for (int kb = 0; kb < num_kb && ok; ++kb) {
-                const int s = kb % stages;
-                const uint32_t ph = (kb / stages) & 1;
-                ok = mbar_wait(&full_bar[s], ph, failed);
+            int it = 0, local = 0;
+            for (int t = blockIdx.x; t < a.tiles && ok; t += gridDim.x, ++local) {
+                const int buf = local % ACC_BUFS;
+                const uint32_t acc = tmem_base + buf * TILE_COLS;
+                // the epilogue must have drained this buffer (ACC_BUFS tiles ago)
+                ok = mbar_wait(&acc_empty_bar[buf], ((local / ACC_BUFS) & 1) ^ 1, failed);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t sa = smem_addr(tiles + (size_t)s * STAGE_BYTES);
-                const uint32_t sb = sa + NA * A_BYTES;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % stages;
+                    const uint32_t ph = (it / stages) & 1;
+                    ok = mbar_wait(&full_bar[s], ph, failed);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t sa = smem_addr(tiles + (size_t)s * STAGE_BYTES);
+                    const uint32_t sb = sa + NA * A_BYTES;
 #pragma unroll
-                for (int k = 0; k < TC_BK / 16; ++k) {
-                    const uint64_t db = umma_desc(sb + k * 32);
-                    umma_bf16(tmem_base, umma_desc(sa + k * 32), db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-                    if (NA == 2) umma_bf16(tmem_base + BN, umma_desc(sa + A_BYTES + k * 32), db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < TC_BK / 16; ++k) {
+                        const uint64_t db = umma_desc(sb + k * 32);
+                        umma_bf16(acc, umma_desc(sa + k * 32), db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        if (NA == 2) umma_bf16(acc + BN, umma_desc(sa + A_BYTES + k * 32), db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&empty_bar[s]);                // the stage is free once these products are done
                 }
-                umma_commit(&empty_bar[s]);                    // the stage is free once these products are done
+                umma_commit(&acc_full_bar[buf]);               // (also after a failure, so that the epilogue wakes)
             }
-            umma_commit(&tmem_full_bar);                       // (also on failure, so that the epilogue wakes)
         }
     } else {
         const int q = warp & 3;                                // this warp's quarter of the TMEM lanes
         const int row = q * 32 + lane;
-        const int o = o0 + row;
-        const bool done = mbar_wait(&tmem_full_bar, 0, failed) && !*failed;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (done) {
-            const int o_limit = EPI == TC_EPI_SWIGLU ? a.F : a.O;
+        const int o_limit = EPI == TC_EPI_SWIGLU ? a.F : a.O;
+        int local = 0;
+        for (int t = blockIdx.x; t < a.tiles; t += gridDim.x, ++local) {
+            const int buf = local % ACC_BUFS;
+            const int o = (t % a.tiles_o) * TC_BM + row, n0 = (t / a.tiles_o) * BN;
+            if (!mbar_wait(&acc_full_bar[buf], (local / ACC_BUFS) & 1, failed) || *failed) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t acc = tmem_base + buf * TILE_COLS + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
-                if (n0 + c0 >= a.N) break;                     // uniform over the warp
                 uint32_t r[32], u[32];
-                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + c0;
-                tmem_ld32(taddr, r);
-                if (EPI == TC_EPI_SWIGLU) tmem_ld32(taddr + BN, u);
+                tmem_ld32(acc + c0, r);
+                if (EPI == TC_EPI_SWIGLU) tmem_ld32(acc + BN + c0, u);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (o < o_limit) {
+                if (c0 + 32 >= BN) {                           // everything of this buffer is in registers now
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(&acc_empty_bar[buf])) : "memory");
+                }
+                if (o < o_limit && n0 + c0 < a.N) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const int n = n0 + c0 + j;
@@ -203,7 +230,8 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                         const float v = __uint_as_float(r[j]);
                         if (EPI == TC_EPI_SWIGLU) {
                             const float up = __uint_as_float(u[j]);
-                            reinterpret_cast<bf16*>(a.y)[(size_t)n * a.ldy + o] = __float2bfloat16_rn(v / (1.f + expf(-v)) * up);
+                            reinterpret_cast<bf16*>(a.y)[(size_t)n * a.ldy + o] =
+                                __float2bfloat16_rn(__fdividef(v, 1.f + __expf(-v)) * up);
                         } else if (EPI == TC_EPI_F32) {
                             reinterpret_cast<float*>(a.y)[(size_t)n * a.ldy + o] = v;
                         } else {
@@ -253,7 +281,18 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box
     return r == CUDA_SUCCESS ? 0 : -6;
 }
 
-template <int BN, int EPI>
+static int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n < 1) n = 1;
+    }
+    return n;
+}
+
+template <int BN, int EPI, int ACC_BUFS>
 static int tc_launch(const CUtensorMap& mw, const CUtensorMap& mx, TcArgs a, int o_tiles, cudaStream_t stream) {
     constexpr int NA = EPI == TC_EPI_SWIGLU ? 2 : 1;
     const size_t stage = (size_t)NA * TC_BM * TC_BK * 2 + (size_t)BN * TC_BK * 2;
@@ -264,12 +303,14 @@ static int tc_launch(const CUtensorMap& mw, const CUtensorMap& mx, TcArgs a, int
     const size_t smem = stage * stages + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, ACC_BUFS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    const dim3 grid(o_tiles, (a.N + BN - 1) / BN);
-    return launch_pdl(gemm_tc_kernel<BN, EPI>, grid, dim3(TC_THREADS), smem, stream, mw, mx, a);
+    a.tiles_o = o_tiles;
+    a.tiles = o_tiles * ((a.N + BN - 1) / BN);
+    const int grid = a.tiles < sm_count() ? a.tiles : sm_count();
+    return launch_pdl(gemm_tc_kernel<BN, EPI, ACC_BUFS>, dim3(grid), dim3(TC_THREADS), smem, stream, mw, mx, a);
 }
 
 ZAI_API int zai_gemm_tc_supports(int N, int O, int K, int epilogue) {
@@ -285,7 +326,13 @@ ZAI_API int zai_gemm_tc(void* y, const void* W, const void* x, int* status, int 
                         cudaStream_t stream) {
     if (!zai_gemm_tc_supports(N, O, K, epilogue)) return ZAI_BAD_SIZE;
     if ((reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(x) & 15)) return ZAI_BAD_SIZE;
-    const int bn = N > 128 ? 256 : 128;
+    // two tiles' accumulators share the 512 TMEM columns: 256 tokens per tile, 128 when a tile has two
+    // accumulators; 128 also when 256 would leave SMs without a tile
+    // (for SwiGLU a tile of 256 tokens would fill all 512 columns and its epilogue could not overlap
+    // the next tile's products; measured no faster, so 128)
+    const int o_rows = epilogue == TC_EPI_SWIGLU ? O / 2 : O;
+    int bn = (N > 128 && epilogue != TC_EPI_SWIGLU) ? 256 : 128;
+    if (bn == 256 && ((o_rows + TC_BM - 1) / TC_BM) * ((N + 255) / 256) < sm_count()) bn = 128;
     CUtensorMap mw, mx;
     int e = make_map(&mw, W, O, K, TC_BM);
     if (e) return e;
@@ -295,12 +342,12 @@ ZAI_API int zai_gemm_tc(void* y, const void* W, const void* x, int* status, int 
     a.y = y; a.status = status; a.N = N; a.O = O; a.K = K;
     a.F = O / 2;
     a.ldy = epilogue == TC_EPI_SWIGLU ? O / 2 : O;
-    a.stages = 0;
+    a.stages = 0; a.tiles_o = 0; a.tiles = 0;
     const int o_tiles = ((epilogue == TC_EPI_SWIGLU ? a.F : O) + TC_BM - 1) / TC_BM;
-#define TC_CASE(BNV, EPIV) if (bn == BNV && epilogue == EPIV) return tc_launch<BNV, EPIV>(mw, mx, a, o_tiles, stream);
-    TC_CASE(128, TC_EPI_BF16) TC_CASE(256, TC_EPI_BF16)
-    TC_CASE(128, TC_EPI_F32) TC_CASE(256, TC_EPI_F32)
-    TC_CASE(128, TC_EPI_SWIGLU) TC_CASE(256, TC_EPI_SWIGLU)
+#define TC_CASE(BNV, EPIV, BUFS) if (bn == BNV && epilogue == EPIV) return tc_launch<BNV, EPIV, BUFS>(mw, mx, a, o_tiles, stream);
+    TC_CASE(128, TC_EPI_BF16, 2) TC_CASE(256, TC_EPI_BF16, 2)
+    TC_CASE(128, TC_EPI_F32, 2) TC_CASE(256, TC_EPI_F32, 2)
+    TC_CASE(128, TC_EPI_SWIGLU, 2) TC_CASE(256, TC_EPI_SWIGLU, 1)
 #undef TC_CASE
     return ZAI_BAD_SIZE;
 }

@@ -9,6 +9,7 @@ cuBLAS through `torch.matmul`, as the reference sends every projection to `cubla
 from __future__ import annotations
 
 import ctypes
+import os
 import sys
 from ctypes import c_float, c_int, c_void_p
 
@@ -49,6 +50,10 @@ _SIGNATURES = {
     "decode_gemm": {
         "zai_skinny_gemm_supports": [_I, _I, _I, _I],
         "zai_skinny_gemm": [_P, _P, _P, _P, _P, _P, _P, _P, _F, _I, _I, _I, _I, _P],
+    },
+    "gemm_tc": {
+        "zai_gemm_tc_supports": [_I, _I, _I, _I],
+        "zai_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
     },
     "sampling": {
         "zai_argmax": [_P, _P, _I, _I, _P],
@@ -95,7 +100,7 @@ def require() -> None:
     if not torch.cuda.is_available():
         raise KernelError("no CUDA device: this engine has no CPU path")
     build.build_all(verbose=True)            # whatever is missing or out of date, several at a time
-    for lib in ("embed", "norm", "activation", "shortconv", "rope_kv", "attention", "attention_mma", "decode_gemm", "sampling"):
+    for lib in ("embed", "norm", "activation", "shortconv", "rope_kv", "attention", "attention_mma", "decode_gemm", "gemm_tc", "sampling"):
         build.load(lib)
 
 
@@ -199,9 +204,44 @@ def _skinny(x, w, epilogue, out_cols, out_dtype):
     return y
 
 
+_tc_status = None
+TC_MIN_ROWS = 128        # from this many rows on a product may go to the tcgen05 kernel
+# Measured on B200 (graph-timed, weights from HBM) the library's two-block 256x256 tiles are 1.15x to
+# 2x faster than this one-block 128x{128,256} kernel at the shapes of the LFM2 models, so products go
+# to the library unless ZAI_TC_GEMM=1 asks for the tcgen05 kernel (its tests call it directly).
+USE_TC_GEMM = os.environ.get("ZAI_TC_GEMM", "0") == "1"
+
+
+def tc_status() -> int:
+    """0, or 1 if a block of the tcgen05 kernel gave up a wait since the last call (reads the device)."""
+    if _tc_status is None:
+        return 0
+    v = int(_tc_status.item())
+    if v:
+        _tc_status.zero_()
+    return v
+
+
+def _tensor_core(x, w, epilogue, out_cols, out_dtype):
+    """The tcgen05 product kernel, if it takes these operands and is the faster choice; else None."""
+    global _tc_status
+    N, (O, K) = x.shape[0], w.shape
+    if not USE_TC_GEMM or N < TC_MIN_ROWS or w.dtype != torch.bfloat16 or x.dtype != torch.bfloat16:
+        return None
+    if not x.is_contiguous() or not _fn("gemm_tc", "zai_gemm_tc_supports")(N, O, K, epilogue):
+        return None
+    if _tc_status is None:
+        _tc_status = torch.zeros(1, dtype=torch.int32, device=w.device)
+    y = torch.empty((N, out_cols), dtype=out_dtype, device=w.device)
+    _check(_fn("gemm_tc", "zai_gemm_tc")(_ptr(y), _ptr(w), _ptr(x), _ptr(_tc_status), N, O, K, epilogue, _stream()),
+           "gemm_tc")
+    return y
+
+
 def linear(x, w, out_dtype=None):
     """x [N, K] times w [O, K] transposed.  x may be a LazyNorm.  Few rows in bfloat16 go to the
-    fused kernel; a matrix kept in 32-bit is multiplied in 32-bit; the rest is the library's."""
+    fused few-rows kernel, many rows to the tcgen05 kernel where it is the faster one; a matrix kept
+    in 32-bit is multiplied in 32-bit; the rest is the library's."""
     in_dtype = x.dtype
     out_dtype = out_dtype or in_dtype
     if in_dtype == torch.bfloat16 and out_dtype in (torch.bfloat16, torch.float32):
@@ -210,6 +250,10 @@ def linear(x, w, out_dtype=None):
             return y
     if isinstance(x, LazyNorm):
         x = x.materialize(sys.modules[__name__])
+    if x.dtype == torch.bfloat16 and out_dtype in (torch.bfloat16, torch.float32):
+        y = _tensor_core(x, w, _EPI_F32 if out_dtype == torch.float32 else _EPI_BF16, w.shape[0], out_dtype)
+        if y is not None:
+            return y
     if x.dtype == torch.float32 or w.dtype == torch.float32 or out_dtype == torch.float32:
         if torch.backends.cuda.matmul.allow_tf32:
             torch.backends.cuda.matmul.allow_tf32 = False
@@ -224,6 +268,11 @@ def linear_swiglu(x, w_gate_up, ff_dim):
     """silu(x . Wgate^T) * (x . Wup^T) with the two matrices stacked as [2F, K]."""
     if x.dtype == torch.bfloat16:
         y = _skinny(x, w_gate_up, _EPI_SWIGLU, ff_dim, torch.bfloat16)
+        if y is not None:
+            return y
+        if isinstance(x, LazyNorm):
+            x = x.materialize(sys.modules[__name__])
+        y = _tensor_core(x, w_gate_up, _EPI_SWIGLU, ff_dim, torch.bfloat16)
         if y is not None:
             return y
     return silu_mul(linear(x, w_gate_up), ff_dim)
