@@ -30,8 +30,19 @@ LFM2_350M = {
     "rope_theta": 1000000.0, "conv_L_cache": 3, "conv_bias": False, "use_qk_norm": True, "norm_eps": 1e-5,
     "tie_embedding": True, "max_position_embeddings": 128000,
 }
+SHAPES = {
+    "350m": dict(hidden_size=1024, num_attention_heads=16, block_ff_dim=6656),
+    "700m": dict(hidden_size=1536, num_attention_heads=24, block_ff_dim=10752),
+    "1.2b": dict(hidden_size=2048, num_attention_heads=32, block_ff_dim=12288),
+}
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
+
+
+def shape_config(name):
+    d = dict(LFM2_350M)
+    d.update(SHAPES[name])
+    return d
 
 
 def peaks():
@@ -59,18 +70,25 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
+            self.rows.append((time.perf_counter(), [x.strip() for x in line.split(",")]))
+
+    def mark(self):
+        """The timed region starts here: earlier samples do not count."""
+        self.t0 = time.perf_counter()
 
     def stop(self):
         if self.proc:
+            time.sleep(0.05)
             self.proc.terminate()
+        t0 = getattr(self, "t0", 0.0)
+        self.rows = [r for t, r in self.rows if t >= t0] or [r for t, r in self.rows[-3:]]
         sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
         mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
@@ -116,6 +134,8 @@ def time_decode(eng, B, steps, warmup, clocks=None):
     context tokens read per step, launches per step, h2d bytes, d2h bytes)."""
     import torch
     from zig_ai_b200.kernels import ops
+    if clocks:
+        clocks.start()                       # nvidia-smi takes a while to give its first sample
     ids = decode_requests(eng, B, 2 * (steps + warmup) + 4, seed=B)
     reqs = [eng.requests[i] for i in ids]
     runner = eng.runner
@@ -132,7 +152,7 @@ def time_decode(eng, B, steps, warmup, clocks=None):
     torch.cuda.synchronize()
     launches0 = ops.launches
     if clocks:
-        clocks.start()
+        clocks.mark()
     start.record()
     for k in range(steps):
         ops.argmax(runner.run_prepared(prepared[warmup + k]))
@@ -195,12 +215,16 @@ def run_ours(args):
     from zig_ai_b200.kernels import build
     build.build_all(verbose=False)
     hbm_peak, flops_peak, peak_src = peaks()
-    cfg = config_from_dict(LFM2_350M)
+    cfg = config_from_dict(shape_config(args.model))
     nums = model_numbers(cfg)
+    if args.workload == "mixed":
+        return run_mixed(args, cfg)
     with tempfile.TemporaryDirectory(prefix="lfm2_350m_") as d:
         z.write_random_model(cfg, 0, d)
         eng = z.Engine(d, "bfloat16", max_num_seqs=64, max_batched_tokens=2048 + 64, max_model_len=CONTEXT,
                        max_tokens=64 * CONTEXT)
+        if args.only == "gemm":
+            return run_gemm_table(cfg)
         if args.only == "prefill":
             print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "ms": round(time_prefill(eng, reps=args.steps), 3)}))
             return 0
@@ -223,17 +247,17 @@ def run_ours(args):
     T = PREFILL_TOKENS
     prefill_flops = 2 * T * nums["layer_params"] + 2 * 1 * nums["head_params"] + nums["n_attn"] * 2 * T * T * Hq * D
     out = {
-        "metric": "decode tok/s @ batch 8 (LFM2-350M shape, context 2048-4096)",
+        "metric": f"decode tok/s @ batch 8 (LFM2-{args.model.upper()} shape, context 2048-4096)",
         "value": round(8 / dev_ms * 1e3, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(dev_ms, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded random weights and token ids)",
         "impl": "ours",
-        "config": {"model": "LFM2-350M shape", "layers": cfg.num_hidden_layers, "layers_of_config": 16,
+        "config": {"model": f"LFM2-{args.model.upper()} shape", "layers": cfg.num_hidden_layers, "layers_of_config": 16,
                    "attn_layers": nums["n_attn"], "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads,
                    "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim, "ff_dim": cfg.ff_dim,
                    "vocab": cfg.vocab_size, "conv_taps": cfg.conv_L_cache, "global_batch": 8, "seq_len": CONTEXT,
                    "mean_context": round(ctx_tokens / 8), "page_size": 16, "parallelism": "single GPU",
-                   "l2": "step reads 0.7 GB of weights (> 126 MB L2)", "peaks": peak_src},
+                   "l2": f"step reads {weight_bytes / 1e9:.2f} GB of weights (> 126 MB L2)", "peaks": peak_src},
         "e2e": {"value": round(8 / e2e_ms * 1e3, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": int(round(launches * args.steps)),
@@ -248,15 +272,116 @@ def run_ours(args):
     return 0
 
 
+def run_gemm_table(cfg):
+    """The products of the model's layers at 2048, 512 and 128 rows: the tcgen05 kernel of this package
+    against the library's product (plus the activation kernel where the tcgen05 kernel fuses it), each
+    timed as a CUDA graph of 20 calls that rotate over copies of the weights (so they come from HBM)."""
+    import ctypes
+    import torch
+    from zig_ai_b200.kernels import ops
+    ops.require()
+    fn = ops._fn("gemm_tc", "zai_gemm_tc")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    H, F = cfg.hidden_size, cfg.ff_dim
+    qkv = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim
+    shapes = [("out_proj", H, H, 0), ("qkv", qkv, H, 0), ("in_proj", 3 * H, H, 0), ("gate_up+swiglu", 2 * F, H, 2), ("down", H, F, 0)]
+
+    def graph_time(f, reps=20):
+        for _ in range(2):
+            f()
+        torch.cuda.synchronize()
+        g, s = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+        with torch.cuda.stream(s):
+            with torch.cuda.graph(g):
+                ops.begin_forward()
+                for _ in range(reps):
+                    f()
+                ops.end_forward()
+        torch.cuda.synchronize()
+        g.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(5):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / (5 * reps) * 1e3
+
+    rows = []
+    for N in (2048, 512, 128):
+        for name, O, K, epi in shapes:
+            ws = [torch.randn(O, K).to(torch.bfloat16).cuda() for _ in range(max(2, min(8, int(200e6 // (O * K * 2)))))]
+            x = torch.randn(N, K).to(torch.bfloat16).cuda()
+            y = torch.empty((N, O // 2 if epi == 2 else O), dtype=torch.bfloat16, device="cuda")
+            it = [0]
+
+            def tc():
+                w = ws[it[0] % len(ws)]
+                it[0] += 1
+                fn(y.data_ptr(), w.data_ptr(), x.data_ptr(), status.data_ptr(), N, O, K, epi, ops._stream())
+
+            def lib():
+                w = ws[it[0] % len(ws)]
+                it[0] += 1
+                if epi == 2:
+                    ops.silu_mul(torch.matmul(x, w.t()), O // 2)
+                else:
+                    torch.matmul(x, w.t())
+            t, t2 = graph_time(tc), graph_time(lib)
+            rows.append({"rows": N, "product": name, "O": O, "K": K, "tcgen05_us": round(t, 1),
+                         "tcgen05_tflops": round(2 * N * O * K / t / 1e6), "library_us": round(t2, 1),
+                         "library_tflops": round(2 * N * O * K / t2 / 1e6)})
+            print(json.dumps(rows[-1]))
+    print(json.dumps({"only": "gemm", "status": int(status.item())}))
+    return 0
+
+
+def run_mixed(args, cfg):
+    """64 requests with prompts of 256..2048 random tokens and 256 new tokens each, chunked prefill
+    interleaved with decoding, through Engine.step(): tokens per second end to end."""
+    import torch
+    import zig_ai_b200 as z
+    from zig_ai_b200.sampling import SamplingParams
+    g = random.Random(7)
+    with tempfile.TemporaryDirectory(prefix="lfm2_mixed_") as d:
+        z.write_random_model(cfg, 0, d)
+        eng = z.Engine(d, "bfloat16", max_num_seqs=64, max_batched_tokens=2048, max_model_len=CONTEXT,
+                       max_tokens=64 * 2560)
+        V = cfg.vocab_size
+        for rep in range(2):                       # the first pass warms up graphs and allocator
+            prompts = [[g.randrange(V) for _ in range(g.randint(256, 2048))] for _ in range(64)]
+            ids = [eng.add_request(p, SamplingParams(temperature=0.0, max_new_tokens=256)) for p in prompts]
+            torch.cuda.synchronize()
+            t0, steps0, done = time.perf_counter(), eng.n_steps, 0
+            while done < len(ids):
+                done += len(eng.step())
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+        n_prompt = sum(len(p) for p in prompts)
+        st = eng.stats()
+    out = {"metric": f"mixed workload tok/s (LFM2-{args.model.upper()} shape, 64 requests, prompts 256-2048, 256 new tokens each)",
+           "value": round(64 * 256 / dt, 1), "unit": "generated tokens/s", "n_gpus": 1, "seconds": round(dt, 3),
+           "prompt_tokens": n_prompt, "prompt_tokens_per_s": round(n_prompt / dt, 1), "steps": eng.n_steps - steps0,
+           "mean_step_ms": round(dt * 1e3 / max(eng.n_steps - steps0, 1), 3),
+           "pages_high_water": max(v for k, v in st.items() if k.endswith("pages_high_water")),
+           "preemptions": st["preemptions"], "dtype": "bf16", "data": "synthetic", "impl": "ours"}
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "gemm"],
                     help="profiling aid: run only the batch-8 decode steps or only the prefill (prints a short line)")
     ap.add_argument("--batch", type=int, default=8, help="with --only decode: the batch size")
+    ap.add_argument("--model", default="350m", choices=sorted(SHAPES), help="which LFM2 shape (default: the 350M shape)")
+    ap.add_argument("--workload", default="steps", choices=["steps", "mixed"],
+                    help="mixed: 64 requests, chunked prefill interleaved with decoding, end to end")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
