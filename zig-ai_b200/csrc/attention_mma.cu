@@ -26,6 +26,9 @@
 #define TILE 64              // keys per tile, query rows per prefill block
 #define CHUNK 256            // keys per decode block
 #define NTHREADS 128
+#ifndef ZAI_DECODE_STAGES
+#define ZAI_DECODE_STAGES 2
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -282,7 +285,7 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_mma_kernel(
 // ------------------------------------------------------------------------------------------ decode
 // part_o [B, Hq, n_chunks, D] unnormalised outputs; part_ml [B, Hq, n_chunks, 2]: maximum (in log2
 // units, already scaled) and sum.  A chunk with no visible key writes (-inf, 0).
-template <int D> struct DecodeStages { static constexpr int N = D <= 64 ? 4 : 3; };   // tiles in flight + 1
+template <int D> struct DecodeStages { static constexpr int N = ZAI_DECODE_STAGES; };   // tiles in flight + 1
 
 template <int D>
 __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
