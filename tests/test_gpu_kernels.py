@@ -390,3 +390,38 @@ def test_tensor_core_gemm_swiglu(N, F, K):
     finally:
         o.USE_TC_GEMM = old
     assert o.tc_status() == 0
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,ps,window,rot,qk_norm", [
+    (4, 2, 16, 16, None, 16, True), (3, 1, 32, 8, None, 32, True), (6, 3, 48, 4, 7, 24, False),
+    (8, 2, 80, 32, None, 80, True), (16, 8, 64, 16, None, 64, True), (2, 2, 128, 16, 40, 64, True), (32, 2, 96, 16, None, 96, True)])
+def test_fused_decode_attention(Hq, Hkv, D, ps, window, rot, qk_norm):
+    """The one-kernel decode attention against the plain versions of its three steps, at contexts of
+    0 keys, around the chunk size of 256, several chunks, and with more chunks launched than needed;
+    run twice on the same buffers (the ticket counters must come back to zero)."""
+    o = ops()
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(40)
+    ctx = [0, 1, 254, 255, 256, 257, 700, 63, 1029]
+    B = len(ctx)
+    num_pages = 1024
+    step = make_step(o, dtype, ctx, [1] * B, ps, num_pages, 41)
+    pages_a = fill_pages(step, ctx, [0] * B, ps, Hkv, D, dtype, num_pages, g)     # the cached keys only
+    pages_b = pages_a.clone()
+    qkv = torch.randn(B, (Hq + 2 * Hkv) * D, generator=g).to(dtype).cuda()
+    qw = (1 + 0.1 * torch.randn(D, generator=g)).cuda() if qk_norm else None
+    kw = (1 + 0.1 * torch.randn(D, generator=g)).cuda() if qk_norm else None
+    va, vb = CacheView(0, pages_a, step.block_tables[0], ps), CacheView(0, pages_b, step.block_tables[0], ps)
+    qb, _ = ref_ops.qk_norm_rope(qkv, qw, kw, 1e-5, rot, 10000.0, step, vb, Hq, Hkv, D, True, True, False)
+    want = ref_ops.paged_attention(qb, step, vb, Hq, Hkv, D, D ** -0.5, window)
+    for max_kv in (step.max_kv_len, 3000):
+        step.max_kv_len = max_kv
+        pa = pages_a.clone()
+        got = o.decode_attention_fused(qkv, qw, kw, 1e-5, rot, 10000.0, step, CacheView(0, pa, step.block_tables[0], ps),
+                                       Hq, Hkv, D, D ** -0.5, window, True)
+        assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2), max_kv
+        assert torch.allclose(pa.float(), pages_b.float(), atol=2e-2, rtol=2e-2)       # the new keys and values
+        assert pa[0].abs().sum() == 0
+    # reading only (a layer that uses another layer's cache): the pages already hold the new position
+    got = o.decode_attention_fused(qkv, qw, kw, 1e-5, rot, 10000.0, step, vb, Hq, Hkv, D, D ** -0.5, window, False)
+    assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2)

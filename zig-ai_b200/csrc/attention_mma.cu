@@ -472,8 +472,309 @@ __global__ void decode_combine_kernel(bf16* __restrict__ out, const float* __res
     }
 }
 
+template <int D> static size_t decode_smem();
+
+// ------------------------------------------------------------------------------------------ fused decode
+// The decode step's whole attention in one kernel, from the raw qkv projection to the output:
+//   * the block normalises (per-head RMSNorm) and rotates its group's query rows itself;
+//   * the block whose chunk holds the new position does the same for the new key, writes key and
+//     value into the request's page, and folds that one key into its sums directly (it is not read
+//     back from the page in this step);
+//   * blocks write their partial sums as before, take a ticket per (request, key/value head), and
+//     the block that draws the last ticket combines all chunks and writes the output (no block waits
+//     for another; the ticket counter is left at zero for the next call).
+// This replaces three kernels of the unfused path (q/k norm + rotary + page write, the chunk
+// kernel, the combine kernel; the reference has one kernel each for norm, rotary, append and
+// attention, src/transformer/hybrid_attn.zig:710-764).
+struct FusedDecodeArgs {
+    bf16* out;                 // [B, Hq, D]
+    float* part_o;             // [B, Hq, n_chunks, D]
+    float* part_ml;            // [B, Hq, n_chunks, 2]
+    int* tickets;              // [B * Hkv], zero before and after
+    const bf16* qkv;           // [B, qkv_cols] = q heads | k heads | v heads
+    const float* q_gamma;      // [D] or null
+    const float* k_gamma;      // [D] or null
+    const float2* cs_table;    // [B, rot/2] (cos, sin) of each row's position, or null when rot == 0
+    bf16* pages;
+    const int* block_table;
+    const int* positions;
+    float eps, scale_log2;
+    int qkv_cols, rot, table_width, page_size, Hq, Hkv, window, write_kv;
+};
+
+// one head row: RMSNorm (if gamma) and rotation of the first `rot` dims; `tmp` holds D floats
+template <int D>
+__device__ __forceinline__ void norm_rotate_row(const bf16* __restrict__ raw, const float* __restrict__ gamma, float eps,
+                                                const float2* __restrict__ cs, int rot, float* tmp, bf16* dst, int lane) {
+    float ss = 0.f;
+    for (int d = lane; d < D; d += 32) {
+        const float v = __bfloat162float(raw[d]);
+        tmp[d] = v;
+        ss += v * v;
+    }
+    if (gamma) {
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)D + eps);
+        for (int d = lane; d < D; d += 32) tmp[d] = tmp[d] * inv * gamma[d];
+    }
+    __syncwarp();
+    const int half = rot >> 1;
+    for (int d = lane; d < D; d += 32) {
+        float v;
+        if (d < half) { const float2 c = cs[d]; v = tmp[d] * c.x - tmp[d + half] * c.y; }
+        else if (d < rot) { const float2 c = cs[d - half]; v = tmp[d - half] * c.y + tmp[d] * c.x; }
+        else v = tmp[d];
+        dst[d] = __float2bfloat16_rn(v);
+    }
+    __syncwarp();
+}
+
+template <int D>
+__global__ void __launch_bounds__(NTHREADS) decode_fused_kernel(const FusedDecodeArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int ST = D + 8, NS = DecodeStages<D>::N;
+    bf16* sq = reinterpret_cast<bf16*>(smem_raw);           // [16][ST]
+    bf16* sk = sq + 16 * ST;                                // [NS][64][ST]
+    bf16* sv = sk + NS * TILE * ST;                         // [NS][64][ST]
+    float* tmp = reinterpret_cast<float*>(sv + NS * TILE * ST);   // [4][D] scratch of the four warps
+    bf16* knew = reinterpret_cast<bf16*>(tmp + 4 * D);      // [D] the new key, [D] the new value
+    bf16* vnew = knew + D;
+    float* snew = reinterpret_cast<float*>(vnew + D);       // [16] scores of the new key
+    __shared__ int s_ticket;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int chunk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z, n_chunks = gridDim.x;
+    const int Hq = a.Hq, Hkv = a.Hkv, G = Hq / Hkv, page_size = a.page_size;
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
+    pdl_trigger();
+    pdl_wait();
+    const int pos = a.positions[b];
+    const int kstart = a.window > 0 ? max(pos - a.window + 1, 0) : 0;
+    const bool has_new = a.write_kv && chunk == pos / CHUNK;        // this block owns the new key
+    const int kend = a.write_kv ? pos : pos + 1;                    // keys read from the pages
+    const int lo = max(chunk * CHUNK, kstart), hi = min((chunk + 1) * CHUNK, kend);
+    const bool any_paged = lo < hi;
+    const int* table = a.block_table + (size_t)b * a.table_width;
+    const size_t page_stride = (size_t)2 * Hkv * page_size * D;
+    const size_t k_off = (size_t)hk * page_size * D, v_off = ((size_t)Hkv + hk) * page_size * D;
+    const int tile0 = lo / TILE, tile1 = any_paged ? (hi + TILE - 1) / TILE : tile0;
+
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    const int g = lane >> 2, tq = lane & 3;
+
+    if (any_paged || has_new) {
+        // the first tiles start moving; one group is committed per tile slot, used or not
+#pragma unroll
+        for (int s = 0; s < NS - 1; ++s) {
+            if (tile0 + s < tile1) {
+                load_kv_tile<D, NTHREADS>(sk + s * TILE * ST, a.pages, table, (tile0 + s) * TILE, lo, hi, page_size, page_shift, page_stride, k_off, tid);
+                load_kv_tile<D, NTHREADS>(sv + s * TILE * ST, a.pages, table, (tile0 + s) * TILE, lo, hi, page_size, page_shift, page_stride, v_off, tid);
+            }
+            cp_async_commit();
+        }
+        // meanwhile: the group's queries, and the new key and value
+        const bf16* row = a.qkv + (size_t)b * a.qkv_cols;
+        const float2* cs = a.rot ? a.cs_table + (size_t)b * (a.rot >> 1) : nullptr;
+        for (int r = warp; r < 16; r += 4) {
+            if (r < G) norm_rotate_row<D>(row + (size_t)(hk * G + r) * D, a.q_gamma, a.eps, cs, a.rot, tmp + warp * D, sq + r * ST, lane);
+            else for (int d = lane; d < D; d += 32) sq[r * ST + d] = __float2bfloat16_rn(0.f);
+        }
+        if (has_new && warp == 0) {
+            norm_rotate_row<D>(row + (size_t)(Hq + hk) * D, a.k_gamma, a.eps, cs, a.rot, tmp, knew, lane);
+            const bf16* vraw = row + (size_t)(Hq + Hkv + hk) * D;
+            int page, off;
+            if (page_shift >= 0) { page = table[pos >> page_shift]; off = pos & (page_size - 1); }
+            else { page = table[pos / page_size]; off = pos % page_size; }
+            bf16* kdst = a.pages + (size_t)page * page_stride + k_off + (size_t)off * D;
+            bf16* vdst = a.pages + (size_t)page * page_stride + v_off + (size_t)off * D;
+            for (int d = lane; d < D; d += 32) {
+                const bf16 v = vraw[d];
+                vnew[d] = v;
+                vdst[d] = v;
+                kdst[d] = knew[d];
+            }
+        }
+        __syncthreads();
+        uint32_t qf[D / 16][4];
+        {
+            const int r = (((lane >> 3) & 1) << 3) + (lane & 7);
+            const int dof = (lane >> 4) << 3;
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) ldmatrix_x4(qf[ks], sq + r * ST + ks * 16 + dof);
+        }
+        if (has_new && warp == 0 && lane < 16) {             // scores of the new key, one query row per lane
+            float dot = 0.f;
+            for (int d = 0; d < D; ++d) dot += __bfloat162float(sq[lane * ST + d]) * __bfloat162float(knew[d]);
+            snew[lane] = dot;
+        }
+
+        for (int t = tile0; t < tile1; ++t) {
+            const int buf = (t - tile0) % NS;
+            cp_async_wait<NS - 2>();                            // tile t has arrived
+            __syncthreads();                                    // and everyone is done with tile t-1
+            {
+                const int nxt = t + NS - 1;
+                if (nxt < tile1) {
+                    const int nb = (nxt - tile0) % NS;
+                    load_kv_tile<D, NTHREADS>(sk + nb * TILE * ST, a.pages, table, nxt * TILE, lo, hi, page_size, page_shift, page_stride, k_off, tid);
+                    load_kv_tile<D, NTHREADS>(sv + nb * TILE * ST, a.pages, table, nxt * TILE, lo, hi, page_size, page_shift, page_stride, v_off, tid);
+                }
+                cp_async_commit();
+            }
+            const int j0 = t * TILE + warp * 16;                // this warp's 16 keys of the tile
+            if (j0 < hi && j0 + 16 > lo) {
+                float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+                qk_16keys<D>(s0, s1, qf, sk + (buf * TILE + warp * 16) * ST, lane);
+                float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int ja = j0 + 2 * tq + e, jb = ja + 8;
+                    if (ja < lo || ja >= hi) { s0[e] = -INFINITY; s0[2 + e] = -INFINITY; }
+                    if (jb < lo || jb >= hi) { s1[e] = -INFINITY; s1[2 + e] = -INFINITY; }
+                    mx0 = fmaxf(mx0, fmaxf(s0[e], s1[e]));
+                    mx1 = fmaxf(mx1, fmaxf(s0[2 + e], s1[2 + e]));
+                }
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+                const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);   // finite: the warp has a visible key
+                const float u0 = n0 * a.scale_log2, u1 = n1 * a.scale_log2;
+                const float c0 = exp2f(m0 * a.scale_log2 - u0), c1 = exp2f(m1 * a.scale_log2 - u1);
+                m0 = n0;
+                m1 = n1;
+#pragma unroll
+                for (int i = 0; i < D / 8; ++i) {
+                    o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1;
+                }
+                s0[0] = exp2f(s0[0] * a.scale_log2 - u0); s0[1] = exp2f(s0[1] * a.scale_log2 - u0);
+                s0[2] = exp2f(s0[2] * a.scale_log2 - u1); s0[3] = exp2f(s0[3] * a.scale_log2 - u1);
+                s1[0] = exp2f(s1[0] * a.scale_log2 - u0); s1[1] = exp2f(s1[1] * a.scale_log2 - u0);
+                s1[2] = exp2f(s1[2] * a.scale_log2 - u1); s1[3] = exp2f(s1[3] * a.scale_log2 - u1);
+                l0 = l0 * c0 + s0[0] + s0[1] + s1[0] + s1[1];
+                l1 = l1 * c1 + s0[2] + s0[3] + s1[2] + s1[3];
+                uint32_t pf[4];
+                pf[0] = pack_bf16(s0[0], s0[1]);
+                pf[1] = pack_bf16(s0[2], s0[3]);
+                pf[2] = pack_bf16(s1[0], s1[1]);
+                pf[3] = pack_bf16(s1[2], s1[3]);
+                pv_16keys<D>(o, pf, sv + (buf * TILE + warp * 16) * ST, lane);
+            }
+        }
+        cp_async_wait<0>();
+        __syncthreads();                                        // tiles done; snew, vnew visible
+        if (has_new && warp == 0) {                             // fold the new key into warp 0's sums
+            const float s0 = snew[g], s1 = snew[g + 8];
+            const float n0 = fmaxf(m0, s0), n1 = fmaxf(m1, s1);
+            const float c0 = exp2f(m0 * a.scale_log2 - n0 * a.scale_log2), c1 = exp2f(m1 * a.scale_log2 - n1 * a.scale_log2);
+            const float p0 = exp2f(s0 * a.scale_log2 - n0 * a.scale_log2), p1 = exp2f(s1 * a.scale_log2 - n1 * a.scale_log2);
+            m0 = n0;
+            m1 = n1;
+            l0 = l0 * c0 + (tq == 0 ? p0 : 0.f);                // the row's sum is spread over the four lanes of a quad
+            l1 = l1 * c1 + (tq == 0 ? p1 : 0.f);
+#pragma unroll
+            for (int i = 0; i < D / 8; ++i) {
+                const float v0 = __bfloat162float(vnew[i * 8 + 2 * tq]), v1 = __bfloat162float(vnew[i * 8 + 2 * tq + 1]);
+                o[i][0] = o[i][0] * c0 + p0 * v0; o[i][1] = o[i][1] * c0 + p0 * v1;
+                o[i][2] = o[i][2] * c1 + p1 * v0; o[i][3] = o[i][3] * c1 + p1 * v1;
+            }
+        }
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+        // combine the four warps through shared memory (the tiles are no longer needed)
+        float* wo = reinterpret_cast<float*>(sk);               // [4][16][D]
+        float* wm = wo + 4 * 16 * D;                            // [4][16] maxima (log2 units)
+        float* wl = wm + 4 * 16;                                // [4][16] sums
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+            const int d = i * 8 + 2 * tq;
+            wo[(warp * 16 + g) * D + d] = o[i][0];
+            wo[(warp * 16 + g) * D + d + 1] = o[i][1];
+            wo[(warp * 16 + g + 8) * D + d] = o[i][2];
+            wo[(warp * 16 + g + 8) * D + d + 1] = o[i][3];
+        }
+        if (tq == 0) {
+            wm[warp * 16 + g] = m0 == -INFINITY ? -INFINITY : m0 * a.scale_log2;
+            wm[warp * 16 + g + 8] = m1 == -INFINITY ? -INFINITY : m1 * a.scale_log2;
+            wl[warp * 16 + g] = l0;
+            wl[warp * 16 + g + 8] = l1;
+        }
+        __syncthreads();
+        for (int idx = tid; idx < G * D; idx += NTHREADS) {
+            const int r = idx / D, d = idx % D;
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) M = fmaxf(M, wm[w * 16 + r]);
+            float acc = 0.f, L = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float mw = wm[w * 16 + r];
+                const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+                acc += wo[(w * 16 + r) * D + d] * f;
+                L += wl[w * 16 + r] * f;
+            }
+            const size_t base = ((size_t)b * Hq + hk * G + r) * n_chunks + chunk;
+            a.part_o[base * D + d] = acc;
+            if (d == 0) {
+                a.part_ml[base * 2] = M;
+                a.part_ml[base * 2 + 1] = L;
+            }
+        }
+    } else if (tid < G) {
+        float* ml = a.part_ml + (((size_t)b * Hq + hk * G + tid) * n_chunks + chunk) * 2;
+        ml[0] = -INFINITY;
+        ml[1] = 0.f;
+    }
+
+    // ---- the last block of this (request, key/value head) combines the chunks
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_ticket = atomicAdd(&a.tickets[b * Hkv + hk], 1);
+    __syncthreads();
+    if (s_ticket != n_chunks - 1) return;
+    __threadfence();
+    for (int idx = tid; idx < G * D; idx += NTHREADS) {
+        const int r = idx / D, d = idx % D;
+        const size_t bh = (size_t)b * Hq + hk * G + r;
+        const float* ml = a.part_ml + bh * n_chunks * 2;
+        float M = -INFINITY;
+        for (int c = 0; c < n_chunks; ++c) M = fmaxf(M, __ldcg(ml + 2 * c));
+        float acc = 0.f, L = 0.f;
+        for (int c = 0; c < n_chunks; ++c) {
+            const float mc = __ldcg(ml + 2 * c);
+            if (mc == -INFINITY) continue;
+            const float f = exp2f(mc - M);
+            acc += __ldcg(a.part_o + (bh * n_chunks + c) * D + d) * f;
+            L += __ldcg(ml + 2 * c + 1) * f;
+        }
+        a.out[bh * D + d] = __float2bfloat16_rn(acc / L);
+    }
+    if (tid == 0) a.tickets[b * Hkv + hk] = 0;
+}
+
+template <int D> static size_t decode_fused_smem() {
+    return decode_smem<D>() + (size_t)4 * D * sizeof(float) + (size_t)2 * D * sizeof(bf16) + 16 * sizeof(float) + 64;
+}
+
+template <int D>
+static int launch_decode_fused(const FusedDecodeArgs& a, int B, int n_chunks, cudaStream_t stream) {
+    const size_t smem = decode_fused_smem<D>();
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(decode_fused_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    return launch_pdl(decode_fused_kernel<D>, dim3(n_chunks, a.Hkv, B), dim3(NTHREADS), smem, stream, a);
+}
+
 template <int D> static size_t prefill_smem() { return (size_t)(PREFILL_ROWS + 4 * TILE) * (D + 8) * sizeof(bf16); }
-template <int D> static size_t decode_smem() {
+template <int D> size_t decode_smem() {
     const size_t tiles = (size_t)(16 + 2 * DecodeStages<D>::N * TILE) * (D + 8) * sizeof(bf16);
     const size_t comb = 16 * (D + 8) * sizeof(bf16) + (size_t)(4 * 16 * D + 2 * 4 * 16) * sizeof(float);
     return tiles > comb ? tiles : comb;
@@ -548,6 +849,28 @@ ZAI_API int zai_decode_attention_mma(void* out, float* part_o, float* part_ml, c
     if (n_chunks < 1 || Hkv > 65535 || B > 65535 || Hq % Hkv != 0 || Hq / Hkv > 16) return ZAI_BAD_SIZE;
 #define X(d) if (D == d) return launch_decode<d>((bf16*)out, part_o, part_ml, (const bf16*)q, (const bf16*)pages, block_table, \
                                                  table_width, positions, B, n_chunks, page_size, Hq, Hkv, scale, window, stream);
+    ZAI_HEAD_DIMS(X)
+#undef X
+    return ZAI_BAD_SIZE;
+}
+
+// The decode step's attention from the raw qkv rows: see decode_fused_kernel.  `tickets` holds
+// B * Hkv zeros (and again after the call).
+ZAI_API int zai_decode_attention_fused(void* out, float* part_o, float* part_ml, int* tickets, const void* qkv,
+                                       int qkv_cols, const float* q_gamma, const float* k_gamma, float eps,
+                                       const float2* cs_table, int rot, void* pages, const int* block_table,
+                                       int table_width, const int* positions, int B, int n_chunks, int page_size,
+                                       int Hq, int Hkv, int D, float scale, int window, int write_kv,
+                                       cudaStream_t stream) {
+    if (B <= 0) return ZAI_OK;
+    if (n_chunks < 1 || Hkv > 65535 || B > 65535 || Hq % Hkv != 0 || Hq / Hkv > 16 || rot < 0 || rot > D || (rot & 1))
+        return ZAI_BAD_SIZE;
+    FusedDecodeArgs a;
+    a.out = (bf16*)out; a.part_o = part_o; a.part_ml = part_ml; a.tickets = tickets; a.qkv = (const bf16*)qkv;
+    a.q_gamma = q_gamma; a.k_gamma = k_gamma; a.cs_table = cs_table; a.pages = (bf16*)pages; a.block_table = block_table;
+    a.positions = positions; a.eps = eps; a.scale_log2 = scale * 1.4426950408889634f; a.qkv_cols = qkv_cols; a.rot = rot;
+    a.table_width = table_width; a.page_size = page_size; a.Hq = Hq; a.Hkv = Hkv; a.window = window; a.write_kv = write_kv;
+#define X(d) if (D == d) return launch_decode_fused<d>(a, B, n_chunks, stream);
     ZAI_HEAD_DIMS(X)
 #undef X
     return ZAI_BAD_SIZE;

@@ -44,6 +44,8 @@ _SIGNATURES = {
         "zai_attention_mma_supports": [_I, _I, _I],
         "zai_prefill_attention_mma": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
         "zai_decode_attention_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+        "zai_decode_attention_fused": [_P, _P, _P, _P, _P, _I, _P, _P, _F, _P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I,
+                                       _F, _I, _I, _P],
         "zai_decode_chunk_keys": [],
         "zai_prefill_block_rows": [],
     },
@@ -390,6 +392,40 @@ def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=Non
         _ptr(out), _ptr(q), _ptr(cache.pages), _dt(q), _ptr(bt), bt.shape[1],
         _ptr(step.positions), _ptr(step.seq_idx), cache.page_size, N, heads, kv_heads, head_dim, float(scale),
         int(window or 0), _stream()), "paged_attention")
+    return out
+
+
+_tickets = {}
+
+
+def fused_decode_attention_available(dtype, heads, kv_heads, head_dim) -> bool:
+    return dtype == torch.bfloat16 and bool(_fn("attention_mma", "zai_attention_mma_supports")(head_dim, heads, kv_heads))
+
+
+def decode_attention_fused(qkv, q_w, k_w, eps, rotary_dim, theta, step, cache, heads, kv_heads, head_dim, scale,
+                           window=None, write=True):
+    """A decode step's attention in one kernel, from the qkv projection's rows [B, (Hq + 2 Hkv) D]:
+    q/k RMSNorm, rotation, the new key and value into their page, attention over the pages in chunks
+    of keys, and the combination of the chunks.  Every row of the step is one token."""
+    _cuda(qkv, q_w, k_w)
+    B, cols = qkv.shape
+    dev = qkv.device
+    out = torch.empty((B, heads * head_dim), dtype=qkv.dtype, device=dev)
+    chunk = _fn("attention_mma", "zai_decode_chunk_keys")()
+    n_chunks = max(-(-int(step.max_kv_len) // chunk), 1)
+    part_o = torch.empty((B, heads, n_chunks, head_dim), dtype=torch.float32, device=dev)
+    part_ml = torch.empty((B, heads, n_chunks, 2), dtype=torch.float32, device=dev)
+    tickets = _tickets.get(str(dev))
+    if tickets is None or tickets.numel() < B * kv_heads:
+        tickets = torch.zeros(max(B * kv_heads, 65536), dtype=torch.int32, device=dev)
+        _tickets[str(dev)] = tickets
+    table = rope_table(step, rotary_dim, theta, dev) if rotary_dim else None
+    bt = cache.block_table
+    _check(_fn("attention_mma", "zai_decode_attention_fused")(
+        _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(tickets), _ptr(qkv), cols, _ptr(q_w), _ptr(k_w), float(eps),
+        _ptr(table), int(rotary_dim), _ptr(cache.pages), _ptr(bt), bt.shape[1], _ptr(step.positions), B, n_chunks,
+        cache.page_size, heads, kv_heads, head_dim, float(scale), int(window or 0), int(bool(write)), _stream()),
+        "decode_attention_fused")
     return out
 
 

@@ -67,6 +67,14 @@ class Attention(Mixer):
         write = write_cache and self.kv_proj
         qkv = ops.linear(x, self.w_qkv)
         rot = self.position.rotary()
+        fused = getattr(ops, "fused_decode_attention_available", None)
+        if (rot is not None and step.decode_only and self.kv_proj and fused is not None
+                and fused(qkv.dtype, self.heads, self.kv_heads, self.head_dim)):
+            # every row is one token: norm, rotation, page write, attention and the combination of
+            # the key chunks run as one kernel
+            o = ops.decode_attention_fused(qkv, self.q_norm, self.k_norm, self.eps, rot[0], rot[1], step, cache,
+                                           self.heads, self.kv_heads, self.head_dim, self.scale, self.window, write)
+            return ops.linear(o, self.w_o)
         if rot is not None:
             q, _ = ops.qk_norm_rope(qkv, self.q_norm, self.k_norm, self.eps, rot[0], rot[1], step, cache,
                                     self.heads, self.kv_heads, self.head_dim, self.kv_proj, write, False)
