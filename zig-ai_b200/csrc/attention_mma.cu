@@ -86,6 +86,35 @@ __device__ __forceinline__ void load_kv_tile(bf16* dst, const bf16* __restrict__
     }
 }
 
+// The same for one warp alone: rows t0 .. t0+63 of keys and values of one head, each row's page
+// looked up once for both.
+template <int D>
+__device__ __forceinline__ void load_kv_tile_warp(bf16* kdst, bf16* vdst, const bf16* __restrict__ pages,
+                                                  const int* __restrict__ table, int t0, int kstart, int kend,
+                                                  int page_size, int page_shift, size_t page_stride, size_t k_off,
+                                                  size_t v_off, int lane) {
+    constexpr int CH = D / 8;
+    for (int idx = lane; idx < TILE * CH; idx += 32) {
+        const int r = idx / CH, c = idx % CH;
+        const int j = t0 + r;
+        const bool valid = j >= kstart && j < kend;
+        const bf16* src = pages;
+        if (valid) {
+            int page, off;
+            if (page_shift >= 0) {
+                page = table[j >> page_shift];
+                off = j & (page_size - 1);
+            } else {
+                page = table[j / page_size];
+                off = j % page_size;
+            }
+            src = pages + (size_t)page * page_stride + (size_t)off * D + c * 8;
+        }
+        cp_async16(kdst + r * (D + 8) + c * 8, src + (valid ? k_off : 0), valid);
+        cp_async16(vdst + r * (D + 8) + c * 8, src + (valid ? v_off : 0), valid);
+    }
+}
+
 // S[16 x 16 keys] += Q (A fragments of all D/16 steps) . K^T for the 16 keys at `krows` (shared, stride D+8)
 template <int D>
 __device__ __forceinline__ void qk_16keys(float (&s0)[4], float (&s1)[4], const uint32_t (&qf)[D / 16][4],
@@ -500,6 +529,7 @@ struct FusedDecodeArgs {
     const int* positions;
     float eps, scale_log2;
     int qkv_cols, rot, table_width, page_size, Hq, Hkv, window, write_kv;
+    int chunk_keys;            // keys per block: a multiple of 64
 };
 
 // one head row: RMSNorm (if gamma) and rotation of the first `rot` dims; `tmp` holds D floats
@@ -532,11 +562,11 @@ __device__ __forceinline__ void norm_rotate_row(const bf16* __restrict__ raw, co
 template <int D>
 __global__ void __launch_bounds__(NTHREADS) decode_fused_kernel(const FusedDecodeArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    constexpr int ST = D + 8, NS = DecodeStages<D>::N;
+    constexpr int ST = D + 8;
     bf16* sq = reinterpret_cast<bf16*>(smem_raw);           // [16][ST]
-    bf16* sk = sq + 16 * ST;                                // [NS][64][ST]
-    bf16* sv = sk + NS * TILE * ST;                         // [NS][64][ST]
-    float* tmp = reinterpret_cast<float*>(sv + NS * TILE * ST);   // [4][D] scratch of the four warps
+    bf16* sk = sq + 16 * ST;                                // [4 warps][64][ST]: each warp loads and reads its own tiles
+    bf16* sv = sk + 4 * TILE * ST;                          // [4 warps][64][ST]
+    float* tmp = reinterpret_cast<float*>(sv + 4 * TILE * ST);    // [4][D] scratch of the four warps
     bf16* knew = reinterpret_cast<bf16*>(tmp + 4 * D);      // [D] the new key, [D] the new value
     bf16* vnew = knew + D;
     float* snew = reinterpret_cast<float*>(vnew + D);       // [16] scores of the new key
@@ -549,9 +579,9 @@ __global__ void __launch_bounds__(NTHREADS) decode_fused_kernel(const FusedDecod
     pdl_wait();
     const int pos = a.positions[b];
     const int kstart = a.window > 0 ? max(pos - a.window + 1, 0) : 0;
-    const bool has_new = a.write_kv && chunk == pos / CHUNK;        // this block owns the new key
+    const bool has_new = a.write_kv && chunk == pos / a.chunk_keys;        // this block owns the new key
     const int kend = a.write_kv ? pos : pos + 1;                    // keys read from the pages
-    const int lo = max(chunk * CHUNK, kstart), hi = min((chunk + 1) * CHUNK, kend);
+    const int lo = max(chunk * a.chunk_keys, kstart), hi = min((chunk + 1) * a.chunk_keys, kend);
     const bool any_paged = lo < hi;
     const int* table = a.block_table + (size_t)b * a.table_width;
     const size_t page_stride = (size_t)2 * Hkv * page_size * D;
@@ -565,15 +595,13 @@ __global__ void __launch_bounds__(NTHREADS) decode_fused_kernel(const FusedDecod
     const int g = lane >> 2, tq = lane & 3;
 
     if (any_paged || has_new) {
-        // the first tiles start moving; one group is committed per tile slot, used or not
-#pragma unroll
-        for (int s = 0; s < NS - 1; ++s) {
-            if (tile0 + s < tile1) {
-                load_kv_tile<D, NTHREADS>(sk + s * TILE * ST, a.pages, table, (tile0 + s) * TILE, lo, hi, page_size, page_shift, page_stride, k_off, tid);
-                load_kv_tile<D, NTHREADS>(sv + s * TILE * ST, a.pages, table, (tile0 + s) * TILE, lo, hi, page_size, page_shift, page_stride, v_off, tid);
-            }
-            cp_async_commit();
-        }
+        // each warp takes the tiles tile0 + warp, tile0 + warp + 4, ... of the chunk and loads them
+        // itself (no block-wide barrier per tile); the first one starts moving now
+        bf16* wk = sk + warp * TILE * ST;
+        bf16* wv = sv + warp * TILE * ST;
+        if (tile0 + warp < tile1)
+            load_kv_tile_warp<D>(wk, wv, a.pages, table, (tile0 + warp) * TILE, lo, hi, page_size, page_shift, page_stride, k_off, v_off, lane);
+        cp_async_commit();
         // meanwhile: the group's queries, and the new key and value
         const bf16* row = a.qkv + (size_t)b * a.qkv_cols;
         const float2* cs = a.rot ? a.cs_table + (size_t)b * (a.rot >> 1) : nullptr;
@@ -610,58 +638,65 @@ __global__ void __launch_bounds__(NTHREADS) decode_fused_kernel(const FusedDecod
             snew[lane] = dot;
         }
 
-        for (int t = tile0; t < tile1; ++t) {
-            const int buf = (t - tile0) % NS;
-            cp_async_wait<NS - 2>();                            // tile t has arrived
-            __syncthreads();                                    // and everyone is done with tile t-1
-            {
-                const int nxt = t + NS - 1;
-                if (nxt < tile1) {
-                    const int nb = (nxt - tile0) % NS;
-                    load_kv_tile<D, NTHREADS>(sk + nb * TILE * ST, a.pages, table, nxt * TILE, lo, hi, page_size, page_shift, page_stride, k_off, tid);
-                    load_kv_tile<D, NTHREADS>(sv + nb * TILE * ST, a.pages, table, nxt * TILE, lo, hi, page_size, page_shift, page_stride, v_off, tid);
+        for (int t = tile0 + warp; t < tile1; t += 4) {
+            cp_async_wait<0>();
+            __syncwarp();                                       // this warp's tile t has arrived
+            float sc[8][4];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
+#pragma unroll
+            for (int kb = 0; kb < 4; ++kb) qk_16keys<D>(sc[2 * kb], sc[2 * kb + 1], qf, wk + kb * 16 * ST, lane);
+            float mx0 = -INFINITY, mx1 = -INFINITY;
+            const bool edge = t * TILE < lo || (t + 1) * TILE > hi;      // some keys of the tile are not visible
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+                if (edge) {
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int j = t * TILE + nt * 8 + 2 * tq + e;
+                        if (j < lo || j >= hi) { sc[nt][e] = -INFINITY; sc[nt][2 + e] = -INFINITY; }
+                    }
                 }
-                cp_async_commit();
+                mx0 = fmaxf(mx0, fmaxf(sc[nt][0], sc[nt][1]));
+                mx1 = fmaxf(mx1, fmaxf(sc[nt][2], sc[nt][3]));
             }
-            const int j0 = t * TILE + warp * 16;                // this warp's 16 keys of the tile
-            if (j0 < hi && j0 + 16 > lo) {
-                float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
-                qk_16keys<D>(s0, s1, qf, sk + (buf * TILE + warp * 16) * ST, lane);
-                float mx0 = -INFINITY, mx1 = -INFINITY;
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);   // finite: the tile has a visible key
+            const float u0 = n0 * a.scale_log2, u1 = n1 * a.scale_log2;
+            const float c0 = exp2f(m0 * a.scale_log2 - u0), c1 = exp2f(m1 * a.scale_log2 - u1);
+            m0 = n0;
+            m1 = n1;
+            l0 *= c0;
+            l1 *= c1;
 #pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int ja = j0 + 2 * tq + e, jb = ja + 8;
-                    if (ja < lo || ja >= hi) { s0[e] = -INFINITY; s0[2 + e] = -INFINITY; }
-                    if (jb < lo || jb >= hi) { s1[e] = -INFINITY; s1[2 + e] = -INFINITY; }
-                    mx0 = fmaxf(mx0, fmaxf(s0[e], s1[e]));
-                    mx1 = fmaxf(mx1, fmaxf(s0[2 + e], s1[2 + e]));
-                }
-                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-                const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);   // finite: the warp has a visible key
-                const float u0 = n0 * a.scale_log2, u1 = n1 * a.scale_log2;
-                const float c0 = exp2f(m0 * a.scale_log2 - u0), c1 = exp2f(m1 * a.scale_log2 - u1);
-                m0 = n0;
-                m1 = n1;
+            for (int i = 0; i < D / 8; ++i) {
+                o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1;
+            }
 #pragma unroll
-                for (int i = 0; i < D / 8; ++i) {
-                    o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1;
-                }
-                s0[0] = exp2f(s0[0] * a.scale_log2 - u0); s0[1] = exp2f(s0[1] * a.scale_log2 - u0);
-                s0[2] = exp2f(s0[2] * a.scale_log2 - u1); s0[3] = exp2f(s0[3] * a.scale_log2 - u1);
-                s1[0] = exp2f(s1[0] * a.scale_log2 - u0); s1[1] = exp2f(s1[1] * a.scale_log2 - u0);
-                s1[2] = exp2f(s1[2] * a.scale_log2 - u1); s1[3] = exp2f(s1[3] * a.scale_log2 - u1);
-                l0 = l0 * c0 + s0[0] + s0[1] + s1[0] + s1[1];
-                l1 = l1 * c1 + s0[2] + s0[3] + s1[2] + s1[3];
+            for (int nt = 0; nt < 8; ++nt) {
+                sc[nt][0] = exp2f(sc[nt][0] * a.scale_log2 - u0);
+                sc[nt][1] = exp2f(sc[nt][1] * a.scale_log2 - u0);
+                sc[nt][2] = exp2f(sc[nt][2] * a.scale_log2 - u1);
+                sc[nt][3] = exp2f(sc[nt][3] * a.scale_log2 - u1);
+                l0 += sc[nt][0] + sc[nt][1];
+                l1 += sc[nt][2] + sc[nt][3];
+            }
+#pragma unroll
+            for (int kb = 0; kb < 4; ++kb) {
                 uint32_t pf[4];
-                pf[0] = pack_bf16(s0[0], s0[1]);
-                pf[1] = pack_bf16(s0[2], s0[3]);
-                pf[2] = pack_bf16(s1[0], s1[1]);
-                pf[3] = pack_bf16(s1[2], s1[3]);
-                pv_16keys<D>(o, pf, sv + (buf * TILE + warp * 16) * ST, lane);
+                pf[0] = pack_bf16(sc[2 * kb][0], sc[2 * kb][1]);
+                pf[1] = pack_bf16(sc[2 * kb][2], sc[2 * kb][3]);
+                pf[2] = pack_bf16(sc[2 * kb + 1][0], sc[2 * kb + 1][1]);
+                pf[3] = pack_bf16(sc[2 * kb + 1][2], sc[2 * kb + 1][3]);
+                pv_16keys<D>(o, pf, wv + kb * 16 * ST, lane);
             }
+            __syncwarp();                                       // the buffers are read; the next tile may land
+            if (t + 4 < tile1)
+                load_kv_tile_warp<D>(wk, wv, a.pages, table, (t + 4) * TILE, lo, hi, page_size, page_shift, page_stride, k_off, v_off, lane);
+            cp_async_commit();
         }
         cp_async_wait<0>();
         __syncthreads();                                        // tiles done; snew, vnew visible
@@ -758,7 +793,8 @@ __global__ void __launch_bounds__(NTHREADS) decode_fused_kernel(const FusedDecod
 }
 
 template <int D> static size_t decode_fused_smem() {
-    return decode_smem<D>() + (size_t)4 * D * sizeof(float) + (size_t)2 * D * sizeof(bf16) + 16 * sizeof(float) + 64;
+    const size_t tiles = (size_t)(16 + 2 * 4 * TILE) * (D + 8) * sizeof(bf16);
+    return tiles + (size_t)4 * D * sizeof(float) + (size_t)2 * D * sizeof(bf16) + 16 * sizeof(float) + 64;
 }
 
 template <int D>
@@ -860,16 +896,17 @@ ZAI_API int zai_decode_attention_fused(void* out, float* part_o, float* part_ml,
                                        int qkv_cols, const float* q_gamma, const float* k_gamma, float eps,
                                        const float2* cs_table, int rot, void* pages, const int* block_table,
                                        int table_width, const int* positions, int B, int n_chunks, int page_size,
-                                       int Hq, int Hkv, int D, float scale, int window, int write_kv,
+                                       int Hq, int Hkv, int D, float scale, int window, int write_kv, int chunk_keys,
                                        cudaStream_t stream) {
     if (B <= 0) return ZAI_OK;
+    if (chunk_keys < TILE || chunk_keys % TILE) return ZAI_BAD_SIZE;
     if (n_chunks < 1 || Hkv > 65535 || B > 65535 || Hq % Hkv != 0 || Hq / Hkv > 16 || rot < 0 || rot > D || (rot & 1))
         return ZAI_BAD_SIZE;
     FusedDecodeArgs a;
     a.out = (bf16*)out; a.part_o = part_o; a.part_ml = part_ml; a.tickets = tickets; a.qkv = (const bf16*)qkv;
     a.q_gamma = q_gamma; a.k_gamma = k_gamma; a.cs_table = cs_table; a.pages = (bf16*)pages; a.block_table = block_table;
     a.positions = positions; a.eps = eps; a.scale_log2 = scale * 1.4426950408889634f; a.qkv_cols = qkv_cols; a.rot = rot;
-    a.table_width = table_width; a.page_size = page_size; a.Hq = Hq; a.Hkv = Hkv; a.window = window; a.write_kv = write_kv;
+    a.table_width = table_width; a.page_size = page_size; a.Hq = Hq; a.Hkv = Hkv; a.window = window; a.write_kv = write_kv; a.chunk_keys = chunk_keys;
 #define X(d) if (D == d) return launch_decode_fused<d>(a, B, n_chunks, stream);
     ZAI_HEAD_DIMS(X)
 #undef X

@@ -45,7 +45,7 @@ _SIGNATURES = {
         "zai_prefill_attention_mma": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
         "zai_decode_attention_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
         "zai_decode_attention_fused": [_P, _P, _P, _P, _P, _I, _P, _P, _F, _P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I,
-                                       _F, _I, _I, _P],
+                                       _F, _I, _I, _I, _P],
         "zai_decode_chunk_keys": [],
         "zai_prefill_block_rows": [],
     },
@@ -396,6 +396,7 @@ def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=Non
 
 
 _tickets = {}
+DECODE_BLOCKS_WANTED = 1500      # about two waves of five blocks per SM
 
 
 def fused_decode_attention_available(dtype, heads, kv_heads, head_dim) -> bool:
@@ -411,7 +412,13 @@ def decode_attention_fused(qkv, q_w, k_w, eps, rotary_dim, theta, step, cache, h
     B, cols = qkv.shape
     dev = qkv.device
     out = torch.empty((B, heads * head_dim), dtype=qkv.dtype, device=dev)
-    chunk = _fn("attention_mma", "zai_decode_chunk_keys")()
+    # keys per block: enough blocks to fill the SMs a few times over, few enough that a block's
+    # start-up and its partial sums are spread over many keys (a power of two between 128 and 1024)
+    want = int(step.max_kv_len) * B * kv_heads // DECODE_BLOCKS_WANTED
+    chunk = 128
+    while chunk < 1024 and chunk < want:
+        chunk *= 2
+    chunk = int(os.environ.get("ZAI_DECODE_CHUNK", chunk))
     n_chunks = max(-(-int(step.max_kv_len) // chunk), 1)
     part_o = torch.empty((B, heads, n_chunks, head_dim), dtype=torch.float32, device=dev)
     part_ml = torch.empty((B, heads, n_chunks, 2), dtype=torch.float32, device=dev)
@@ -424,7 +431,7 @@ def decode_attention_fused(qkv, q_w, k_w, eps, rotary_dim, theta, step, cache, h
     _check(_fn("attention_mma", "zai_decode_attention_fused")(
         _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(tickets), _ptr(qkv), cols, _ptr(q_w), _ptr(k_w), float(eps),
         _ptr(table), int(rotary_dim), _ptr(cache.pages), _ptr(bt), bt.shape[1], _ptr(step.positions), B, n_chunks,
-        cache.page_size, heads, kv_heads, head_dim, float(scale), int(window or 0), int(bool(write)), _stream()),
+        cache.page_size, heads, kv_heads, head_dim, float(scale), int(window or 0), int(bool(write)), chunk, _stream()),
         "decode_attention_fused")
     return out
 
