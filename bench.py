@@ -153,12 +153,17 @@ def time_decode(eng, B, steps, warmup, clocks=None):
     launches0 = ops.launches
     if clocks:
         clocks.mark()
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps - 1)]
     start.record()
     for k in range(steps):
         ops.argmax(runner.run_prepared(prepared[warmup + k]))
+        if k < steps - 1:
+            marks[k].record()
     stop.record()
     torch.cuda.synchronize()
     dev_ms = start.elapsed_time(stop) / steps
+    edges = [start] + marks + [stop]
+    per_step = [edges[k].elapsed_time(edges[k + 1]) for k in range(steps)]
     launches = (ops.launches - launches0) / steps
     # the scheduler's view has to follow what was run behind its back
     for r in reqs:
@@ -168,10 +173,20 @@ def time_decode(eng, B, steps, warmup, clocks=None):
         eng.step()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
+    e2e_steps = []
     for _ in range(steps):
+        t1 = time.perf_counter()
         eng.step()
+        e2e_steps.append((time.perf_counter() - t1) * 1e3)
     torch.cuda.synchronize()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / steps
+    if os.environ.get("ZAI_BENCH_STEPS"):
+        worst = max(range(steps), key=lambda k: per_step[k])
+        worst_e = max(range(steps), key=lambda k: e2e_steps[k])
+        print(f"[bench] batch {B}: device median {sorted(per_step)[steps // 2]:.3f} ms, worst {per_step[worst]:.3f} ms at step "
+              f"{worst}; e2e median {sorted(e2e_steps)[steps // 2]:.3f} ms, worst {e2e_steps[worst_e]:.3f} ms at step {worst_e}; "
+              f"kernel status {ops.tc_status()}",
+              file=sys.stderr, flush=True)
     clock_info = clocks.stop() if clocks else None
     for r in list(reqs):
         if r.request_id in eng.requests:
@@ -222,7 +237,7 @@ def run_ours(args):
     with tempfile.TemporaryDirectory(prefix="lfm2_350m_") as d:
         z.write_random_model(cfg, 0, d)
         eng = z.Engine(d, "bfloat16", max_num_seqs=64, max_batched_tokens=2048 + 64, max_model_len=CONTEXT,
-                       max_tokens=64 * CONTEXT)
+                       max_tokens=64 * CONTEXT, page_size=args.page_size)
         if args.only == "gemm":
             return run_gemm_table(cfg)
         if args.only == "prefill":
@@ -256,7 +271,7 @@ def run_ours(args):
                    "attn_layers": nums["n_attn"], "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads,
                    "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim, "ff_dim": cfg.ff_dim,
                    "vocab": cfg.vocab_size, "conv_taps": cfg.conv_L_cache, "global_batch": 8, "seq_len": CONTEXT,
-                   "mean_context": round(ctx_tokens / 8), "page_size": 16, "parallelism": "single GPU",
+                   "mean_context": round(ctx_tokens / 8), "page_size": args.page_size, "parallelism": "single GPU",
                    "l2": f"step reads {weight_bytes / 1e9:.2f} GB of weights (> 126 MB L2)", "peaks": peak_src},
         "e2e": {"value": round(8 / e2e_ms * 1e3, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -379,6 +394,7 @@ def main():
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "gemm"],
                     help="profiling aid: run only the batch-8 decode steps or only the prefill (prints a short line)")
     ap.add_argument("--batch", type=int, default=8, help="with --only decode: the batch size")
+    ap.add_argument("--page-size", type=int, default=64, help="positions per cache page")
     ap.add_argument("--model", default="350m", choices=sorted(SHAPES), help="which LFM2 shape (default: the 350M shape)")
     ap.add_argument("--workload", default="steps", choices=["steps", "mixed"],
                     help="mixed: 64 requests, chunked prefill interleaved with decoding, end to end")

@@ -394,12 +394,15 @@ def test_tensor_core_gemm_swiglu(N, F, K):
 
 @pytest.mark.parametrize("Hq,Hkv,D,ps,window,rot,qk_norm", [
     (4, 2, 16, 16, None, 16, True), (3, 1, 32, 8, None, 32, True), (6, 3, 48, 4, 7, 24, False),
-    (8, 2, 80, 32, None, 80, True), (16, 8, 64, 16, None, 64, True), (2, 2, 128, 16, 40, 64, True), (32, 2, 96, 16, None, 96, True)])
-def test_fused_decode_attention(Hq, Hkv, D, ps, window, rot, qk_norm):
+    (8, 2, 80, 32, None, 80, True), (16, 8, 64, 16, None, 64, True), (2, 2, 128, 16, 40, 64, True), (32, 2, 96, 16, None, 96, True),
+    (4, 1, 64, 8, None, 64, True), (6, 2, 64, 32, 300, 32, False), (16, 1, 64, 64, None, 64, True)])
+@pytest.mark.parametrize("tma", [True, False])
+def test_fused_decode_attention(Hq, Hkv, D, ps, window, rot, qk_norm, tma):
     """The one-kernel decode attention against the plain versions of its three steps, at contexts of
     0 keys, around the chunk size of 256, several chunks, and with more chunks launched than needed;
     run twice on the same buffers (the ticket counters must come back to zero)."""
     o = ops()
+    o.USE_TMA_ATTENTION = tma          # (head size 64 and pages of 8..64 positions go through TMA; the rest does not)
     dtype = torch.bfloat16
     g = torch.Generator().manual_seed(40)
     ctx = [0, 1, 254, 255, 256, 257, 700, 63, 1029]
@@ -425,3 +428,39 @@ def test_fused_decode_attention(Hq, Hkv, D, ps, window, rot, qk_norm):
     # reading only (a layer that uses another layer's cache): the pages already hold the new position
     got = o.decode_attention_fused(qkv, qw, kw, 1e-5, rot, 10000.0, step, vb, Hq, Hkv, D, D ** -0.5, window, False)
     assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+    o.USE_TMA_ATTENTION = True
+    assert o.tc_status() == 0
+
+
+@pytest.mark.parametrize("ps", [16, 64])
+def test_tma_decode_attention_long_contexts_repeat(ps):
+    """Contexts of thousands of keys, so that every block's ring of stages goes round many times, on
+    a pool larger than L2 so that loads land late and out of order; repeated launches must give the
+    same bits each time, agree with the kernel that loads with plain copies, and never give up a wait."""
+    o = ops()
+    dtype = torch.bfloat16
+    Hq, Hkv, D = 16, 8, 64
+    g = torch.Generator().manual_seed(52)
+    ctx = [4000 - 37 * i for i in range(32)]
+    B = len(ctx)
+    num_pages = (B * 4096) // ps + 1
+    step = make_step(o, dtype, ctx, [1] * B, ps, num_pages, 53)
+    pages = fill_pages(step, ctx, [0] * B, ps, Hkv, D, dtype, num_pages, g)
+    qkv = torch.randn(B, (Hq + 2 * Hkv) * D, generator=g).to(dtype).cuda()
+    qw = (1 + 0.1 * torch.randn(D, generator=g)).cuda()
+    kw = (1 + 0.1 * torch.randn(D, generator=g)).cuda()
+    view = CacheView(0, pages, step.block_tables[0], ps)
+    step.max_kv_len = 4096
+    o.USE_TMA_ATTENTION = False
+    want = o.decode_attention_fused(qkv, qw, kw, 1e-5, D, 10000.0, step, view, Hq, Hkv, D, D ** -0.5, None, True)
+    o.USE_TMA_ATTENTION = True
+    flush = torch.empty(160 * 2 ** 20, dtype=torch.uint8, device="cuda")
+    first = None
+    for rep in range(40):
+        flush.fill_(rep)
+        got = o.decode_attention_fused(qkv, qw, kw, 1e-5, D, 10000.0, step, view, Hq, Hkv, D, D ** -0.5, None, True)
+        if first is None:
+            first = got.clone()
+            assert torch.allclose(got.float(), want.float(), atol=2e-3, rtol=2e-2)
+        assert torch.equal(got, first), rep
+    assert o.tc_status() == 0

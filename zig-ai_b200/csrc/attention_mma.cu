@@ -22,6 +22,7 @@
 // row's sums are formed in the same order however the request was cut into steps and whatever
 // else is in the batch.  Pages: [num_pages, 2, Hkv, page_size, D].
 #include "common.cuh"
+#include "mma_helpers.cuh"
 
 #define TILE 64              // keys per tile, query rows per prefill block
 #define CHUNK 256            // keys per decode block
@@ -29,34 +30,6 @@
 #ifndef ZAI_DECODE_STAGES
 #define ZAI_DECODE_STAGES 2
 #endif
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
-    const int bytes = valid ? 16 : 0;        // 0: the 16 bytes are filled with zeros
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(smem)), "l"(gmem), "r"(bytes));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
-
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
-}
-// d += a (16x16, row) * b (16x8, col)
-__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
 
 // Rows t0 .. t0+63 of the keys (kv = 0) or values (kv = 1) of one head into shared memory, row
 // stride D + 8 elements; rows outside [kstart, kend) are filled with zeros.  `page_shift` is
@@ -531,33 +504,6 @@ struct FusedDecodeArgs {
     int qkv_cols, rot, table_width, page_size, Hq, Hkv, window, write_kv;
     int chunk_keys;            // keys per block: a multiple of 64
 };
-
-// one head row: RMSNorm (if gamma) and rotation of the first `rot` dims; `tmp` holds D floats
-template <int D>
-__device__ __forceinline__ void norm_rotate_row(const bf16* __restrict__ raw, const float* __restrict__ gamma, float eps,
-                                                const float2* __restrict__ cs, int rot, float* tmp, bf16* dst, int lane) {
-    float ss = 0.f;
-    for (int d = lane; d < D; d += 32) {
-        const float v = __bfloat162float(raw[d]);
-        tmp[d] = v;
-        ss += v * v;
-    }
-    if (gamma) {
-        ss = warp_sum(ss);
-        const float inv = rsqrtf(ss / (float)D + eps);
-        for (int d = lane; d < D; d += 32) tmp[d] = tmp[d] * inv * gamma[d];
-    }
-    __syncwarp();
-    const int half = rot >> 1;
-    for (int d = lane; d < D; d += 32) {
-        float v;
-        if (d < half) { const float2 c = cs[d]; v = tmp[d] * c.x - tmp[d + half] * c.y; }
-        else if (d < rot) { const float2 c = cs[d - half]; v = tmp[d - half] * c.y + tmp[d] * c.x; }
-        else v = tmp[d];
-        dst[d] = __float2bfloat16_rn(v);
-    }
-    __syncwarp();
-}
 
 template <int D>
 __global__ void __launch_bounds__(NTHREADS) decode_fused_kernel(const FusedDecodeArgs a) {

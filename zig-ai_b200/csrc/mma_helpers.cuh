@@ -1,0 +1,62 @@
+// Small device helpers shared by the tensor-core attention kernels: asynchronous copies,
+// ldmatrix, mma.sync m16n8k16 (bfloat16 operands, 32-bit accumulation) and the per-head
+// RMSNorm + rotation of one row.
+#pragma once
+#include "common.cuh"
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+    const int bytes = valid ? 16 : 0;        // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(smem)), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+// d += a (16x16, row) * b (16x8, col)
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+
+// one head row: RMSNorm (if gamma) and rotation of the first `rot` dims; `tmp` holds D floats
+template <int D>
+__device__ __forceinline__ void norm_rotate_row(const bf16* __restrict__ raw, const float* __restrict__ gamma, float eps,
+                                                const float2* __restrict__ cs, int rot, float* tmp, bf16* dst, int lane) {
+    float ss = 0.f;
+    for (int d = lane; d < D; d += 32) {
+        const float v = __bfloat162float(raw[d]);
+        tmp[d] = v;
+        ss += v * v;
+    }
+    if (gamma) {
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)D + eps);
+        for (int d = lane; d < D; d += 32) tmp[d] = tmp[d] * inv * gamma[d];
+    }
+    __syncwarp();
+    const int half = rot >> 1;
+    for (int d = lane; d < D; d += 32) {
+        float v;
+        if (d < half) { const float2 c = cs[d]; v = tmp[d] * c.x - tmp[d + half] * c.y; }
+        else if (d < rot) { const float2 c = cs[d - half]; v = tmp[d - half] * c.y + tmp[d] * c.x; }
+        else v = tmp[d];
+        dst[d] = __float2bfloat16_rn(v);
+    }
+    __syncwarp();
+}
+

@@ -21,7 +21,7 @@ from .scheduler import Request, Scheduler, StepPlan
 
 class Engine:
     def __init__(self, model_dir: str, dtype="bfloat16", max_num_seqs: int = 64, max_batched_tokens: int = 2048,
-                 max_model_len: Optional[int] = None, max_tokens: Optional[int] = None, page_size: int = 16,
+                 max_model_len: Optional[int] = None, max_tokens: Optional[int] = None, page_size: int = 64,
                  device=None, ops=None):
         """`max_tokens`: positions the cache pool holds in all (default: room for `max_num_seqs`
         requests of `max_model_len`, capped at 1 Mi positions)."""

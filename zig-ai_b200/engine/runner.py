@@ -159,7 +159,7 @@ class ModelRunner:
 
 
 def load_runner(model_dir: str, dtype="bfloat16", max_tokens: int = 4096, max_requests: int = 64,
-                page_size: int = 16, device=None, ops=None, graphs: bool = True,
+                page_size: int = 64, device=None, ops=None, graphs: bool = True,
                 max_positions: Optional[int] = None) -> ModelRunner:
     """Read config.json, build the model its architecture names, load the tensors and make a cache
     for `max_tokens` positions."""

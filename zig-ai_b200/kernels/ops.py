@@ -57,6 +57,11 @@ _SIGNATURES = {
         "zai_gemm_tc_supports": [_I, _I, _I, _I],
         "zai_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
     },
+    "attention_tma": {
+        "zai_decode_attention_tma_supports": [_I, _I, _I, _I],
+        "zai_decode_attention_tma": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _F, _P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I,
+                                     _I, _F, _I, _I, _I, _P],
+    },
     "sampling": {
         "zai_argmax": [_P, _P, _I, _I, _P],
         "zai_repetition_penalty": [_P, _P, _P, _P, _P, _I, _I, _P],
@@ -102,7 +107,7 @@ def require() -> None:
     if not torch.cuda.is_available():
         raise KernelError("no CUDA device: this engine has no CPU path")
     build.build_all(verbose=True)            # whatever is missing or out of date, several at a time
-    for lib in ("embed", "norm", "activation", "shortconv", "rope_kv", "attention", "attention_mma", "decode_gemm", "gemm_tc", "sampling"):
+    for lib in ("embed", "norm", "activation", "shortconv", "rope_kv", "attention", "attention_mma", "attention_tma", "decode_gemm", "gemm_tc", "sampling"):
         build.load(lib)
 
 
@@ -396,6 +401,7 @@ def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=Non
 
 
 _tickets = {}
+USE_TMA_ATTENTION = os.environ.get("ZAI_TMA_ATTENTION", "1") == "1"   # keys and values by TMA where the sizes allow
 DECODE_BLOCKS_WANTED = 1500      # about two waves of five blocks per SM
 
 
@@ -428,6 +434,16 @@ def decode_attention_fused(qkv, q_w, k_w, eps, rotary_dim, theta, step, cache, h
         _tickets[str(dev)] = tickets
     table = rope_table(step, rotary_dim, theta, dev) if rotary_dim else None
     bt = cache.block_table
+    if USE_TMA_ATTENTION and _fn("attention_tma", "zai_decode_attention_tma_supports")(head_dim, heads, kv_heads, cache.page_size):
+        global _tc_status
+        if _tc_status is None:
+            _tc_status = torch.zeros(1, dtype=torch.int32, device=dev)
+        _check(_fn("attention_tma", "zai_decode_attention_tma")(
+            _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(tickets), _ptr(_tc_status), _ptr(qkv), cols, _ptr(q_w), _ptr(k_w),
+            float(eps), _ptr(table), int(rotary_dim), _ptr(cache.pages), cache.pages.shape[0], _ptr(bt), bt.shape[1],
+            _ptr(step.positions), B, n_chunks, cache.page_size, heads, kv_heads, head_dim, float(scale), int(window or 0),
+            int(bool(write)), chunk, _stream()), "decode_attention_tma")
+        return out
     _check(_fn("attention_mma", "zai_decode_attention_fused")(
         _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(tickets), _ptr(qkv), cols, _ptr(q_w), _ptr(k_w), float(eps),
         _ptr(table), int(rotary_dim), _ptr(cache.pages), _ptr(bt), bt.shape[1], _ptr(step.positions), B, n_chunks,
