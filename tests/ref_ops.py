@@ -75,6 +75,10 @@ def short_conv(bcx, conv_w, conv_b, state, step, taps, write_state=True):
     return out
 
 
+def linear_short_conv(x, w_in, conv_w, conv_b, state, step, taps, write_state=True):
+    return short_conv(linear(x, w_in), conv_w, conv_b, state, step, taps, write_state)
+
+
 def _rms(x, w, eps):
     ms = (x * x).mean(dim=-1, keepdim=True)
     y = x * torch.rsqrt(ms + eps)

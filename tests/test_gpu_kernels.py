@@ -340,6 +340,60 @@ def test_skinny_gemm_with_norm_residual_and_gathered_rows(M, O, K, eps):
     assert torch.equal(lazy.residual.data, h)
 
 
+@pytest.mark.parametrize("M", [1, 5, 8, 13, 16])
+@pytest.mark.parametrize("C,K,taps,bias,norm", [(1024, 1024, 3, False, True), (96, 96, 3, True, True), (100, 64, 4, True, False),
+                                                (517, 1000, 2, False, True), (72, 40, 1, True, False)])
+def test_projection_with_short_conv_epilogue(M, C, K, taps, bias, norm):
+    """The short convolution's input projection with gates, taps and state update as its epilogue,
+    against the product followed by the plain convolution; the slots of the rows are not in order and
+    one state row more than needed is kept; with and without writing the state back."""
+    o = ops()
+    g = torch.Generator().manual_seed(23)
+    w_in = (torch.randn(3 * C, K, generator=g) * K ** -0.5).to(torch.bfloat16).cuda()
+    conv_w = torch.randn(C, taps, generator=g).cuda()
+    conv_b = torch.randn(C, generator=g).cuda() if bias else None
+    slots = [3 * i + 2 for i in range(M)]
+    slots.reverse()
+    state0 = torch.randn(3 * M + 4, taps, C, generator=g).cuda()
+    step = make_step(o, torch.bfloat16, [7 + i for i in range(M)], [1] * M, 16, 64, 24, slots=slots)
+    h = (torch.randn(M, K, generator=g) * 2).cuda()
+    delta = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    gamma = (1 + 0.1 * torch.randn(K, generator=g)).cuda()
+    xb = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    for write in (False, True):
+        # the projections with the kernel's own rounding points: x = bf16((h + delta) gamma), the row's
+        # 1/rms applied to the 32-bit sums, B, C and x~ rounded to bfloat16 as when they are stored
+        if norm:
+            hsum = h + delta.float()
+            xin = (hsum * gamma).to(torch.bfloat16)
+            inv = torch.rsqrt((hsum * hsum).mean(-1, keepdim=True) + 1e-5)
+        else:
+            xin, inv = xb, 1.0
+        bcx = ((xin.float() @ w_in.float().t()) * inv).to(torch.bfloat16)
+        st_want = state0.clone()
+        want = ref_ops.short_conv(bcx, conv_w, conv_b, st_want, step, taps, write)
+        # the size of what is summed (the sum itself may cancel): |C| (|b| + sum |w_j s_j| + |w_last B x~|)
+        Bf, Cf, Xf = bcx[:, :C].float(), bcx[:, C:2 * C].float(), bcx[:, 2 * C:].float()
+        hist = state0[torch.tensor(slots, device="cuda")][:, :taps - 1]                       # [M, taps-1, C]
+        size = (hist * conv_w.t()[None, :taps - 1]).abs().sum(1) + (conv_w[:, taps - 1][None] * Bf * Xf).abs()
+        if bias:
+            size = size + conv_b.abs()[None]
+        size = Cf.abs() * size
+        st_got = state0.clone()
+        lazy = _lazy(h.clone(), delta, gamma, 1e-5) if norm else None
+        before = o.launches
+        got = o.linear_short_conv(lazy if norm else xb, w_in, conv_w, conv_b, st_got, step, taps, write)
+        assert o.launches == before + 1                    # one kernel
+        # B, C, x~ and z are each rounded to bfloat16 from 32-bit sums that may differ in their last
+        # bits (another order of summation): a few steps of 2^-8 of what is summed
+        assert ((got.float() - want.float()).abs() <= 2 ** -6 * size + 1e-3).all()
+        assert torch.allclose(st_got, st_want, atol=1e-3, rtol=2 ** -6)
+        if not write:
+            assert torch.equal(st_got, state0)
+        if norm:
+            assert torch.equal(lazy.residual.data, h + delta.float())
+
+
 # ----------------------------------------------------------------------------- many-rows products (tcgen05)
 def _tc_call(o, y, w, x, epilogue):
     import ctypes

@@ -20,7 +20,10 @@
 
 #define TT_D 64
 #define TT_TILE 64
+#ifndef TT_CONSUMERS
 #define TT_CONSUMERS 4
+#endif
+#define TT_STAGES 4          // a multiple of the consumer warps: a stage always belongs to the same warp
 #define TT_THREADS ((TT_CONSUMERS + 1) * 32)
 #define TT_SPIN_LIMIT 4000000
 #define TT_STAGE_BYTES (2 * TT_TILE * TT_D * 2)       // keys then values: 16 KB
@@ -125,8 +128,12 @@ __global__ void __launch_bounds__(TT_THREADS) decode_tma_kernel(const __grid_con
     }
     __syncthreads();
     pdl_trigger();
-    pdl_wait();
+    // The producer warp reads only what no kernel of this step writes before it (positions, block
+    // table, the cached keys and values), so it does not wait for the kernel before this one: its
+    // loads fly while that kernel (the qkv projection) still runs.  The consumers need its result.
+    // (A layer that only reads a cache which another layer wrote earlier in this step waits, too.)
     const int pos = a.positions[b];
+    if (warp != 0 || !a.write_kv) pdl_wait();
     const int kstart = a.window > 0 ? max(pos - a.window + 1, 0) : 0;
     const bool has_new = a.write_kv && chunk == pos / a.chunk_keys;
     const int kend = a.write_kv ? pos : pos + 1;
@@ -184,12 +191,13 @@ __global__ void __launch_bounds__(TT_THREADS) decode_tma_kernel(const __grid_con
             // ---- consumers: first the group's queries, and the new key and value
             const bf16* row = a.qkv + (size_t)b * a.qkv_cols;
             const float2* cs = a.rot ? a.cs_table + (size_t)b * (a.rot >> 1) : nullptr;
+            // the rows to prepare (the group's G queries, then the new key) go round the warps
             for (int r = cw; r < 16; r += TT_CONSUMERS) {
                 if (r < G) norm_rotate_row<D>(row + (size_t)(hk * G + r) * D, a.q_gamma, a.eps, cs, a.rot, tmp + cw * D, sq + r * ST, lane);
                 else for (int d = lane; d < D; d += 32) sq[r * ST + d] = __float2bfloat16_rn(0.f);
             }
-            if (has_new && cw == 0) {
-                norm_rotate_row<D>(row + (size_t)(Hq + hk) * D, a.k_gamma, a.eps, cs, a.rot, tmp, knew, lane);
+            if (has_new && cw == G % TT_CONSUMERS) {
+                norm_rotate_row<D>(row + (size_t)(Hq + hk) * D, a.k_gamma, a.eps, cs, a.rot, tmp + cw * D, knew, lane);
                 const bf16* vraw = row + (size_t)(Hq + Hkv + hk) * D;
                 const int page = table[pos >> a.page_shift], off = pos & (ps - 1);
                 const size_t page_stride = (size_t)2 * Hkv * ps * D;
@@ -203,6 +211,7 @@ __global__ void __launch_bounds__(TT_THREADS) decode_tma_kernel(const __grid_con
                 }
             }
             asm volatile("bar.sync 1, %0;" ::"n"(TT_CONSUMERS * 32) : "memory");      // the four consumer warps
+            zai_mark(1);
             uint32_t qf[D / 16][4];
             {
                 const int r = (((lane >> 3) & 1) << 3) + (lane & 7);
@@ -279,7 +288,9 @@ __global__ void __launch_bounds__(TT_THREADS) decode_tma_kernel(const __grid_con
             }
             // every consumer is done with the ring (its first stages are reused for the partial sums
             // below), and snew, vnew are visible to the first consumer
+            zai_mark(2);
             asm volatile("bar.sync 1, %0;" ::"n"(TT_CONSUMERS * 32) : "memory");
+            zai_mark(3);
             if (has_new && cw == 0) {                                          // fold the new key into this warp's sums
                 const float s0 = snew[g], s1 = snew[g + 8];
                 const float n0 = fmaxf(m0, s0), n1 = fmaxf(m1, s1);
@@ -350,6 +361,7 @@ __global__ void __launch_bounds__(TT_THREADS) decode_tma_kernel(const __grid_con
     if (tid == 0 && failed_flag) atomicExch(a.status, 1);
 
     // ---- the last block of this (request, key/value head) combines the chunks
+    zai_mark(4);
     __threadfence();
     __syncthreads();
     if (tid == 0) s_ticket = atomicAdd(&a.tickets[b * Hkv + hk], 1);
@@ -435,7 +447,8 @@ ZAI_API int zai_decode_attention_tma(void* out, float* part_o, float* part_ml, i
     // stage count that the warps do not divide, the warp that reads a stage's next round could test
     // the barrier while the round before is still in flight, and a parity test cannot tell "two
     // phases behind" from "done".
-    a.stages = tiles < TT_CONSUMERS ? (tiles < 2 ? 2 : tiles) : TT_CONSUMERS;
+    static_assert(TT_STAGES % TT_CONSUMERS == 0, "a stage must always be read by the same warp");
+    a.stages = tiles < TT_STAGES ? (tiles < 2 ? 2 : tiles) : TT_STAGES;
     const size_t tail = (size_t)16 * (TT_D + 8) * 2 + (size_t)4 * TT_D * 4 + (size_t)2 * TT_D * 2 + 16 * 4;
     const size_t smem = 1024 + (size_t)a.stages * TT_STAGE_BYTES + tail;
     static size_t configured = 0;

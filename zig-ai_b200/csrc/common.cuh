@@ -54,8 +54,72 @@ static inline int launch_status() { return (int)cudaGetLastError(); }
 // write); what it does before that (address arithmetic, loads of weights) overlaps the predecessor.
 // pdl_trigger() lets the kernel after this one begin its own start-up.  Both are no-ops in a kernel
 // launched the ordinary way.  ZAI_PDL=0 in the environment launches everything the ordinary way.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+//
+// Built with -DZAI_TIMELINE (ZAI_TIMELINE=1 in the environment when the libraries are built), the
+// last thread of every kernel's first block notes the global timer before and after the wait, so a
+// step's kernels can be laid out on one time axis without a profiler's serialisation:
+// zai_timeline_read() returns the records (tag of the library, time at the wait, time after it).
+#ifdef ZAI_TIMELINE
+#ifndef ZAI_TIMELINE_TAG
+#define ZAI_TIMELINE_TAG 0
+#endif
+#define ZAI_TIMELINE_RECORDS 16384
+static __device__ unsigned long long zai_tl_records[ZAI_TIMELINE_RECORDS * 2];
+static __device__ unsigned int zai_tl_count;
+__device__ __forceinline__ unsigned long long zai_global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#endif
+__device__ __forceinline__ void pdl_wait() {
+#ifdef ZAI_TIMELINE
+    const bool rec = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == blockDim.x - 1 && threadIdx.y == 0;
+    unsigned long long t0 = 0;
+    if (rec) t0 = zai_global_ns();
+#endif
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+#ifdef ZAI_TIMELINE
+    if (rec) {
+        const unsigned long long t1 = zai_global_ns();
+        const unsigned int i = atomicAdd(&zai_tl_count, 1u);
+        if (i < ZAI_TIMELINE_RECORDS) {
+            zai_tl_records[2 * i] = t0;
+            zai_tl_records[2 * i + 1] = t1;
+        }
+    }
+#endif
+}
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// A further point on the time axis from inside a kernel (same thread as above); a record with both
+// times equal and `id` in the low byte of the first.  Compiles to nothing without ZAI_TIMELINE.
+__device__ __forceinline__ void zai_mark(int id) {
+#ifdef ZAI_TIMELINE
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == blockDim.x - 1 && threadIdx.y == 0) {
+        const unsigned long long t = zai_global_ns();
+        const unsigned int i = atomicAdd(&zai_tl_count, 1u);
+        if (i < ZAI_TIMELINE_RECORDS) {
+            zai_tl_records[2 * i] = (unsigned long long)(id & 255) | (1ull << 63);
+            zai_tl_records[2 * i + 1] = t;
+        }
+    }
+#else
+    (void)id;
+#endif
+}
+#ifdef ZAI_TIMELINE
+// Copies up to `max_records` (t_wait, t_after) pairs to `out` and empties the list; returns how many.
+ZAI_API int zai_timeline_read(unsigned long long* out, int max_records) {
+    unsigned int n = 0;
+    if (cudaMemcpyFromSymbol(&n, zai_tl_count, sizeof(n)) != cudaSuccess) return -1;
+    if (n > ZAI_TIMELINE_RECORDS) n = ZAI_TIMELINE_RECORDS;
+    if ((int)n > max_records) n = (unsigned int)max_records;
+    if (n && cudaMemcpyFromSymbol(out, zai_tl_records, (size_t)n * 2 * sizeof(unsigned long long)) != cudaSuccess) return -1;
+    const unsigned int zero = 0;
+    cudaMemcpyToSymbol(zai_tl_count, &zero, sizeof(zero));
+    return (int)n;
+}
+#endif
 
 #include <stdlib.h>
 static inline bool pdl_enabled() {

@@ -6,7 +6,9 @@
 //            32-bit sum h + delta is also written out as the new residual stream), optionally on
 //            gathered rows;  or x given in bfloat16
 //   after:   bfloat16 store;  32-bit store (logits);  SwiGLU  a = silu(gate) * up  on a stacked
-//            gate|up matrix (rows f and F + f are computed by the same warp)
+//            gate|up matrix (rows f and F + f are computed by the same warp);  the short convolution's
+//            gates, taps and state update on a stacked B|C|x matrix (rows c, H + c and 2H + c are
+//            computed by the same warp; formulas src/cuda/layer_kernels.cu:206-221)
 //
 // The reference runs a decode token's projections as cublasSgemm with M = 1 and separate norm,
 // residual and activation kernels (src/transformer/hybrid_layer.zig:607-672; formulas
@@ -18,11 +20,13 @@
 // row come from shared memory with the same lane mapping, so no shuffles are needed (the order of
 // k inside a 32-k block is permuted identically for both operands).  A block's warps split K
 // between them and add their partial sums through shared memory in a fixed order.
+#include <cstdlib>
 #include "common.cuh"
 
 #define SG_WARPS 8
 
-enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2 };
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_CONV = 3 };
+#define SG_CONV_TAPS 4        // the fused convolution takes up to this many taps
 
 struct SkinnyArgs {
     const bf16* W;        // [O, K]
@@ -37,10 +41,18 @@ struct SkinnyArgs {
     int M, O, K, ldy;
     int F;                // SwiGLU: gate rows 0..F-1, up rows F..2F-1 (O = 2F)
     int n_tiles, tpc, sk; // tiles of 16 weight rows; tiles per unit; K slices per tile
+    int half_tiles;       // 1: a tile is 8 weight rows (the other 8 rows of the instruction are zeros), for more units
     int units;            // work units (tpc tiles each), taken round robin by the blocks
     int ring_rounds;      // rounds (of four 32-k blocks) of weights each warp keeps in flight
     int red_offset;       // byte offset of the cross-warp sum buffer in shared memory (after x)
     int ring_offset;      // byte offset of the weight rings (after the sum buffer)
+    // convolution epilogue (O = 3F: B rows, C rows, x rows of F channels each)
+    const float* conv_w;  // [F, taps]
+    const float* conv_b;  // [F] or null
+    float* conv_state;    // [slots, state_rows, F]
+    const int* slot_ids;  // [M]
+    int taps, state_rows, write_state;
+    int l2_prefetch_bytes; // how much of its weight rows a block asks into L2 before it waits for the kernel before it
 };
 
 __device__ __forceinline__ void cp_async16_zfill(void* smem, const void* gmem, bool valid) {
@@ -79,6 +91,7 @@ __global__ void __launch_bounds__(SG_WARPS * 32, 2) skinny_gemm_kernel(const Ski
     const int K = a.K, XS = K + 8;
     float* inv_s = reinterpret_cast<float*>(smem_raw);        // [8*MT] 1/rms of each row (64 floats reserved)
     bf16* xs = reinterpret_cast<bf16*>(smem_raw + 256);      // [8*MT][K + 8]
+    float* gs = reinterpret_cast<float*>(smem_raw + 256 + (size_t)8 * MT * XS * sizeof(bf16));   // [K] the norm's weight
     float* red = reinterpret_cast<float*>(smem_raw + a.red_offset);   // [warps][MT*4][32]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -92,12 +105,24 @@ __global__ void __launch_bounds__(SG_WARPS * 32, 2) skinny_gemm_kernel(const Ski
     const int n_units = ((int)a.units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
     const int total_rounds = n_units * rpu;
     const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
-    auto rows_of = [&](int unit_index, int& row_lo, int& row_hi) {
+    // weight rows of the lane: (row_lo, row_hi) are rows g and g + 8 of the 16-row operand.  The
+    // convolution has two such operands per tile of 8 channels: j = 0: B and C of channel c0 + g;
+    // j = 1: x of channel c0 + g (its other 8 rows are zeros).
+    auto rows_of = [&](int unit_index, int j, int& row_lo, int& row_hi) {
         const int tile = (blockIdx.x + unit_index * gridDim.x) * a.tpc + tile_in_unit;
-        if (EPI == EPI_SWIGLU) {
+        if (EPI == EPI_CONV) {
+            const int ch = tile * 8 + g;
+            const bool v = tile < a.n_tiles && ch < a.F;
+            if (j == 0) { row_lo = v ? ch : -1; row_hi = v ? a.F + ch : -1; }
+            else { row_lo = v ? 2 * a.F + ch : -1; row_hi = -1; }
+        } else if (EPI == EPI_SWIGLU) {
             row_lo = tile * 8 + g;
             row_hi = a.F + tile * 8 + g;
             if (tile >= a.n_tiles || row_lo >= a.F) { row_lo = -1; row_hi = -1; }
+        } else if (a.half_tiles) {
+            row_lo = tile * 8 + g;
+            row_hi = -1;
+            if (tile >= a.n_tiles || row_lo >= a.O) row_lo = -1;
         } else {
             row_lo = tile * 16 + g;
             row_hi = row_lo + 8;
@@ -112,23 +137,27 @@ __global__ void __launch_bounds__(SG_WARPS * 32, 2) skinny_gemm_kernel(const Ski
     // Without the norm, x needs no staging: each lane's fragments of the token rows travel through
     // the same ring, right behind the weights of their block (they depend on the kernel before this
     // one, so they are issued after the wait; every warp loads only its own K slice of x).
-    constexpr int SLOT = (2 + (NORM ? 0 : MT)) * 512;       // bytes of one 32-k block in a warp's ring
+    constexpr int NT = EPI == EPI_CONV ? 2 : 1;             // 16-row operands per tile
+    constexpr int SLOT = (2 * NT + (NORM ? 0 : MT)) * 512;  // bytes of one 32-k block in a warp's ring
     const int ring_rounds = a.ring_rounds;
     unsigned char* ring = smem_raw + a.ring_offset + (size_t)warp * ring_rounds * 4 * SLOT;
     auto issue_w = [&](int r) {
         if (r < total_rounds) {
-            int row_lo, row_hi;
-            rows_of(r / rpu, row_lo, row_hi);
-            const bf16* w_lo = a.W + (size_t)(row_lo < 0 ? 0 : row_lo) * K + 8 * t;
-            const bf16* w_hi = a.W + (size_t)(row_hi < 0 ? 0 : row_hi) * K + 8 * t;
-            const int kb = kb0 + (r % rpu) * 4;
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int k0 = (kb + u) << 5;
-                const bool ok = (kb + u) < kb1 && k0 + 8 * t < K;   // past the slice or past K: zeros
-                unsigned char* slot = ring + (size_t)((r % ring_rounds) * 4 + u) * SLOT + lane * 16;
-                cp_async16_zfill(slot, w_lo + k0, ok && row_lo >= 0);
-                cp_async16_zfill(slot + 512, w_hi + k0, ok && row_hi >= 0);
+            for (int j = 0; j < NT; ++j) {
+                int row_lo, row_hi;
+                rows_of(r / rpu, j, row_lo, row_hi);
+                const bf16* w_lo = a.W + (size_t)(row_lo < 0 ? 0 : row_lo) * K + 8 * t;
+                const bf16* w_hi = a.W + (size_t)(row_hi < 0 ? 0 : row_hi) * K + 8 * t;
+                const int kb = kb0 + (r % rpu) * 4;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int k0 = (kb + u) << 5;
+                    const bool ok = (kb + u) < kb1 && k0 + 8 * t < K;   // past the slice or past K: zeros
+                    unsigned char* slot = ring + (size_t)((r % ring_rounds) * 4 + u) * SLOT + j * 1024 + lane * 16;
+                    cp_async16_zfill(slot, w_lo + k0, ok && row_lo >= 0);
+                    cp_async16_zfill(slot + 512, w_hi + k0, ok && row_hi >= 0);
+                }
             }
         }
     };
@@ -139,7 +168,7 @@ __global__ void __launch_bounds__(SG_WARPS * 32, 2) skinny_gemm_kernel(const Ski
             for (int u = 0; u < 4; ++u) {
                 const int k0 = (kb + u) << 5;
                 const bool ok = (kb + u) < kb1 && k0 + 8 * t < K;
-                unsigned char* slot = ring + (size_t)((r % ring_rounds) * 4 + u) * SLOT + 1024 + lane * 16;
+                unsigned char* slot = ring + (size_t)((r % ring_rounds) * 4 + u) * SLOT + NT * 1024 + lane * 16;
 #pragma unroll
                 for (int nt = 0; nt < MT; ++nt) {
                     const int m = nt * 8 + g;
@@ -152,8 +181,69 @@ __global__ void __launch_bounds__(SG_WARPS * 32, 2) skinny_gemm_kernel(const Ski
         issue_w(r);
         cp_async_commit_group();
     }
+    // The rest of this block's weight rows are asked into L2 now: this kernel's blocks become resident
+    // while the kernel before it on the stream still runs, so the rows arrive from memory meanwhile
+    // and the products below find them in L2.
+    if (warp == 0 && EPI != EPI_CONV) {
+        size_t budget = (size_t)a.l2_prefetch_bytes;
+        for (int u = 0; u < n_units && budget > 0; ++u) {
+            const int tile_first = (blockIdx.x + u * gridDim.x) * a.tpc;
+            const int rows_per_tile = (EPI == EPI_SWIGLU || a.half_tiles) ? 8 : 16;
+            const int row0 = tile_first * rows_per_tile;
+            const int limit = EPI == EPI_SWIGLU ? a.F : a.O;
+            const int nrows = min(limit, row0 + a.tpc * rows_per_tile) - row0;
+            if (nrows <= 0) break;
+            size_t bytes = (size_t)nrows * K * sizeof(bf16);
+            if (bytes > budget) bytes = budget & ~(size_t)15;
+            budget -= bytes;
+            for (int half = 0; half < (EPI == EPI_SWIGLU ? 2 : 1); ++half) {
+                const unsigned char* base = reinterpret_cast<const unsigned char*>(a.W + ((size_t)row0 + (size_t)half * a.F) * K);
+                for (size_t off = (size_t)lane * 4096; off < bytes; off += (size_t)32 * 4096) {
+                    const uint32_t n = (uint32_t)min((size_t)4096, bytes - off);
+                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + off), "r"(n) : "memory");
+                }
+            }
+        }
+    }
+    // ---- the convolution's inputs of a unit (state, taps, bias of the lane's channel and tokens) are
+    // asked for at the start of the unit and used in its epilogue, so their way from memory is hidden
+    // behind the product (after the wait: the kernel before this one may have written the state)
+    float cv_prev[EPI == EPI_CONV ? MT : 1][2][SG_CONV_TAPS - 1], cv_w[SG_CONV_TAPS], cv_b = 0.f;
+    int cv_slot[EPI == EPI_CONV ? MT : 1][2];
+    auto conv_inputs = [&](int unit) {
+        if (EPI != EPI_CONV || kslice != 0) return;
+        const int tile = (blockIdx.x + unit * gridDim.x) * a.tpc + tile_in_unit;
+        const int ch = tile * 8 + g;
+        const bool vc = tile < a.n_tiles && ch < a.F;
+        cv_b = (vc && a.conv_b) ? a.conv_b[ch] : 0.f;
+#pragma unroll
+        for (int j = 0; j < SG_CONV_TAPS; ++j) cv_w[j] = (vc && j < a.taps) ? a.conv_w[(size_t)ch * a.taps + j] : 0.f;
+#pragma unroll
+        for (int nt = 0; nt < (EPI == EPI_CONV ? MT : 1); ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int tok = nt * 8 + 2 * t + e;
+                cv_slot[nt][e] = tok < a.M ? a.slot_ids[tok] : 0;
+#pragma unroll
+                for (int j = 0; j < SG_CONV_TAPS - 1; ++j)
+                    cv_prev[nt][e][j] = (vc && tok < a.M && j < a.taps - 1)
+                        ? a.conv_state[((size_t)cv_slot[nt][e] * a.state_rows + j) * a.F + ch] : 0.f;
+            }
+    };
+    // the norm's weight and the rows' source indices are written by no kernel of the step: they are
+    // fetched before the wait, the weight into shared memory
+    int src_row0 = warp, src_row1 = warp + SG_WARPS;
+    if (NORM) {
+        for (int k = tid * 4; k < K; k += SG_WARPS * 32 * 4) *reinterpret_cast<float4*>(gs + k) = *reinterpret_cast<const float4*>(a.gamma + k);
+        if (a.row_idx) {
+            if (src_row0 < a.M) src_row0 = a.row_idx[src_row0];
+            if (src_row1 < a.M) src_row1 = a.row_idx[src_row1];
+        }
+    }
     pdl_trigger();
     pdl_wait();
+    if (n_units > 0) conv_inputs(0);                         // asked for now, used in the epilogue
+    if (NORM) __syncthreads();                               // gs is complete
     if (!NORM) {
         for (int r = 0; r < ring_rounds; ++r) issue_x(r);
         cp_async_commit_group();
@@ -161,6 +251,8 @@ __global__ void __launch_bounds__(SG_WARPS * 32, 2) skinny_gemm_kernel(const Ski
 
     // ---- x into shared memory, once per block.  With the norm, x = (h + delta) * gamma rounded to
     // bfloat16; the row's factor rsqrt(mean((h + delta)^2) + eps) is applied to the sums afterwards.
+    // A warp takes a row; a lane asks for up to eight 16-byte pieces of h and of delta before it uses
+    // the first, so a row of up to 1024 values costs one trip to memory.
     if (NORM) {
         for (int m = warp; m < 8 * MT; m += SG_WARPS) {
             bf16* dst = xs + (size_t)m * XS;
@@ -169,25 +261,25 @@ __global__ void __launch_bounds__(SG_WARPS * 32, 2) skinny_gemm_kernel(const Ski
                 if (lane == 0) inv_s[m] = 0.f;
                 continue;
             }
-            const size_t src = (size_t)(a.row_idx ? a.row_idx[m] : m) * K;
+            const size_t src = (size_t)(m < SG_WARPS ? src_row0 : src_row1) * K;
             float ss = 0.f;
-            for (int kq = lane * 4; kq < K; kq += 512) {          // four 128-wide pieces at a time, loads first
-                float4 v[4], gm[4];
-                uint2 d[4];
+            for (int kq = lane * 4; kq < K; kq += 1024) {
+                float4 v[8];
+                uint2 d[8];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < 8; ++u) {
                     const int k = kq + u * 128;
                     if (k < K) {
                         v[u] = *reinterpret_cast<const float4*>(a.h + src + k);
-                        gm[u] = *reinterpret_cast<const float4*>(a.gamma + k);
                         if (a.delta) d[u] = *reinterpret_cast<const uint2*>(a.delta + src + k);
                     }
                 }
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < 8; ++u) {
                     const int k = kq + u * 128;
                     if (k < K) {
                         float4 w = v[u];
+                        const float4 gm = *reinterpret_cast<const float4*>(gs + k);
                         if (a.delta) {
                             const __nv_bfloat162 d0 = *reinterpret_cast<const __nv_bfloat162*>(&d[u].x);
                             const __nv_bfloat162 d1 = *reinterpret_cast<const __nv_bfloat162*>(&d[u].y);
@@ -195,8 +287,8 @@ __global__ void __launch_bounds__(SG_WARPS * 32, 2) skinny_gemm_kernel(const Ski
                         }
                         ss += w.x * w.x + w.y * w.y + w.z * w.z + w.w * w.w;
                         if (a.h_out && blockIdx.x == 0) *reinterpret_cast<float4*>(a.h_out + (size_t)m * K + k) = w;
-                        __nv_bfloat162 o0 = __floats2bfloat162_rn(w.x * gm[u].x, w.y * gm[u].y);
-                        __nv_bfloat162 o1 = __floats2bfloat162_rn(w.z * gm[u].z, w.w * gm[u].w);
+                        __nv_bfloat162 o0 = __floats2bfloat162_rn(w.x * gm.x, w.y * gm.y);
+                        __nv_bfloat162 o1 = __floats2bfloat162_rn(w.z * gm.z, w.w * gm.w);
                         uint2 o;
                         o.x = *reinterpret_cast<uint32_t*>(&o0);
                         o.y = *reinterpret_cast<uint32_t*>(&o1);
@@ -209,6 +301,7 @@ __global__ void __launch_bounds__(SG_WARPS * 32, 2) skinny_gemm_kernel(const Ski
         }
     }
     if (NORM) __syncthreads();
+    zai_mark(1);
     float inv_tok[MT][2];
 #pragma unroll
     for (int nt = 0; nt < MT; ++nt) {
@@ -218,42 +311,74 @@ __global__ void __launch_bounds__(SG_WARPS * 32, 2) skinny_gemm_kernel(const Ski
 
     const bf16* xrow = xs + (size_t)g * XS + 8 * t;
     for (int unit = 0; unit < n_units; ++unit) {
+        if (unit > 0) conv_inputs(unit);
         // ---- the products of this unit's slice: a round's slots are refilled as soon as it is read
-        float c[MT][4];
+        float c[NT][MT][4];
 #pragma unroll
-        for (int i = 0; i < MT; ++i) c[i][0] = c[i][1] = c[i][2] = c[i][3] = 0.f;
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int i = 0; i < MT; ++i) c[j][i][0] = c[j][i][1] = c[j][i][2] = c[j][i][3] = 0.f;
         for (int q = 0; q < rpu; ++q) {
             const int r = unit * rpu + q;
             const int kb = kb0 + q * 4;
             // round r has landed when at most this many later groups are pending (without the norm
             // the group with the first rounds' x sits between the first weights and the steady rounds)
             cp_async_wait_rounds(NORM ? ring_rounds - 1 : min(r, ring_rounds - 1));
-            uint4 wl[4], wh[4], bx[4][MT];
+            if (NT == 1) {
+                uint4 wl[4], wh[4], bx[4][MT];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const unsigned char* slot = ring + (size_t)((r % ring_rounds) * 4 + u) * SLOT + lane * 16;
-                wl[u] = *reinterpret_cast<const uint4*>(slot);
-                wh[u] = *reinterpret_cast<const uint4*>(slot + 512);
-                if (!NORM) {
+                for (int u = 0; u < 4; ++u) {
+                    const unsigned char* slot = ring + (size_t)((r % ring_rounds) * 4 + u) * SLOT + lane * 16;
+                    wl[u] = *reinterpret_cast<const uint4*>(slot);
+                    wh[u] = *reinterpret_cast<const uint4*>(slot + 512);
+                    if (!NORM) {
 #pragma unroll
-                    for (int nt = 0; nt < MT; ++nt) bx[u][nt] = *reinterpret_cast<const uint4*>(slot + 1024 + nt * 512);
+                        for (int nt = 0; nt < MT; ++nt) bx[u][nt] = *reinterpret_cast<const uint4*>(slot + 1024 + nt * 512);
+                    }
                 }
-            }
-            issue_w(r + ring_rounds);
-            issue_x(r + ring_rounds);
-            cp_async_commit_group();                            // one group per round, used or not
+                issue_w(r + ring_rounds);
+                issue_x(r + ring_rounds);
+                cp_async_commit_group();                            // one group per round, used or not
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int k0 = (kb + u) << 5;
-                const bool kin = (kb + u) < kb1 && k0 + 8 * t < K;
+                for (int u = 0; u < 4; ++u) {
+                    const int k0 = (kb + u) << 5;
+                    const bool kin = (kb + u) < kb1 && k0 + 8 * t < K;
 #pragma unroll
-                for (int nt = 0; nt < MT; ++nt) {
-                    uint4 b4;
-                    if (NORM) b4 = kin ? *reinterpret_cast<const uint4*>(xrow + (size_t)nt * 8 * XS + k0) : zero4;
-                    else b4 = bx[u][nt];
-                    mma16816(c[nt], wl[u].x, wh[u].x, wl[u].y, wh[u].y, b4.x, b4.y);
-                    mma16816(c[nt], wl[u].z, wh[u].z, wl[u].w, wh[u].w, b4.z, b4.w);
+                    for (int nt = 0; nt < MT; ++nt) {
+                        uint4 b4;
+                        if (NORM) b4 = kin ? *reinterpret_cast<const uint4*>(xrow + (size_t)nt * 8 * XS + k0) : zero4;
+                        else b4 = bx[u][nt];
+                        mma16816(c[0][nt], wl[u].x, wh[u].x, wl[u].y, wh[u].y, b4.x, b4.y);
+                        mma16816(c[0][nt], wl[u].z, wh[u].z, wl[u].w, wh[u].w, b4.z, b4.w);
+                    }
                 }
+            } else {
+                // two operands per 32-k block: read and multiply block by block, refill afterwards
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const unsigned char* slot = ring + (size_t)((r % ring_rounds) * 4 + u) * SLOT + lane * 16;
+                    const int k0 = (kb + u) << 5;
+                    const bool kin = (kb + u) < kb1 && k0 + 8 * t < K;
+                    uint4 b4[MT];
+#pragma unroll
+                    for (int nt = 0; nt < MT; ++nt) {
+                        if (NORM) b4[nt] = kin ? *reinterpret_cast<const uint4*>(xrow + (size_t)nt * 8 * XS + k0) : zero4;
+                        else b4[nt] = *reinterpret_cast<const uint4*>(slot + NT * 1024 + nt * 512);
+                    }
+#pragma unroll
+                    for (int j = 0; j < NT; ++j) {
+                        const uint4 wl = *reinterpret_cast<const uint4*>(slot + j * 1024);
+                        const uint4 wh = *reinterpret_cast<const uint4*>(slot + j * 1024 + 512);
+#pragma unroll
+                        for (int nt = 0; nt < MT; ++nt) {
+                            mma16816(c[j][nt], wl.x, wh.x, wl.y, wh.y, b4[nt].x, b4[nt].y);
+                            mma16816(c[j][nt], wl.z, wh.z, wl.w, wh.w, b4[nt].z, b4[nt].w);
+                        }
+                    }
+                }
+                issue_w(r + ring_rounds);
+                issue_x(r + ring_rounds);
+                cp_async_commit_group();
             }
         }
         // ---- add the K slices of a tile in a fixed order
@@ -261,30 +386,68 @@ __global__ void __launch_bounds__(SG_WARPS * 32, 2) skinny_gemm_kernel(const Ski
             __syncthreads();                                    // the readers of the last unit are done
             if (kslice > 0) {
 #pragma unroll
-                for (int i = 0; i < MT; ++i)
+                for (int j = 0; j < NT; ++j)
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) red[((size_t)warp * MT * 4 + i * 4 + e) * 32 + lane] = c[i][e];
+                    for (int i = 0; i < MT; ++i)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) red[((size_t)warp * NT * MT * 4 + (j * MT + i) * 4 + e) * 32 + lane] = c[j][i][e];
             }
             __syncthreads();
             if (kslice == 0) {
                 for (int s2 = 1; s2 < a.sk; ++s2)
 #pragma unroll
-                    for (int i = 0; i < MT; ++i)
+                    for (int j = 0; j < NT; ++j)
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) c[i][e] += red[((size_t)(warp + s2) * MT * 4 + i * 4 + e) * 32 + lane];
+                        for (int i = 0; i < MT; ++i)
+#pragma unroll
+                            for (int e = 0; e < 4; ++e)
+                                c[j][i][e] += red[((size_t)(warp + s2) * NT * MT * 4 + (j * MT + i) * 4 + e) * 32 + lane];
             }
         }
         if (kslice != 0) continue;
         // ---- after the product: lane holds rows (g, g+8) x tokens (8 nt + 2t, + 1)
+        if (EPI == EPI_CONV) {
+            const int tile = (blockIdx.x + unit * gridDim.x) * a.tpc + tile_in_unit;
+            const int ch = tile * 8 + g;
+            if (tile >= a.n_tiles || ch >= a.F) continue;
+#pragma unroll
+            for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int tok = nt * 8 + 2 * t + e;
+                    if (tok >= a.M) continue;
+                    const float inv = inv_tok[nt][e];
+                    // the three projections rounded as if stored, then the gated convolution in 32-bit
+                    const float Bv = __bfloat162float(__float2bfloat16_rn(c[0][nt][e] * inv));
+                    const float Cv = __bfloat162float(__float2bfloat16_rn(c[0][nt][2 + e] * inv));
+                    const float Xv = __bfloat162float(__float2bfloat16_rn(c[NT - 1][nt][e] * inv));
+                    const float u = Bv * Xv;
+                    float y = cv_b, w_last = 0.f;
+#pragma unroll
+                    for (int j = 0; j < SG_CONV_TAPS; ++j) {
+                        if (j < a.taps - 1) y += cv_w[j] * cv_prev[nt][e][j < SG_CONV_TAPS - 1 ? j : 0];
+                        if (j == a.taps - 1) w_last = cv_w[j];
+                    }
+                    y += w_last * u;
+                    reinterpret_cast<bf16*>(a.y)[(size_t)tok * a.ldy + ch] = __float2bfloat16_rn(Cv * y);
+                    if (a.write_state) {
+                        float* st = a.conv_state + (size_t)cv_slot[nt][e] * a.state_rows * a.F + ch;
+#pragma unroll
+                        for (int j = 0; j < SG_CONV_TAPS - 1; ++j)
+                            if (j < a.taps - 1) st[(size_t)j * a.F] = (j + 1 < a.taps - 1) ? cv_prev[nt][e][(j + 1) % (SG_CONV_TAPS - 1)] : u;
+                    }
+                }
+            continue;
+        }
         int row_lo, row_hi;
-        rows_of(unit, row_lo, row_hi);
+        rows_of(unit, 0, row_lo, row_hi);
 #pragma unroll
         for (int nt = 0; nt < MT; ++nt) {
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int tok = nt * 8 + 2 * t + e;
                 if (tok >= a.M) continue;
-                const float lo = c[nt][e] * inv_tok[nt][e], hi = c[nt][2 + e] * inv_tok[nt][e];
+                const float lo = c[0][nt][e] * inv_tok[nt][e], hi = c[0][nt][2 + e] * inv_tok[nt][e];
                 if (EPI == EPI_SWIGLU) {
                     if (row_lo >= 0)
                         reinterpret_cast<bf16*>(a.y)[(size_t)tok * a.ldy + row_lo] = __float2bfloat16_rn(lo / (1.f + expf(-lo)) * hi);
@@ -299,6 +462,7 @@ __global__ void __launch_bounds__(SG_WARPS * 32, 2) skinny_gemm_kernel(const Ski
         }
     }
     cp_async_wait_rounds(0);
+    zai_mark(2);
 }
 
 static int sg_sm_count() {
@@ -311,17 +475,28 @@ static int sg_sm_count() {
     }
     return n;
 }
+// Bytes per block asked into L2 ahead of the wait (ZAI_SKINNY_L2_PREFETCH_KB, default 384 KB: with one
+// block per SM about 57 MB, under half of L2)
+static int skinny_l2_prefetch_bytes() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("ZAI_SKINNY_L2_PREFETCH_KB");
+        v = (e ? atoi(e) : 384) * 1024;
+        if (v < 0) v = 0;
+    }
+    return v;
+}
 static size_t skinny_x_bytes(int mt, int K, bool norm) {
     if (!norm) return 1024;                                 // x travels through the rings
-    return (256 + (size_t)8 * mt * (K + 8) * sizeof(bf16) + 1023) / 1024 * 1024;
+    return (256 + (size_t)8 * mt * (K + 8) * sizeof(bf16) + (size_t)K * sizeof(float) + 1023) / 1024 * 1024;
 }
-static size_t skinny_round_bytes(int mt, bool norm) { return (size_t)SG_WARPS * 4 * (2 + (norm ? 0 : mt)) * 512; }
-static size_t skinny_red_bytes(int mt) { return (size_t)SG_WARPS * mt * 4 * 32 * sizeof(float); }
+static size_t skinny_round_bytes(int mt, bool norm, int nt) { return (size_t)SG_WARPS * 4 * (2 * nt + (norm ? 0 : mt)) * 512; }
+static size_t skinny_red_bytes(int mt, int nt) { return (size_t)SG_WARPS * nt * mt * 4 * 32 * sizeof(float); }
 // Rounds per warp in flight: up to 64 KB per block, less when x is large, so that a block stays near
 // 112 KB of shared memory and two kernels' blocks fit on an SM together.
-static int skinny_ring_rounds(int mt, int K, bool norm) {
-    const size_t fixed = skinny_x_bytes(mt, K, norm) + skinny_red_bytes(mt);
-    const size_t round = skinny_round_bytes(mt, norm);
+static int skinny_ring_rounds(int mt, int K, bool norm, int nt) {
+    const size_t fixed = skinny_x_bytes(mt, K, norm) + skinny_red_bytes(mt, nt);
+    const size_t round = skinny_round_bytes(mt, norm, nt);
     const size_t room_half = fixed < (size_t)112 * 1024 ? (size_t)112 * 1024 - fixed : 0;
     const size_t room_full = fixed < (size_t)216 * 1024 ? (size_t)216 * 1024 - fixed : 0;
     int r = (int)(room_half / round);
@@ -330,28 +505,35 @@ static int skinny_ring_rounds(int mt, int K, bool norm) {
     return r;
 }
 
-// How to cut the work: K slices per tile (1, 2, 4 or 8; a slice has at least four 32-k blocks), so that
-// the busiest block has the least to do, counting a fixed cost per unit.
-static void skinny_plan(int n_tiles, int K, int* tpc, int* sk, int* units) {
+// How to cut the work: K slices per tile (1, 2, 4 or 8; a slice has at least four 32-k blocks) and
+// whole tiles (16 weight rows) or half tiles (8 rows, twice as many units, half the bytes per round),
+// so that the busiest block has the least to do, counting a fixed cost per unit.
+static void skinny_plan(int rows, bool may_halve, int K, int* n_tiles, int* half, int* tpc, int* sk, int* units, int rows_per_tile = 16) {
     const int blocks32 = (K + 31) / 32;
-    int best_sk = 1;
     long best_cost = -1;
-    for (int s = 1; s <= SG_WARPS; s *= 2) {
-        const int per = (blocks32 + s - 1) / s;
-        if (s > 1 && per < 4) break;
-        const int u = (n_tiles + SG_WARPS / s - 1) / (SG_WARPS / s);
-        const int waves = (u + sg_sm_count() - 1) / sg_sm_count();
-        const long cost = (long)waves * (((per + 3) / 4) * 4 + 6);
-        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_sk = s; }
+    for (int h = 0; h <= (may_halve ? 1 : 0); ++h) {
+        const int tiles = h ? (rows + 7) / 8 : (rows + rows_per_tile - 1) / rows_per_tile;
+        for (int s = 1; s <= SG_WARPS; s *= 2) {
+            const int per = (blocks32 + s - 1) / s;
+            if (s > 1 && per < 4) break;
+            const int u = (tiles + SG_WARPS / s - 1) / (SG_WARPS / s);
+            const int waves = (u + sg_sm_count() - 1) / sg_sm_count();
+            const long cost = (long)waves * ((long)((per + 3) / 4) * 4 * (h ? 6 : 10) + 60);
+            if (best_cost < 0 || cost < best_cost) {
+                best_cost = cost;
+                *sk = s;
+                *half = h;
+                *n_tiles = tiles;
+            }
+        }
     }
-    *sk = best_sk;
-    *tpc = SG_WARPS / best_sk;
-    *units = (n_tiles + *tpc - 1) / *tpc;
+    *tpc = SG_WARPS / *sk;
+    *units = (*n_tiles + *tpc - 1) / *tpc;
 }
 
 template <int MT, int EPI, bool NORM>
 static int skinny_launch(const SkinnyArgs& a, cudaStream_t stream) {
-    const size_t smem = (size_t)a.ring_offset + skinny_round_bytes(MT, NORM) * a.ring_rounds;
+    const size_t smem = (size_t)a.ring_offset + skinny_round_bytes(MT, NORM, EPI == EPI_CONV ? 2 : 1) * a.ring_rounds;
     static size_t configured = 0;
     if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<MT, EPI, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -373,8 +555,25 @@ static int skinny_dispatch_mt(const SkinnyArgs& a, cudaStream_t stream) {
 ZAI_API int zai_skinny_gemm_supports(int M, int O, int K, int epilogue) {
     if (M < 1 || M > 16 || O < 1 || K < 8 || (K & 7)) return 0;    // more rows: the library's product is faster
     if (epilogue == EPI_SWIGLU && (O & 1)) return 0;
+    if (epilogue == EPI_CONV && O % 3) return 0;
     const int mt = M <= 8 ? 1 : 2;
-    return skinny_ring_rounds(mt, K, true) >= 1;
+    return skinny_ring_rounds(mt, K, true, epilogue == EPI_CONV ? 2 : 1) >= 1;
+}
+
+static int skinny_run(SkinnyArgs& a, int epilogue, cudaStream_t stream) {
+    const int mt = a.M <= 8 ? 1 : 2, nt = epilogue == EPI_CONV ? 2 : 1;
+    const bool norm = a.h != nullptr;
+    if (norm && (a.K & 3)) return ZAI_BAD_SIZE;
+    a.ring_rounds = skinny_ring_rounds(mt, a.K, norm, nt);
+    if (a.ring_rounds < 1) return ZAI_BAD_SIZE;
+    a.red_offset = (int)skinny_x_bytes(mt, a.K, norm);
+    a.ring_offset = a.red_offset + (int)skinny_red_bytes(mt, nt);
+    a.l2_prefetch_bytes = skinny_l2_prefetch_bytes();
+    if (epilogue == EPI_BF16) return norm ? skinny_dispatch_mt<EPI_BF16, true>(a, stream) : skinny_dispatch_mt<EPI_BF16, false>(a, stream);
+    if (epilogue == EPI_F32) return norm ? skinny_dispatch_mt<EPI_F32, true>(a, stream) : skinny_dispatch_mt<EPI_F32, false>(a, stream);
+    if (epilogue == EPI_SWIGLU) return norm ? skinny_dispatch_mt<EPI_SWIGLU, true>(a, stream) : skinny_dispatch_mt<EPI_SWIGLU, false>(a, stream);
+    if (epilogue == EPI_CONV) return norm ? skinny_dispatch_mt<EPI_CONV, true>(a, stream) : skinny_dispatch_mt<EPI_CONV, false>(a, stream);
+    return ZAI_BAD_SIZE;
 }
 
 // y = epilogue(x . W^T).  With `h` given, x = rmsnorm(h[row_idx] + delta[row_idx]) * gamma and, if
@@ -383,23 +582,38 @@ ZAI_API int zai_skinny_gemm_supports(int M, int O, int K, int epilogue) {
 ZAI_API int zai_skinny_gemm(void* y, const void* W, const void* x, const float* h, const void* delta,
                             const float* gamma, const int* row_idx, float* h_out, float eps, int M, int O, int K,
                             int epilogue, cudaStream_t stream) {
-    if (!zai_skinny_gemm_supports(M, O, K, epilogue)) return ZAI_BAD_SIZE;
-    if (h && (K & 3)) return ZAI_BAD_SIZE;
-    SkinnyArgs a;
+    if (epilogue == EPI_CONV || !zai_skinny_gemm_supports(M, O, K, epilogue)) return ZAI_BAD_SIZE;
+    SkinnyArgs a = {};
     a.W = (const bf16*)W; a.x = (const bf16*)x; a.h = h; a.delta = (const bf16*)delta; a.gamma = gamma;
     a.row_idx = row_idx; a.h_out = h_out; a.y = y; a.eps = eps; a.M = M; a.O = O; a.K = K;
     a.F = O / 2;
     a.ldy = epilogue == EPI_SWIGLU ? O / 2 : O;
-    a.n_tiles = epilogue == EPI_SWIGLU ? (a.F + 7) / 8 : (O + 15) / 16;
-    skinny_plan(a.n_tiles, K, &a.tpc, &a.sk, &a.units);
-    const int mt = M <= 8 ? 1 : 2;
-    const bool norm = h != nullptr;
-    a.ring_rounds = skinny_ring_rounds(mt, K, norm);
-    if (a.ring_rounds < 1) return ZAI_BAD_SIZE;
-    a.red_offset = (int)skinny_x_bytes(mt, K, norm);
-    a.ring_offset = a.red_offset + (int)skinny_red_bytes(mt);
-    if (epilogue == EPI_BF16) return norm ? skinny_dispatch_mt<EPI_BF16, true>(a, stream) : skinny_dispatch_mt<EPI_BF16, false>(a, stream);
-    if (epilogue == EPI_F32) return norm ? skinny_dispatch_mt<EPI_F32, true>(a, stream) : skinny_dispatch_mt<EPI_F32, false>(a, stream);
-    if (epilogue == EPI_SWIGLU) return norm ? skinny_dispatch_mt<EPI_SWIGLU, true>(a, stream) : skinny_dispatch_mt<EPI_SWIGLU, false>(a, stream);
-    return ZAI_BAD_SIZE;
+    if (epilogue == EPI_SWIGLU) {
+        skinny_plan(a.F * 2, false, K, &a.n_tiles, &a.half_tiles, &a.tpc, &a.sk, &a.units);   // 8 gate + 8 up rows per tile
+    } else {
+        skinny_plan(O, true, K, &a.n_tiles, &a.half_tiles, &a.tpc, &a.sk, &a.units);
+    }
+    return skinny_run(a, epilogue, stream);
+}
+
+// The short convolution's input projection with the convolution as its epilogue, for steps in which
+// every row is one token of its own request:  (B, C, x~) = x . W^T with W = [3F, K] stacked;
+// u = B x~;  y = bias + sum_j w[c, j] state[j, c] + w[c, taps-1] u;  z = C y (bfloat16 [M, F]);  the
+// state of the row's slot moves on by one (if write_state).  B, C and x~ are rounded to bfloat16
+// before they are used, as when they are stored.  taps <= 4.
+ZAI_API int zai_skinny_conv(void* z, const void* W, const void* x, const float* h, const void* delta, const float* gamma,
+                            float* h_out, float eps, const float* conv_w, const float* conv_b, float* state,
+                            const int* slot_ids, int M, int F, int K, int taps, int state_rows, int write_state,
+                            cudaStream_t stream) {
+    if (F < 1 || taps < 1 || taps > SG_CONV_TAPS || state_rows < taps - 1) return ZAI_BAD_SIZE;
+    if (!zai_skinny_gemm_supports(M, 3 * F, K, EPI_CONV)) return ZAI_BAD_SIZE;
+    SkinnyArgs a = {};
+    a.W = (const bf16*)W; a.x = (const bf16*)x; a.h = h; a.delta = (const bf16*)delta; a.gamma = gamma;
+    a.row_idx = nullptr; a.h_out = h_out; a.y = z; a.eps = eps; a.M = M; a.O = 3 * F; a.K = K;
+    a.F = F;
+    a.ldy = F;
+    a.conv_w = conv_w; a.conv_b = conv_b; a.conv_state = state; a.slot_ids = slot_ids;
+    a.taps = taps; a.state_rows = state_rows; a.write_state = write_state;
+    skinny_plan(F, false, K, &a.n_tiles, &a.half_tiles, &a.tpc, &a.sk, &a.units, 8);   // 8 channels per tile
+    return skinny_run(a, EPI_CONV, stream);
 }

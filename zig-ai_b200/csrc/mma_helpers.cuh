@@ -33,30 +33,55 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 
-// one head row: RMSNorm (if gamma) and rotation of the first `rot` dims; `tmp` holds D floats
+// one head row: RMSNorm (if gamma) and rotation of the first `rot` dims; `tmp` holds D floats.  The
+// row, the norm's weight and the rotation's cosines and sines are all asked for before the first
+// of them is used, so the three loads cost one trip to memory, not three.
 template <int D>
 __device__ __forceinline__ void norm_rotate_row(const bf16* __restrict__ raw, const float* __restrict__ gamma, float eps,
                                                 const float2* __restrict__ cs, int rot, float* tmp, bf16* dst, int lane) {
-    float ss = 0.f;
-    for (int d = lane; d < D; d += 32) {
-        const float v = __bfloat162float(raw[d]);
-        tmp[d] = v;
-        ss += v * v;
+    constexpr int PER = (D + 31) / 32;
+    const int half = rot >> 1;
+    float v[PER], gm[PER];
+    float2 c[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int d = lane + 32 * i;
+        v[i] = 0.f;
+        gm[i] = 1.f;
+        c[i] = make_float2(1.f, 0.f);
+        if (d < D) {
+            v[i] = __bfloat162float(raw[d]);
+            if (gamma) gm[i] = gamma[d];
+            if (d < rot) c[i] = cs[d < half ? d : d - half];
+        }
     }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) ss += v[i] * v[i];
+    float inv = 1.f;
     if (gamma) {
         ss = warp_sum(ss);
-        const float inv = rsqrtf(ss / (float)D + eps);
-        for (int d = lane; d < D; d += 32) tmp[d] = tmp[d] * inv * gamma[d];
+        inv = rsqrtf(ss / (float)D + eps);
+    }
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int d = lane + 32 * i;
+        if (d < D) {
+            if (gamma) v[i] = v[i] * inv * gm[i];
+            tmp[d] = v[i];
+        }
     }
     __syncwarp();
-    const int half = rot >> 1;
-    for (int d = lane; d < D; d += 32) {
-        float v;
-        if (d < half) { const float2 c = cs[d]; v = tmp[d] * c.x - tmp[d + half] * c.y; }
-        else if (d < rot) { const float2 c = cs[d - half]; v = tmp[d - half] * c.y + tmp[d] * c.x; }
-        else v = tmp[d];
-        dst[d] = __float2bfloat16_rn(v);
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int d = lane + 32 * i;
+        if (d < D) {
+            float r;
+            if (d < half) r = v[i] * c[i].x - tmp[d + half] * c[i].y;
+            else if (d < rot) r = tmp[d - half] * c[i].y + v[i] * c[i].x;
+            else r = v[i];
+            dst[d] = __float2bfloat16_rn(r);
+        }
     }
     __syncwarp();
 }
-

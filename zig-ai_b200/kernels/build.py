@@ -25,6 +25,11 @@ from typing import Dict, List
 CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc")
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ARCH_FLAGS + ["-O3", "-lineinfo", "-std=c++17", "-shared", "-Xcompiler", "-fPIC"]
+# ZAI_TIMELINE=1: kernels note the global timer around their dependency wait (csrc/common.cuh); these
+# libraries are kept in a folder of their own
+TIMELINE = os.environ.get("ZAI_TIMELINE", "0") == "1"
+if TIMELINE:
+    NVCC_FLAGS = NVCC_FLAGS + ["-DZAI_TIMELINE"]
 EXTRA_FLAGS: Dict[str, List[str]] = {}
 EXTRA_LIBS: Dict[str, List[str]] = {}
 
@@ -62,7 +67,7 @@ def lib_dir() -> str:
 
 
 def _find_lib_dir() -> str:
-    d = os.path.join(CSRC, "_build")
+    d = os.path.join(CSRC, "_build_timeline" if TIMELINE else "_build")
     try:
         os.makedirs(d, exist_ok=True)
         probe = os.path.join(d, f".w{os.getpid()}")
@@ -71,7 +76,7 @@ def _find_lib_dir() -> str:
         os.remove(probe)
         return d
     except OSError:
-        d = os.path.join(tempfile.gettempdir(), f"zig_ai_b200_{os.getuid()}", "_build")
+        d = os.path.join(tempfile.gettempdir(), f"zig_ai_b200_{os.getuid()}", "_build_timeline" if TIMELINE else "_build")
         os.makedirs(d, exist_ok=True)
         return d
 

@@ -52,6 +52,7 @@ _SIGNATURES = {
     "decode_gemm": {
         "zai_skinny_gemm_supports": [_I, _I, _I, _I],
         "zai_skinny_gemm": [_P, _P, _P, _P, _P, _P, _P, _P, _F, _I, _I, _I, _I, _P],
+        "zai_skinny_conv": [_P, _P, _P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     },
     "gemm_tc": {
         "zai_gemm_tc_supports": [_I, _I, _I, _I],
@@ -109,6 +110,32 @@ def require() -> None:
     build.build_all(verbose=True)            # whatever is missing or out of date, several at a time
     for lib in ("embed", "norm", "activation", "shortconv", "rope_kv", "attention", "attention_mma", "attention_tma", "decode_gemm", "gemm_tc", "sampling"):
         build.load(lib)
+
+
+def timeline():
+    """With libraries built under ZAI_TIMELINE=1: the kernels run since the last call, as a list of
+    (library, ns when the kernel's first block reached its dependency wait, ns when the wait was
+    over) in the order of the second time; marks set inside kernels come as ("<library> mark <id>",
+    ns, ns).  Reads the device."""
+    import ctypes
+    if not build.TIMELINE:
+        raise KernelError("the libraries were built without ZAI_TIMELINE=1")
+    torch.cuda.synchronize()
+    out = []
+    buf = (ctypes.c_ulonglong * (2 * 16384))()
+    for name in build.sources():
+        lib = build.load(name)
+        fn = lib.zai_timeline_read
+        fn.argtypes = [ctypes.c_void_p, c_int]
+        fn.restype = c_int
+        n = fn(ctypes.cast(buf, ctypes.c_void_p), 16384)
+        if n < 0:
+            raise KernelError(f"zai_timeline_read failed in {name}")
+        for i in range(n):
+            a, b = int(buf[2 * i]), int(buf[2 * i + 1])
+            out.append((f"{name} mark {a & 255}", b, b) if a >> 63 else (name, a, b))
+    out.sort(key=lambda r: r[2])
+    return out
 
 
 def _dt(t: torch.Tensor) -> int:
@@ -293,6 +320,43 @@ def silu_mul(gu, ff_dim):
     return out
 
 
+_EPI_CONV = 3
+FUSED_CONV_MAX_TAPS = 4
+
+
+def linear_short_conv(x, w_in, conv_w, conv_b, state, step, taps, write_state=True):
+    """z = C * conv(state ++ B * x~) with (B, C, x~) = x . w_in^T: the short convolution's input
+    projection, gates, taps and state update.  A step of single tokens (at most 16) runs as one
+    kernel, the convolution being the product's epilogue; other steps as the product and the
+    convolution kernel."""
+    lazy = isinstance(x, LazyNorm)
+    M = (x.rows.numel() if x.rows is not None else x.residual.data.shape[0]) if lazy else x.shape[0]
+    O, K = w_in.shape
+    C = O // 3
+    fused = (step.decode_only and taps <= FUSED_CONV_MAX_TAPS and w_in.dtype == torch.bfloat16 and x.dtype == torch.bfloat16
+             and (not lazy or x.rows is None) and state.dtype == torch.float32 and state.shape[-1] == C
+             and M == step.n_seqs and _fn("decode_gemm", "zai_skinny_gemm_supports")(M, O, K, _EPI_CONV))
+    if not fused:
+        return short_conv(linear(x, w_in), conv_w, conv_b, state, step, taps, write_state)
+    _cuda(w_in, conv_w, conv_b, state)
+    z = torch.empty((M, C), dtype=torch.bfloat16, device=w_in.device)
+    fn = _fn("decode_gemm", "zai_skinny_conv")
+    tail = (_ptr(conv_w), _ptr(conv_b), _ptr(state), _ptr(step.slot_ids), M, C, K, int(taps), state.shape[1],
+            int(bool(write_state)), _stream())
+    if lazy:
+        res = x.residual
+        _cuda(res.data, x.delta, x.gamma)
+        h_out = torch.empty_like(res.data) if x.delta is not None else None
+        _check(fn(_ptr(z), _ptr(w_in), None, _ptr(res.data), _ptr(x.delta), _ptr(x.gamma), _ptr(h_out), float(x.eps), *tail),
+               "skinny_conv")
+        if h_out is not None:
+            res.data = h_out
+    else:
+        _cuda(x)
+        _check(fn(_ptr(z), _ptr(w_in), _ptr(x), None, None, None, None, 0.0, *tail), "skinny_conv")
+    return z
+
+
 def short_conv(bcx, conv_w, conv_b, state, step, taps, write_state=True):
     _cuda(bcx, conv_w, conv_b, state)
     N, C = bcx.shape[0], bcx.shape[1] // 3
@@ -402,7 +466,7 @@ def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=Non
 
 _tickets = {}
 USE_TMA_ATTENTION = os.environ.get("ZAI_TMA_ATTENTION", "1") == "1"   # keys and values by TMA where the sizes allow
-DECODE_BLOCKS_WANTED = 1500      # about two waves of five blocks per SM
+DECODE_BLOCKS_WANTED = 500
 
 
 def fused_decode_attention_available(dtype, heads, kv_heads, head_dim) -> bool:
@@ -418,11 +482,12 @@ def decode_attention_fused(qkv, q_w, k_w, eps, rotary_dim, theta, step, cache, h
     B, cols = qkv.shape
     dev = qkv.device
     out = torch.empty((B, heads * head_dim), dtype=qkv.dtype, device=dev)
-    # keys per block: enough blocks to fill the SMs a few times over, few enough that a block's
-    # start-up and its partial sums are spread over many keys (a power of two between 128 and 1024)
+    # keys per block: about DECODE_BLOCKS_WANTED blocks (a little more than the SMs hold at once), so
+    # that a block's start-up and its partial sums are spread over many keys without leaving SMs
+    # idle (a power of two between 256 and 1024)
     want = int(step.max_kv_len) * B * kv_heads // DECODE_BLOCKS_WANTED
-    chunk = 128
-    while chunk < 1024 and chunk < want:
+    chunk = 256
+    while chunk < 1024 and chunk * 3 < want * 2:
         chunk *= 2
     chunk = int(os.environ.get("ZAI_DECODE_CHUNK", chunk))
     n_chunks = max(-(-int(step.max_kv_len) // chunk), 1)

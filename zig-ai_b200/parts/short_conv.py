@@ -51,8 +51,7 @@ class ShortConv(Mixer):
 
     def forward(self, x, step, cache, write_cache=True):
         ops = step.ops
-        bcx = ops.linear(x, self.w_in)
-        z = ops.short_conv(bcx, self.conv_w, self.conv_b, cache.state, step, self.taps, write_cache)
+        z = ops.linear_short_conv(x, self.w_in, self.conv_w, self.conv_b, cache.state, step, self.taps, write_cache)
         return ops.linear(z, self.w_out)
 
 
