@@ -243,6 +243,8 @@ def run_ours(args):
         if args.only == "prefill":
             print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "ms": round(time_prefill(eng, reps=args.steps), 3)}))
             return 0
+        if args.only == "timeline":
+            return run_timeline(eng, args.batch)
         if args.only == "decode":
             ms, e2e, ctx, launches, _, _, _ = time_decode(eng, args.batch, args.steps, args.warmup)
             print(json.dumps({"only": "decode", "batch": args.batch, "ms_per_step": round(ms, 4),
@@ -284,6 +286,41 @@ def run_ours(args):
         "clocks": clock_info,
     }
     print(json.dumps(out))
+    return 0
+
+
+def run_timeline(eng, B):
+    """One decode step's kernels on the device's own clock (libraries built with ZAI_TIMELINE=1): when
+    each kernel's first block was resident and waiting, when its wait for the kernel before it ended,
+    and how long until the next kernel's wait ended (its share of the step)."""
+    import collections
+    from zig_ai_b200.kernels import ops
+    ids = decode_requests(eng, B, 40, seed=B)
+    reqs = [eng.requests[i] for i in ids]
+    runner = eng.runner
+    prepared = [runner.prepare_decode([(r.request_id, [(7 * k + j) % 1000], [0]) for j, r in enumerate(reqs)])
+                for k in range(12)]
+    for k in range(10):
+        ops.argmax(runner.run_prepared(prepared[k]))
+    ops.timeline()
+    for k in range(10, 12):
+        ops.argmax(runner.run_prepared(prepared[k]))
+    tl = [r for r in ops.timeline() if " mark " not in r[0]]
+    starts = [i for i, r in enumerate(tl) if r[0] == "embed_kernel"]
+    step = tl[starts[-1]:]
+    t0 = step[0][2]
+    print(f"batch {B}: {len(step)} kernels, {(step[-1][2] - t0) / 1e3:.1f} us from the first kernel's start to the last one's")
+    print("  # kernel                                   resident at   wait over   waited   until next (us)")
+    agg = collections.OrderedDict()
+    for i, (name, a, b) in enumerate(step):
+        nxt = step[i + 1][2] if i + 1 < len(step) else b
+        print(f"{i:3d} {name:40s} {(a - t0) / 1e3:10.2f} {(b - t0) / 1e3:11.2f} {(b - a) / 1e3:8.2f} {(nxt - b) / 1e3:8.2f}")
+        e = agg.setdefault(name, [0, 0.0])
+        e[0] += 1
+        e[1] += (nxt - b) / 1e3
+    print("by kernel (launches, us in the step, us each):")
+    for name, (n, us) in sorted(agg.items(), key=lambda kv: -kv[1][1]):
+        print(f"  {name:40s} {n:3d} {us:8.1f} {us / n:7.2f}")
     return 0
 
 
@@ -391,7 +428,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "gemm"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "gemm", "timeline"],
                     help="profiling aid: run only the batch-8 decode steps or only the prefill (prints a short line)")
     ap.add_argument("--batch", type=int, default=8, help="with --only decode: the batch size")
     ap.add_argument("--page-size", type=int, default=64, help="positions per cache page")

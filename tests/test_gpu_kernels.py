@@ -276,7 +276,8 @@ def _lazy(h, delta, gamma, eps, rows=None):
 
 
 @pytest.mark.parametrize("M", [1, 3, 8, 13, 16, 40, 64])
-@pytest.mark.parametrize("O,K", [(96, 96), (517, 1000), (1024, 1024), (3072, 1024), (1024, 4608), (130, 8)])
+@pytest.mark.parametrize("O,K", [(96, 96), (517, 1000), (1024, 1024), (3072, 1024), (1024, 4608), (130, 8),
+                                 (1000, 2048), (130, 8192), (96, 6144), (2048, 7168), (40, 1536), (33, 12288), (16, 12296)])
 def test_skinny_gemm_plain_input(M, O, K):
     o = ops()
     g = torch.Generator().manual_seed(20)

@@ -211,7 +211,6 @@ __global__ void __launch_bounds__(TT_THREADS) decode_tma_kernel(const __grid_con
                 }
             }
             asm volatile("bar.sync 1, %0;" ::"n"(TT_CONSUMERS * 32) : "memory");      // the four consumer warps
-            zai_mark(1);
             uint32_t qf[D / 16][4];
             {
                 const int r = (((lane >> 3) & 1) << 3) + (lane & 7);
@@ -288,9 +287,7 @@ __global__ void __launch_bounds__(TT_THREADS) decode_tma_kernel(const __grid_con
             }
             // every consumer is done with the ring (its first stages are reused for the partial sums
             // below), and snew, vnew are visible to the first consumer
-            zai_mark(2);
             asm volatile("bar.sync 1, %0;" ::"n"(TT_CONSUMERS * 32) : "memory");
-            zai_mark(3);
             if (has_new && cw == 0) {                                          // fold the new key into this warp's sums
                 const float s0 = snew[g], s1 = snew[g + 8];
                 const float n0 = fmaxf(m0, s0), n1 = fmaxf(m1, s1);
@@ -361,7 +358,6 @@ __global__ void __launch_bounds__(TT_THREADS) decode_tma_kernel(const __grid_con
     if (tid == 0 && failed_flag) atomicExch(a.status, 1);
 
     // ---- the last block of this (request, key/value head) combines the chunks
-    zai_mark(4);
     __threadfence();
     __syncthreads();
     if (tid == 0) s_ticket = atomicAdd(&a.tickets[b * Hkv + hk], 1);

@@ -58,63 +58,65 @@ static inline int launch_status() { return (int)cudaGetLastError(); }
 // Built with -DZAI_TIMELINE (ZAI_TIMELINE=1 in the environment when the libraries are built), the
 // last thread of every kernel's first block notes the global timer before and after the wait, so a
 // step's kernels can be laid out on one time axis without a profiler's serialisation:
-// zai_timeline_read() returns the records (tag of the library, time at the wait, time after it).
+// zai_timeline_read() returns the records (id, time at the wait, time after it); the id is the
+// source line of the wait times 256 plus a number the kernel may add (a template variant).
 #ifdef ZAI_TIMELINE
-#ifndef ZAI_TIMELINE_TAG
-#define ZAI_TIMELINE_TAG 0
-#endif
 #define ZAI_TIMELINE_RECORDS 16384
-static __device__ unsigned long long zai_tl_records[ZAI_TIMELINE_RECORDS * 2];
+static __device__ unsigned long long zai_tl_records[ZAI_TIMELINE_RECORDS * 3];
 static __device__ unsigned int zai_tl_count;
 __device__ __forceinline__ unsigned long long zai_global_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
+__device__ __forceinline__ void zai_tl_put(unsigned long long id, unsigned long long t0, unsigned long long t1) {
+    const unsigned int i = atomicAdd(&zai_tl_count, 1u);
+    if (i < ZAI_TIMELINE_RECORDS) {
+        zai_tl_records[3 * i] = id;
+        zai_tl_records[3 * i + 1] = t0;
+        zai_tl_records[3 * i + 2] = t1;
+    }
+}
+__device__ __forceinline__ bool zai_tl_thread() {
+    return blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == blockDim.x - 1 && threadIdx.y == 0;
+}
 #endif
-__device__ __forceinline__ void pdl_wait() {
+__device__ __forceinline__ void pdl_wait_at(int line, int variant) {
 #ifdef ZAI_TIMELINE
-    const bool rec = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == blockDim.x - 1 && threadIdx.y == 0;
+    const bool rec = zai_tl_thread();
     unsigned long long t0 = 0;
     if (rec) t0 = zai_global_ns();
 #endif
     asm volatile("griddepcontrol.wait;" ::: "memory");
 #ifdef ZAI_TIMELINE
-    if (rec) {
-        const unsigned long long t1 = zai_global_ns();
-        const unsigned int i = atomicAdd(&zai_tl_count, 1u);
-        if (i < ZAI_TIMELINE_RECORDS) {
-            zai_tl_records[2 * i] = t0;
-            zai_tl_records[2 * i + 1] = t1;
-        }
-    }
+    if (rec) zai_tl_put((unsigned long long)line * 256 + (unsigned long long)(variant & 255), t0, zai_global_ns());
+#else
+    (void)line;
+    (void)variant;
 #endif
 }
+#define pdl_wait() pdl_wait_at(__LINE__, 0)
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-// A further point on the time axis from inside a kernel (same thread as above); a record with both
-// times equal and `id` in the low byte of the first.  Compiles to nothing without ZAI_TIMELINE.
-__device__ __forceinline__ void zai_mark(int id) {
+// A further point on the time axis from inside a kernel (same thread as above): a record with both
+// times equal and the id (1 << 32) + mark.  Compiles to nothing without ZAI_TIMELINE.
+__device__ __forceinline__ void zai_mark(int mark) {
 #ifdef ZAI_TIMELINE
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == blockDim.x - 1 && threadIdx.y == 0) {
+    if (zai_tl_thread()) {
         const unsigned long long t = zai_global_ns();
-        const unsigned int i = atomicAdd(&zai_tl_count, 1u);
-        if (i < ZAI_TIMELINE_RECORDS) {
-            zai_tl_records[2 * i] = (unsigned long long)(id & 255) | (1ull << 63);
-            zai_tl_records[2 * i + 1] = t;
-        }
+        zai_tl_put((1ull << 32) + (unsigned long long)(mark & 255), t, t);
     }
 #else
-    (void)id;
+    (void)mark;
 #endif
 }
 #ifdef ZAI_TIMELINE
-// Copies up to `max_records` (t_wait, t_after) pairs to `out` and empties the list; returns how many.
+// Copies up to `max_records` (id, t_wait, t_after) triples to `out` and empties the list; returns how many.
 ZAI_API int zai_timeline_read(unsigned long long* out, int max_records) {
     unsigned int n = 0;
     if (cudaMemcpyFromSymbol(&n, zai_tl_count, sizeof(n)) != cudaSuccess) return -1;
     if (n > ZAI_TIMELINE_RECORDS) n = ZAI_TIMELINE_RECORDS;
     if ((int)n > max_records) n = (unsigned int)max_records;
-    if (n && cudaMemcpyFromSymbol(out, zai_tl_records, (size_t)n * 2 * sizeof(unsigned long long)) != cudaSuccess) return -1;
+    if (n && cudaMemcpyFromSymbol(out, zai_tl_records, (size_t)n * 3 * sizeof(unsigned long long)) != cudaSuccess) return -1;
     const unsigned int zero = 0;
     cudaMemcpyToSymbol(zai_tl_count, &zero, sizeof(zero));
     return (int)n;

@@ -241,7 +241,7 @@ __global__ void __launch_bounds__(SG_WARPS * 32, 2) skinny_gemm_kernel(const Ski
         }
     }
     pdl_trigger();
-    pdl_wait();
+    pdl_wait_at(__LINE__, 1 + EPI * 2 + (NORM ? 1 : 0));
     if (n_units > 0) conv_inputs(0);                         // asked for now, used in the epilogue
     if (NORM) __syncthreads();                               // gs is complete
     if (!NORM) {
@@ -301,7 +301,6 @@ __global__ void __launch_bounds__(SG_WARPS * 32, 2) skinny_gemm_kernel(const Ski
         }
     }
     if (NORM) __syncthreads();
-    zai_mark(1);
     float inv_tok[MT][2];
 #pragma unroll
     for (int nt = 0; nt < MT; ++nt) {
@@ -462,7 +461,187 @@ __global__ void __launch_bounds__(SG_WARPS * 32, 2) skinny_gemm_kernel(const Ski
         }
     }
     cp_async_wait_rounds(0);
-    zai_mark(2);
+}
+
+// ---- long rows (K of several thousand, the feed-forward's second product): K cut across a cluster
+//
+// With one block per tile, a tile's K slices are the block's 8 warps, and each warp walks its slice
+// round by round behind a ring of two rounds: a chain of trips to memory after the wait, and every
+// block needs all of x.  Here a tile of 16 weight rows belongs to a cluster of CS blocks; K is cut
+// into 8 CS slices, one per warp, short enough that a warp's whole slice of the weights is asked for
+// before the wait and its slice of x in one go after it.  The warps of a block add their sums
+// through shared memory, the blocks of the cluster through rank 0's shared memory (written by the
+// other ranks, then a cluster barrier), both in a fixed order.
+#define SK_MAX_BLOCKS 6            // 32-k blocks per warp at most
+
+struct SplitKArgs {
+    const bf16* W;        // [O, K]
+    const bf16* x;        // [M, K]
+    void* y;              // [M, O] bfloat16 or float
+    int M, O, K, n_tiles;
+    int per;              // 32-k blocks per warp
+    int f32_out;
+};
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// address of `local` (in this block's shared memory) in the shared memory of block `rank` of the cluster
+__device__ __forceinline__ uint32_t cluster_map(const void* local, uint32_t rank) {
+    uint32_t a = (uint32_t)__cvta_generic_to_shared(local), r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_store_f32(uint32_t addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+
+template <int MT, int CS>
+__global__ void __launch_bounds__(SG_WARPS * 32) skinny_splitk_kernel(const SplitKArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int rank = (int)cluster_rank(), tile = blockIdx.x / CS;
+    const int K = a.K, per = a.per;
+    constexpr int SLOT = (2 + MT) * 512;                     // weights rows g, g+8 and MT token groups of one 32-k block
+    unsigned char* mine = smem_raw + (size_t)warp * SK_MAX_BLOCKS * SLOT;
+    float* red = reinterpret_cast<float*>(smem_raw + (size_t)SG_WARPS * SK_MAX_BLOCKS * SLOT);   // [warps][MT*4][32]
+    float* cred = red + SG_WARPS * MT * 4 * 32;                                                  // [CS][MT*4][32], used on rank 0
+    const int blocks32 = (K + 31) >> 5;
+    const int kb0 = (rank * SG_WARPS + warp) * per;
+    int row_lo = tile * 16 + g, row_hi = row_lo + 8;
+    if (row_lo >= a.O) row_lo = -1;
+    if (row_hi >= a.O) row_hi = -1;
+    const bf16* w_lo = a.W + (size_t)(row_lo < 0 ? 0 : row_lo) * K + 8 * t;
+    const bf16* w_hi = a.W + (size_t)(row_hi < 0 ? 0 : row_hi) * K + 8 * t;
+#pragma unroll
+    for (int u = 0; u < SK_MAX_BLOCKS; ++u) {
+        const int k0 = (kb0 + u) << 5;
+        const bool ok = u < per && (kb0 + u) < blocks32 && k0 + 8 * t < K;
+        cp_async16_zfill(mine + u * SLOT + lane * 16, w_lo + k0, ok && row_lo >= 0);
+        cp_async16_zfill(mine + u * SLOT + 512 + lane * 16, w_hi + k0, ok && row_hi >= 0);
+    }
+    cp_async_commit_group();
+    pdl_trigger();
+    pdl_wait();
+#pragma unroll
+    for (int u = 0; u < SK_MAX_BLOCKS; ++u) {
+        const int k0 = (kb0 + u) << 5;
+        const bool ok = u < per && (kb0 + u) < blocks32 && k0 + 8 * t < K;
+#pragma unroll
+        for (int nt = 0; nt < MT; ++nt) {
+            const int m = nt * 8 + g;
+            cp_async16_zfill(mine + u * SLOT + 1024 + nt * 512 + lane * 16, a.x + (size_t)(m < a.M ? m : 0) * K + k0 + 8 * t, ok && m < a.M);
+        }
+    }
+    cp_async_commit_group();
+    cp_async_wait_rounds(0);
+    float c[MT][4];
+#pragma unroll
+    for (int i = 0; i < MT; ++i) c[i][0] = c[i][1] = c[i][2] = c[i][3] = 0.f;
+#pragma unroll
+    for (int u = 0; u < SK_MAX_BLOCKS; ++u) {
+        if (u < per) {
+            const uint4 wl = *reinterpret_cast<const uint4*>(mine + u * SLOT + lane * 16);
+            const uint4 wh = *reinterpret_cast<const uint4*>(mine + u * SLOT + 512 + lane * 16);
+#pragma unroll
+            for (int nt = 0; nt < MT; ++nt) {
+                const uint4 b4 = *reinterpret_cast<const uint4*>(mine + u * SLOT + 1024 + nt * 512 + lane * 16);
+                mma16816(c[nt], wl.x, wh.x, wl.y, wh.y, b4.x, b4.y);
+                mma16816(c[nt], wl.z, wh.z, wl.w, wh.w, b4.z, b4.w);
+            }
+        }
+    }
+    // ---- the block's warps, in order
+    if (warp > 0) {
+#pragma unroll
+        for (int i = 0; i < MT; ++i)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) red[((size_t)warp * MT * 4 + i * 4 + e) * 32 + lane] = c[i][e];
+    }
+    __syncthreads();
+    if (warp == 0) {
+        for (int w2 = 1; w2 < SG_WARPS; ++w2)
+#pragma unroll
+            for (int i = 0; i < MT; ++i)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) c[i][e] += red[((size_t)w2 * MT * 4 + i * 4 + e) * 32 + lane];
+        if (rank > 0) {                                     // into rank 0's shared memory
+#pragma unroll
+            for (int i = 0; i < MT; ++i)
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    cluster_store_f32(cluster_map(cred + ((size_t)rank * MT * 4 + i * 4 + e) * 32 + lane, 0), c[i][e]);
+        }
+    }
+    cluster_sync_all();
+    if (rank != 0 || warp != 0) return;
+    for (int r2 = 1; r2 < CS; ++r2)
+#pragma unroll
+        for (int i = 0; i < MT; ++i)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) c[i][e] += cred[((size_t)r2 * MT * 4 + i * 4 + e) * 32 + lane];
+#pragma unroll
+    for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int tok = nt * 8 + 2 * t + e;
+            if (tok >= a.M) continue;
+            const float lo = c[nt][e], hi = c[nt][2 + e];
+            if (a.f32_out) {
+                if (row_lo >= 0) reinterpret_cast<float*>(a.y)[(size_t)tok * a.O + row_lo] = lo;
+                if (row_hi >= 0) reinterpret_cast<float*>(a.y)[(size_t)tok * a.O + row_hi] = hi;
+            } else {
+                if (row_lo >= 0) reinterpret_cast<bf16*>(a.y)[(size_t)tok * a.O + row_lo] = __float2bfloat16_rn(lo);
+                if (row_hi >= 0) reinterpret_cast<bf16*>(a.y)[(size_t)tok * a.O + row_hi] = __float2bfloat16_rn(hi);
+            }
+        }
+}
+
+template <int MT, int CS>
+static int splitk_launch(const SplitKArgs& a, cudaStream_t stream) {
+    const size_t smem = (size_t)SG_WARPS * SK_MAX_BLOCKS * (2 + MT) * 512 + (size_t)(SG_WARPS + CS) * MT * 4 * 32 * sizeof(float);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(skinny_splitk_kernel<MT, CS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(a.n_tiles * CS));
+    cfg.blockDim = dim3(SG_WARPS * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CS;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    return (int)cudaLaunchKernelEx(&cfg, skinny_splitk_kernel<MT, CS>, a);
+}
+
+// Cluster size for a plain-input product with rows of K values: 0 = the one-block kernel
+static int splitk_cluster(int K) {
+    static int off = -1;
+    if (off < 0) {
+        const char* e = getenv("ZAI_SKINNY_SPLITK");
+        off = (e && e[0] == '0') ? 1 : 0;
+    }
+    if (off) return 0;
+    const int blocks32 = (K + 31) / 32;
+    if (blocks32 >= 192 && (blocks32 + 31) / 32 > SK_MAX_BLOCKS && (blocks32 + 63) / 64 <= SK_MAX_BLOCKS) return 8;   // K > 6144
+    if (blocks32 >= 96 && (blocks32 + 31) / 32 <= SK_MAX_BLOCKS) return 4;      // K >= 3072
+    if (blocks32 >= 48 && (blocks32 + 15) / 16 <= SK_MAX_BLOCKS) return 2;      // K >= 1536
+    return 0;
 }
 
 static int sg_sm_count() {
@@ -552,12 +731,14 @@ static int skinny_dispatch_mt(const SkinnyArgs& a, cudaStream_t stream) {
 }
 
 // 1 if the kernel takes these sizes (else the caller uses the library product and separate kernels)
-ZAI_API int zai_skinny_gemm_supports(int M, int O, int K, int epilogue) {
+// `norm`: x comes as the 32-bit residual stream to be normed (it is staged in shared memory whole,
+// which bounds K), not as bfloat16 rows.
+ZAI_API int zai_skinny_gemm_supports(int M, int O, int K, int epilogue, int norm) {
     if (M < 1 || M > 16 || O < 1 || K < 8 || (K & 7)) return 0;    // more rows: the library's product is faster
     if (epilogue == EPI_SWIGLU && (O & 1)) return 0;
     if (epilogue == EPI_CONV && O % 3) return 0;
     const int mt = M <= 8 ? 1 : 2;
-    return skinny_ring_rounds(mt, K, true, epilogue == EPI_CONV ? 2 : 1) >= 1;
+    return skinny_ring_rounds(mt, K, norm != 0, epilogue == EPI_CONV ? 2 : 1) >= 1;
 }
 
 static int skinny_run(SkinnyArgs& a, int epilogue, cudaStream_t stream) {
@@ -582,7 +763,18 @@ static int skinny_run(SkinnyArgs& a, int epilogue, cudaStream_t stream) {
 ZAI_API int zai_skinny_gemm(void* y, const void* W, const void* x, const float* h, const void* delta,
                             const float* gamma, const int* row_idx, float* h_out, float eps, int M, int O, int K,
                             int epilogue, cudaStream_t stream) {
-    if (epilogue == EPI_CONV || !zai_skinny_gemm_supports(M, O, K, epilogue)) return ZAI_BAD_SIZE;
+    if (epilogue == EPI_CONV || !zai_skinny_gemm_supports(M, O, K, epilogue, h != nullptr)) return ZAI_BAD_SIZE;
+    const int cs = (!h && (epilogue == EPI_BF16 || epilogue == EPI_F32)) ? splitk_cluster(K) : 0;
+    if (cs) {
+        SplitKArgs b;
+        b.W = (const bf16*)W; b.x = (const bf16*)x; b.y = y; b.M = M; b.O = O; b.K = K;
+        b.n_tiles = (O + 15) / 16;
+        b.per = ((K + 31) / 32 + SG_WARPS * cs - 1) / (SG_WARPS * cs);
+        b.f32_out = epilogue == EPI_F32;
+        if (cs == 8) return M <= 8 ? splitk_launch<1, 8>(b, stream) : splitk_launch<2, 8>(b, stream);
+        if (cs == 4) return M <= 8 ? splitk_launch<1, 4>(b, stream) : splitk_launch<2, 4>(b, stream);
+        return M <= 8 ? splitk_launch<1, 2>(b, stream) : splitk_launch<2, 2>(b, stream);
+    }
     SkinnyArgs a = {};
     a.W = (const bf16*)W; a.x = (const bf16*)x; a.h = h; a.delta = (const bf16*)delta; a.gamma = gamma;
     a.row_idx = row_idx; a.h_out = h_out; a.y = y; a.eps = eps; a.M = M; a.O = O; a.K = K;
@@ -606,7 +798,7 @@ ZAI_API int zai_skinny_conv(void* z, const void* W, const void* x, const float* 
                             const int* slot_ids, int M, int F, int K, int taps, int state_rows, int write_state,
                             cudaStream_t stream) {
     if (F < 1 || taps < 1 || taps > SG_CONV_TAPS || state_rows < taps - 1) return ZAI_BAD_SIZE;
-    if (!zai_skinny_gemm_supports(M, 3 * F, K, EPI_CONV)) return ZAI_BAD_SIZE;
+    if (!zai_skinny_gemm_supports(M, 3 * F, K, EPI_CONV, h != nullptr)) return ZAI_BAD_SIZE;
     SkinnyArgs a = {};
     a.W = (const bf16*)W; a.x = (const bf16*)x; a.h = h; a.delta = (const bf16*)delta; a.gamma = gamma;
     a.row_idx = nullptr; a.h_out = h_out; a.y = z; a.eps = eps; a.M = M; a.O = 3 * F; a.K = K;

@@ -50,7 +50,7 @@ _SIGNATURES = {
         "zai_prefill_block_rows": [],
     },
     "decode_gemm": {
-        "zai_skinny_gemm_supports": [_I, _I, _I, _I],
+        "zai_skinny_gemm_supports": [_I, _I, _I, _I, _I],
         "zai_skinny_gemm": [_P, _P, _P, _P, _P, _P, _P, _P, _F, _I, _I, _I, _I, _P],
         "zai_skinny_conv": [_P, _P, _P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     },
@@ -112,17 +112,35 @@ def require() -> None:
         build.load(lib)
 
 
+_SKINNY_VARIANTS = {1: "bf16", 2: "norm, bf16", 3: "f32", 4: "norm, f32", 5: "swiglu", 6: "norm, swiglu", 7: "conv",
+                    8: "norm, conv"}
+
+
+def _kernel_at(lib: str, line: int, cache={}) -> str:
+    """The name of the __global__ function whose body holds `line` of csrc/<lib>.cu."""
+    import re
+    if lib not in cache:
+        with open(os.path.join(build.CSRC, lib + ".cu")) as f:
+            cache[lib] = f.read().split("\n")
+    name = "?"
+    for text in cache[lib][:line]:
+        m = re.search(r"__global__[^(]*?(\w+)\s*\(", re.sub(r"__launch_bounds__\([^)]*\)", "", text))
+        if m:
+            name = m.group(1)
+    return name
+
+
 def timeline():
     """With libraries built under ZAI_TIMELINE=1: the kernels run since the last call, as a list of
-    (library, ns when the kernel's first block reached its dependency wait, ns when the wait was
-    over) in the order of the second time; marks set inside kernels come as ("<library> mark <id>",
+    (kernel, ns when the kernel's first block reached its dependency wait, ns when the wait was
+    over) in the order of the second time; marks set inside kernels come as ("<library> mark <n>",
     ns, ns).  Reads the device."""
     import ctypes
     if not build.TIMELINE:
         raise KernelError("the libraries were built without ZAI_TIMELINE=1")
     torch.cuda.synchronize()
     out = []
-    buf = (ctypes.c_ulonglong * (2 * 16384))()
+    buf = (ctypes.c_ulonglong * (3 * 16384))()
     for name in build.sources():
         lib = build.load(name)
         fn = lib.zai_timeline_read
@@ -132,8 +150,14 @@ def timeline():
         if n < 0:
             raise KernelError(f"zai_timeline_read failed in {name}")
         for i in range(n):
-            a, b = int(buf[2 * i]), int(buf[2 * i + 1])
-            out.append((f"{name} mark {a & 255}", b, b) if a >> 63 else (name, a, b))
+            ident, a, b = int(buf[3 * i]), int(buf[3 * i + 1]), int(buf[3 * i + 2])
+            if ident >> 32:
+                out.append((f"{name} mark {ident & 255}", b, b))
+            else:
+                kernel, variant = _kernel_at(name, ident >> 8), ident & 255
+                if name == "decode_gemm" and variant:
+                    kernel += f" ({_SKINNY_VARIANTS.get(variant, variant)})"
+                out.append((kernel, a, b))
     out.sort(key=lambda r: r[2])
     return out
 
@@ -219,7 +243,7 @@ def _skinny(x, w, epilogue, out_cols, out_dtype):
     O, K = w.shape
     if w.dtype != torch.bfloat16 or (not lazy and x.dtype != torch.bfloat16) or (lazy and x.dtype != torch.bfloat16):
         return None
-    if not _fn("decode_gemm", "zai_skinny_gemm_supports")(M, O, K, epilogue):
+    if not _fn("decode_gemm", "zai_skinny_gemm_supports")(M, O, K, epilogue, int(lazy)):
         return None
     y = torch.empty((M, out_cols), dtype=out_dtype, device=w.device)
     if lazy:
@@ -335,7 +359,7 @@ def linear_short_conv(x, w_in, conv_w, conv_b, state, step, taps, write_state=Tr
     C = O // 3
     fused = (step.decode_only and taps <= FUSED_CONV_MAX_TAPS and w_in.dtype == torch.bfloat16 and x.dtype == torch.bfloat16
              and (not lazy or x.rows is None) and state.dtype == torch.float32 and state.shape[-1] == C
-             and M == step.n_seqs and _fn("decode_gemm", "zai_skinny_gemm_supports")(M, O, K, _EPI_CONV))
+             and M == step.n_seqs and _fn("decode_gemm", "zai_skinny_gemm_supports")(M, O, K, _EPI_CONV, int(lazy)))
     if not fused:
         return short_conv(linear(x, w_in), conv_w, conv_b, state, step, taps, write_state)
     _cuda(w_in, conv_w, conv_b, state)
