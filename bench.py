@@ -305,7 +305,7 @@ def run_timeline(eng, B):
     ops.timeline()
     for k in range(10, 12):
         ops.argmax(runner.run_prepared(prepared[k]))
-    tl = [r for r in ops.timeline() if " mark " not in r[0]]
+    tl = [r for r in ops.timeline() if " mark " not in r[0] and " block " not in r[0]]
     starts = [i for i, r in enumerate(tl) if r[0] == "embed_kernel"]
     step = tl[starts[-1]:]
     t0 = step[0][2]

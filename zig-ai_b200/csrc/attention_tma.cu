@@ -95,9 +95,11 @@ struct TmaDecodeArgs {
     const int* positions;
     float eps, scale_log2;
     int qkv_cols, rot, table_width, page_size, page_shift, Hq, Hkv, window, write_kv, chunk_keys, stages;
+    int chunk_fastest;         // the grid is (chunks, Hkv, B) if set, else (Hkv, B, chunks)
 };
 
-__global__ void __launch_bounds__(TT_THREADS) decode_tma_kernel(const __grid_constant__ CUtensorMap map, const TmaDecodeArgs a) {
+// (128 registers a thread: three blocks of 160 threads share an SM's 64 K registers; a few more and only two fit)
+__global__ void __maxnreg__(128) decode_tma_kernel(const __grid_constant__ CUtensorMap map, const TmaDecodeArgs a) {
     constexpr int D = TT_D, ST = D + 8;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -116,7 +118,13 @@ __global__ void __launch_bounds__(TT_THREADS) decode_tma_kernel(const __grid_con
     volatile int* failed = &failed_flag;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int chunk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z, n_chunks = gridDim.x;
+    // Blocks are handed out in the order of their index, x fastest.  When all of them are resident at
+    // once or nearly so, the chunk is the slowest index: the first chunks of every request (all with
+    // work) start first, the last chunks (short or empty for most requests) last.  With many more
+    // blocks than the SMs hold, the chunk is the fastest index: a request's chunks run together and
+    // are combined as the kernel goes, not all at its end.
+    const int chunk = a.chunk_fastest ? blockIdx.x : blockIdx.z, hk = a.chunk_fastest ? blockIdx.y : blockIdx.x;
+    const int b = a.chunk_fastest ? blockIdx.z : blockIdx.y, n_chunks = a.chunk_fastest ? gridDim.x : gridDim.z;
     const int Hq = a.Hq, Hkv = a.Hkv, G = Hq / Hkv, ps = a.page_size;
     if (tid == 0) {
         failed_flag = 0;
@@ -399,6 +407,17 @@ static TtEncodeTiledFn tt_encode_tiled() {
     return fn;
 }
 
+static int tt_sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n < 1) n = 1;
+    }
+    return n;
+}
+
 // 1 if this kernel takes the sizes: head size 64, a page size that is a power of two from 8 to 64,
 // at most 16 query heads per key/value head
 ZAI_API int zai_decode_attention_tma_supports(int D, int Hq, int Hkv, int page_size) {
@@ -417,7 +436,7 @@ ZAI_API int zai_decode_attention_tma(void* out, float* part_o, float* part_ml, i
                                      cudaStream_t stream) {
     if (B <= 0) return ZAI_OK;
     if (!zai_decode_attention_tma_supports(D, Hq, Hkv, page_size)) return ZAI_BAD_SIZE;
-    if (chunk_keys < TT_TILE || chunk_keys % TT_TILE || n_chunks < 1 || Hkv > 65535 || B > 65535 || rot < 0 || rot > D || (rot & 1))
+    if (chunk_keys < TT_TILE || chunk_keys % TT_TILE || n_chunks < 1 || Hkv > 65535 || B > 65535 || n_chunks > 65535 || rot < 0 || rot > D || (rot & 1))
         return ZAI_BAD_SIZE;
     if (reinterpret_cast<uintptr_t>(pages) & 15) return ZAI_BAD_SIZE;
     // the pool as rows of 64 elements: [num_pages * 2 * Hkv * page_size, 64]; a box is one page-head block
@@ -453,5 +472,7 @@ ZAI_API int zai_decode_attention_tma(void* out, float* part_o, float* part_ml, i
         if (e != cudaSuccess) return (int)e;
         configured = smem;
     }
-    return launch_pdl(decode_tma_kernel, dim3(n_chunks, Hkv, B), dim3(TT_THREADS), smem, stream, map, a);
+    a.chunk_fastest = (long long)B * Hkv * n_chunks > 6 * (long long)tt_sm_count();    // more than two rounds of three blocks per SM
+    const dim3 grid = a.chunk_fastest ? dim3(n_chunks, Hkv, B) : dim3(Hkv, B, n_chunks);
+    return launch_pdl(decode_tma_kernel, grid, dim3(TT_THREADS), smem, stream, map, a);
 }

@@ -109,6 +109,24 @@ __device__ __forceinline__ void zai_mark(int mark) {
     (void)mark;
 #endif
 }
+// The life of every block of a kernel (not only the first): call at the block's start, keep the value,
+// and hand it back at the block's end; a record with the id (2 << 32) + the block's linear index.
+__device__ __forceinline__ unsigned long long zai_block_begin() {
+#ifdef ZAI_TIMELINE
+    return zai_global_ns();
+#else
+    return 0;
+#endif
+}
+__device__ __forceinline__ void zai_block_end(unsigned long long t_begin) {
+#ifdef ZAI_TIMELINE
+    if (threadIdx.x == 0 && threadIdx.y == 0)
+        zai_tl_put((2ull << 32) + blockIdx.x + (unsigned long long)gridDim.x * (blockIdx.y + (unsigned long long)gridDim.y * blockIdx.z),
+                   t_begin, zai_global_ns());
+#else
+    (void)t_begin;
+#endif
+}
 #ifdef ZAI_TIMELINE
 // Copies up to `max_records` (id, t_wait, t_after) triples to `out` and empties the list; returns how many.
 ZAI_API int zai_timeline_read(unsigned long long* out, int max_records) {

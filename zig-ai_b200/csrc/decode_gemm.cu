@@ -654,14 +654,26 @@ static int sg_sm_count() {
     }
     return n;
 }
-// Bytes per block asked into L2 ahead of the wait (ZAI_SKINNY_L2_PREFETCH_KB, default 384 KB: with one
-// block per SM about 57 MB, under half of L2)
+// Bytes per block asked into L2 ahead of the wait (ZAI_SKINNY_L2_PREFETCH_KB; default 0: measured on
+// the LFM2 shapes it gains nothing, the rings already hold what a block needs first)
 static int skinny_l2_prefetch_bytes() {
     static int v = -1;
     if (v < 0) {
         const char* e = getenv("ZAI_SKINNY_L2_PREFETCH_KB");
-        v = (e ? atoi(e) : 384) * 1024;
+        v = (e ? atoi(e) : 0) * 1024;
         if (v < 0) v = 0;
+    }
+    return v;
+}
+// Blocks of one launch: up to two per SM (a block keeps to half of an SM's shared memory), so that a
+// launch with many units has all its weights asked for at once (ZAI_SKINNY_BLOCKS_PER_SM overrides)
+static int sg_slots() {
+    static int v = 0;
+    if (!v) {
+        const char* e = getenv("ZAI_SKINNY_BLOCKS_PER_SM");
+        int per_sm = e ? atoi(e) : 2;
+        if (per_sm < 1) per_sm = 1;
+        v = sg_sm_count() * per_sm;
     }
     return v;
 }
@@ -696,7 +708,7 @@ static void skinny_plan(int rows, bool may_halve, int K, int* n_tiles, int* half
             const int per = (blocks32 + s - 1) / s;
             if (s > 1 && per < 4) break;
             const int u = (tiles + SG_WARPS / s - 1) / (SG_WARPS / s);
-            const int waves = (u + sg_sm_count() - 1) / sg_sm_count();
+            const int waves = (u + sg_slots() - 1) / sg_slots();
             const long cost = (long)waves * ((long)((per + 3) / 4) * 4 * (h ? 6 : 10) + 60);
             if (best_cost < 0 || cost < best_cost) {
                 best_cost = cost;
@@ -720,7 +732,7 @@ static int skinny_launch(const SkinnyArgs& a, cudaStream_t stream) {
         if (e != cudaSuccess) return (int)e;
         configured = smem;
     }
-    const int grid = a.units < sg_sm_count() ? a.units : sg_sm_count();
+    const int grid = a.units < sg_slots() ? a.units : sg_slots();
     return launch_pdl(skinny_gemm_kernel<MT, EPI, NORM>, dim3(grid), dim3(SG_WARPS * 32), smem, stream, a);
 }
 
@@ -747,6 +759,12 @@ static int skinny_run(SkinnyArgs& a, int epilogue, cudaStream_t stream) {
     if (norm && (a.K & 3)) return ZAI_BAD_SIZE;
     a.ring_rounds = skinny_ring_rounds(mt, a.K, norm, nt);
     if (a.ring_rounds < 1) return ZAI_BAD_SIZE;
+    {   // no deeper than the busiest block's rounds: shared memory left free lets the next kernel's blocks in
+        const int per = ((a.K + 31) / 32 + a.sk - 1) / a.sk, rpu = (per + 3) / 4;
+        const int grid = a.units < sg_slots() ? a.units : sg_slots();
+        const int rounds = rpu * ((a.units + grid - 1) / grid);
+        if (a.ring_rounds > rounds) a.ring_rounds = rounds;
+    }
     a.red_offset = (int)skinny_x_bytes(mt, a.K, norm);
     a.ring_offset = a.red_offset + (int)skinny_red_bytes(mt, nt);
     a.l2_prefetch_bytes = skinny_l2_prefetch_bytes();

@@ -151,7 +151,9 @@ def timeline():
             raise KernelError(f"zai_timeline_read failed in {name}")
         for i in range(n):
             ident, a, b = int(buf[3 * i]), int(buf[3 * i + 1]), int(buf[3 * i + 2])
-            if ident >> 32:
+            if ident >> 32 == 2:
+                out.append((f"{name} block {ident & 0xffffffff}", a, b))
+            elif ident >> 32:
                 out.append((f"{name} mark {ident & 255}", b, b))
             else:
                 kernel, variant = _kernel_at(name, ident >> 8), ident & 255
