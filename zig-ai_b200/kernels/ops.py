@@ -124,7 +124,7 @@ def _kernel_at(lib: str, line: int, cache={}) -> str:
             cache[lib] = f.read().split("\n")
     name = "?"
     for text in cache[lib][:line]:
-        m = re.search(r"__global__[^(]*?(\w+)\s*\(", re.sub(r"__launch_bounds__\([^)]*\)", "", text))
+        m = re.search(r"__global__[^(]*?(\w+)\s*\(", re.sub(r"__(launch_bounds|maxnreg)__\([^)]*\)", "", text))
         if m:
             name = m.group(1)
     return name
