@@ -169,7 +169,7 @@ def load_runner(model_dir: str, dtype="bfloat16", max_tokens: int = 4096, max_re
     if ops is None:
         from ..kernels import ops as cuda_ops
         ops = cuda_ops
-        ops.require()
+        ops.require(tdtype)
     if device is None:
         device = torch.device("cuda", torch.cuda.current_device()) if ops.device_type == "cuda" else torch.device("cpu")
     device = torch.device(device)

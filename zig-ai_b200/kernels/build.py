@@ -148,6 +148,14 @@ def build_all(verbose: bool = True, force: bool = False) -> List[str]:
     return [lib_path(n) for n in sources()]
 
 
+def build_some(names: List[str], verbose: bool = True) -> None:
+    """Compile those of the named sources that are missing or out of date, a few at a time."""
+    todo = [n for n in names if not is_current(n)]
+    if todo:
+        with ThreadPoolExecutor(max_workers=min(len(todo), os.cpu_count() or 2)) as ex:
+            list(ex.map(lambda n: compile_one(n, verbose), todo))
+
+
 def load(name: str) -> ctypes.CDLL:
     """The library of csrc/<name>.cu, compiled first if needed."""
     with _lock:

@@ -103,12 +103,23 @@ def _check(code: int, what: str, n: int = 1) -> None:
     raise KernelError(f"{what}: CUDA error {code} at launch")
 
 
-def require() -> None:
-    """Fail loudly unless a CUDA device is present and the core libraries load."""
+CORE_LIBS = ("embed", "norm", "activation", "shortconv", "rope_kv", "attention", "sampling")
+BF16_LIBS = ("attention_mma", "attention_tma", "decode_gemm")
+
+
+def require(dtype=None) -> None:
+    """Fail loudly unless a CUDA device is present and the libraries load that a model of `dtype`
+    uses (all of them if no dtype is given).  What is missing or out of date is compiled now, several
+    sources at a time; a library outside this set is compiled when it is first called."""
     if not torch.cuda.is_available():
         raise KernelError("no CUDA device: this engine has no CPU path")
-    build.build_all(verbose=True)            # whatever is missing or out of date, several at a time
-    for lib in ("embed", "norm", "activation", "shortconv", "rope_kv", "attention", "attention_mma", "attention_tma", "decode_gemm", "gemm_tc", "sampling"):
+    libs = list(CORE_LIBS)
+    if dtype is None or dtype == torch.bfloat16:
+        libs += list(BF16_LIBS)
+        if dtype is None or USE_TC_GEMM:
+            libs.append("gemm_tc")
+    build.build_some(libs, verbose=True)
+    for lib in libs:
         build.load(lib)
 
 
