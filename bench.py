@@ -137,6 +137,7 @@ def time_decode(eng, B, steps, warmup, clocks=None):
     if clocks:
         clocks.start()                       # nvidia-smi takes a while to give its first sample
     ids = decode_requests(eng, B, 2 * (steps + warmup) + 4, seed=B)
+    eng.flush()                              # no step on its way while the runner is driven directly
     reqs = [eng.requests[i] for i in ids]
     runner = eng.runner
     ctx_tokens = sum(r.computed for r in reqs)
@@ -188,6 +189,7 @@ def time_decode(eng, B, steps, warmup, clocks=None):
               f"kernel status {ops.tc_status()}",
               file=sys.stderr, flush=True)
     clock_info = clocks.stop() if clocks else None
+    eng.flush()
     for r in list(reqs):
         if r.request_id in eng.requests:
             eng.scheduler.running.remove(r)
@@ -296,6 +298,7 @@ def run_timeline(eng, B):
     import collections
     from zig_ai_b200.kernels import ops
     ids = decode_requests(eng, B, 40, seed=B)
+    eng.flush()
     reqs = [eng.requests[i] for i in ids]
     runner = eng.runner
     prepared = [runner.prepare_decode([(r.request_id, [(7 * k + j) % 1000], [0]) for j, r in enumerate(reqs)])

@@ -117,3 +117,47 @@ def test_repeated_step_shapes_run_as_graphs_and_agree(tiny_models, dtype):
         traces.check_request(outs[0], want, dtype, f"{dtype} graphed request {k}")
         assert np.array_equal(outs[0], outs[1]) or dtype == "bfloat16" or np.abs(outs[0] - outs[1]).max() < 1e-5
     assert runner.shape_graphs.replays >= 4 and len(runner.shape_graphs.graphs) == 2
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("temperature", [0.0, 0.9])
+def test_a_step_ahead_of_the_host_changes_no_token(tiny_models, dtype, temperature):
+    """With `pipeline` the engine launches a decode step before it has read the tokens of the step
+    before.  Same tokens as without it: requests of different lengths that end at different steps (by
+    their length, and one by an EOS token, whose row of the step launched ahead is dropped), more
+    requests than seats (so that steps with admissions and prompts come between), few pages."""
+    import zig_ai_b200 as z
+    name = "B"
+    g = random.Random(11)
+    V = TINY[name][0]["vocab_size"]
+    prompts = [[g.randrange(V) for _ in range(n)] for n in (9, 3, 21, 5, 14, 2)]
+    news = [12, 30, 7, 19, 25, 9]
+
+    def run(pipeline, eos_of=None):
+        eng = z.Engine(tiny_models[name], dtype, max_num_seqs=3, max_batched_tokens=16, max_model_len=64,
+                       max_tokens=3 * 64, page_size=PAGE_SIZE[name], pipeline=pipeline)
+        ids = [eng.add_request(p, z.SamplingParams(temperature=temperature, top_k=40, seed=5 + i, max_new_tokens=n,
+                                                   eos_id=(eos_of[i] if eos_of else None)))
+               for i, (p, n) in enumerate(zip(prompts, news))]
+        done = {}
+        while eng.has_work():
+            for r in eng.step():
+                done[r.request_id] = r
+        eng.flush()
+        return [done[i].output for i in ids], [done[i].finish_reason for i in ids], eng.stats()
+
+    base, reasons, _ = run(False)
+    assert [len(o) for o in base] == news and set(reasons) == {"length"}
+    got, _, stats = run(True)
+    assert got == base and stats["steps_ahead"] >= 3
+    # an EOS token in the middle of three outputs: the token that the plain run produced there
+    eos = [None, base[1][11], None, base[3][6], base[4][20], None]
+    want = [o if e is None else o[:o.index(e) + 1] for o, e in zip(base, eos)]
+    base_eos, reasons, _ = run(False, eos)
+    assert reasons[1] == reasons[3] == reasons[4] == "eos"
+    if dtype == "float32":            # (in bfloat16 a sampled token may depend on what else was in its step's batch)
+        assert base_eos == want
+    else:
+        assert [o[-1] for o in base_eos] == [w[-1] if e is None else e for w, e in zip(base_eos, eos)]
+    got, reasons, stats = run(True, eos)
+    assert got == base_eos and reasons[1] == "eos" and stats["steps_ahead"] >= 1

@@ -6,6 +6,12 @@ sequence to the scheduler, runs its prompt in chunks, samples, and loops decode 
 second (:1353-1368).  `Engine` does the same for many requests at once: each `step()` asks the
 scheduler for a plan, runs it through the step function, samples on the device and hands the
 tokens back to the scheduler.
+
+While every running request is decoding, the engine keeps one step ahead of the host: the next
+step is launched with its input tokens still on the device (the ids the sampling kernel of the
+step before wrote), and only then are that earlier step's ids read back, so planning, packing and
+the read-back overlap the device's work.  A request that turns out to have ended (an EOS token) has
+one row computed in vain, which is dropped.
 """
 from __future__ import annotations
 
@@ -16,15 +22,16 @@ import torch
 
 from ..sampling.sampler import Sampler, SamplingParams
 from .runner import ModelRunner, load_runner
-from .scheduler import Request, Scheduler, StepPlan
+from .scheduler import RUNNING, PlanEntry, Request, Scheduler, StepPlan
 
 
 class Engine:
     def __init__(self, model_dir: str, dtype="bfloat16", max_num_seqs: int = 64, max_batched_tokens: int = 2048,
                  max_model_len: Optional[int] = None, max_tokens: Optional[int] = None, page_size: int = 64,
-                 device=None, ops=None):
+                 device=None, ops=None, pipeline: bool = True):
         """`max_tokens`: positions the cache pool holds in all (default: room for `max_num_seqs`
-        requests of `max_model_len`, capped at 1 Mi positions)."""
+        requests of `max_model_len`, capped at 1 Mi positions).  `pipeline`: keep one decode step
+        ahead of the host (a step's tokens are then handed out by the `step()` call after it)."""
         from ..config import load_config
         cfg = load_config(model_dir)
         model_max = getattr(cfg, "max_position_embeddings", 1 << 30)
@@ -39,6 +46,12 @@ class Engine:
                                    owner=self.runner)
         self.sampler = Sampler(self.runner.ops, self.runner.device)
         self._next_id = 0
+        self.pipeline = bool(pipeline)
+        self._inflight = None             # a launched step not read back yet: (plan, requests in row order, ids on the
+        #                                   device, their pinned host copy, the event after that copy)
+        self._host_ids: List[torch.Tensor] = []
+        self._host_turn = 0
+        self.n_lookahead = 0
         self.requests: Dict[object, Request] = {}
         self.n_steps = 0
         self.n_prompt_tokens = 0
@@ -64,24 +77,105 @@ class Engine:
         return self.scheduler.has_work()
 
     # ------------------------------------------------------------------ one step
-    def step(self) -> List[Request]:
-        """Plan, run and sample one step; returns the requests that ended in it."""
-        plan: StepPlan = self.scheduler.schedule()
-        ended = list(plan.failed)
-        if plan.entries:
-            entries = [(e.request.request_id, e.tokens, [len(e.tokens) - 1] if e.sample else []) for e in plan.entries]
-            logits = self.runner.step(entries, trusted=True)
-            wanting = [e.request for e in plan.entries if e.sample]
-            ids = self.sampler.sample(logits, [r.params for r in wanting], [len(r.output) for r in wanting],
-                                      [r.output for r in wanting])
-            sampled = {r.request_id: t for r, t in zip(wanting, ids)}
-            self.n_steps += 1
-            self.n_generated += len(ids)
-            self.n_prompt_tokens += plan.n_tokens
-            ended += self.scheduler.commit(plan, sampled)
+    def _launch(self, plan: StepPlan, device_tokens: Optional[torch.Tensor] = None):
+        """Run the plan's step and its sampling kernel; nothing is read back."""
+        entries = [(e.request.request_id, e.tokens, [len(e.tokens) - 1] if e.sample else []) for e in plan.entries]
+        logits = self.runner.step(entries, trusted=True, device_tokens=device_tokens)
+        wanting = [e.request for e in plan.entries if e.sample]
+        ahead = 1 if device_tokens is not None else 0         # one token of each output is still on the device
+        ids = self.sampler.sample_device(logits, [r.params for r in wanting], [len(r.output) + ahead for r in wanting],
+                                         [r.output for r in wanting])
+        # the copy to the host is queued now, before any later step's kernels, so that reading it
+        # waits for this step only
+        if ids.device.type != "cuda":
+            return plan, wanting, ids, ids, None
+        if not self._host_ids:
+            self._host_ids = [torch.empty((max(self.scheduler.max_num_seqs, 1),), dtype=torch.int32).pin_memory()
+                              for _ in range(4)]
+        host = self._host_ids[self._host_turn % len(self._host_ids)]
+        self._host_turn += 1
+        n = int(ids.shape[0])
+        if n > host.shape[0]:
+            host = torch.empty((n,), dtype=torch.int32).pin_memory()
+        host[:n].copy_(ids, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        return plan, wanting, ids, host, done
+
+    def _collect(self, launched) -> List[Request]:
+        """Read a launched step's token ids and hand them to the scheduler; returns the requests that ended."""
+        plan, wanting, _ids_dev, host, done = launched
+        if done is not None:
+            done.synchronize()
+        ids = host[:len(wanting)].tolist()
+        # rows of requests that ended while this step was already on its way count for nothing
+        plan.entries = [e for e in plan.entries if e.request.status == RUNNING]
+        sampled = {r.request_id: t for r, t in zip(wanting, ids) if r.status == RUNNING}
+        self.n_steps += 1
+        self.n_generated += len(sampled)
+        self.n_prompt_tokens += plan.n_tokens
+        return self.scheduler.commit(plan, sampled)
+
+    def _decoding_only(self, plan: StepPlan) -> bool:
+        sch = self.scheduler
+        return (not sch.waiting and not plan.preempted and not plan.failed and len(plan.entries) == len(sch.running)
+                and all(e.sample and len(e.tokens) == 1 and e.request.params.repetition_penalty == 1.0
+                        for e in plan.entries)
+                and self.runner.can_take_device_tokens(len(plan.entries)))
+
+    def _plan_ahead(self, launched) -> Optional[StepPlan]:
+        """The step after `launched` (whose tokens are not known yet), if it can be planned without
+        them: every request decodes on, none can end other than by an EOS token, pages are free."""
+        plan = launched[0]
+        if not self._decoding_only(plan) or len(plan.entries) > self.scheduler.max_batched_tokens:
+            return None
+        cache = self.scheduler.cache
+        for e in plan.entries:
+            r, p = e.request, e.request.params
+            if len(r.output) + 1 >= p.max_new_tokens or len(r.prompt) + len(r.output) + 1 >= self.max_model_len:
+                return None                                    # the launched step's token is its last
+        for e in plan.entries:
+            r = e.request
+            if not cache.can_reserve(r.request_id, r.computed + 2):
+                return None                                    # the scheduler decides who makes room
+            cache.reserve(r.request_id, r.computed + 2)
+        return StepPlan(entries=[PlanEntry(e.request, [0], True) for e in plan.entries])
+
+    def flush(self) -> List[Request]:
+        """Read back a step that is still on its way, if any; returns the requests that ended in it."""
+        if self._inflight is None:
+            return []
+        launched, self._inflight = self._inflight, None
+        return self._retire(self._collect(launched))
+
+    def _retire(self, ended: List[Request]) -> List[Request]:
         for r in ended:
             self.requests.pop(r.request_id, None)
         return ended
+
+    def step(self) -> List[Request]:
+        """Plan, run and sample one step; returns the requests that ended (with `pipeline`, those
+        that ended in the step launched by the call before)."""
+        ended: List[Request] = []
+        if self._inflight is not None:
+            launched, self._inflight = self._inflight, None
+            plan_ahead = self._plan_ahead(launched)
+            if plan_ahead is not None:
+                ahead = self._launch(plan_ahead, device_tokens=launched[2])
+                self.n_lookahead += 1
+                ended = self._collect(launched)
+                self._inflight = ahead
+                return self._retire(ended)
+            ended = self._collect(launched)                    # and plan the next step with its tokens known
+        plan: StepPlan = self.scheduler.schedule()
+        ended += plan.failed
+        if plan.entries:
+            launched = self._launch(plan)
+            if self.pipeline and self._decoding_only(plan):
+                self._inflight = launched                      # read back by the next call
+            else:
+                ended += self._collect(launched)
+        return self._retire(ended)
 
     # ------------------------------------------------------------------ whole generation
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 128, temperature: float = 0.0,
@@ -100,6 +194,7 @@ class Engine:
                 done[r.request_id] = r
             if not self.has_work() and len(done) < len(ids):
                 raise RuntimeError("the scheduler stopped with requests unfinished")
+        self.flush()                                           # a step launched ahead for requests that have ended
         failed = [done[i] for i in ids if done[i].finish_reason == "out_of_pages"]
         if failed:
             raise RuntimeError(f"{len(failed)} request(s) could not be served: out of pages")
@@ -108,6 +203,7 @@ class Engine:
     def stats(self) -> dict:
         out = dict(self.runner.cache.stats())
         out.update(steps=self.n_steps, generated=self.n_generated, tokens_run=self.n_prompt_tokens,
+                   steps_ahead=self.n_lookahead,
                    preemptions=self.scheduler.n_preemptions, running=len(self.scheduler.running),
                    waiting=len(self.scheduler.waiting))
         return out

@@ -222,10 +222,14 @@ class DecodeGraphs:
             self.ops.launches += self.launches_per_replay[B]
         return logits[:n]
 
-    def run(self, spans, tables) -> torch.Tensor:
+    def run(self, spans, tables, device_tokens: torch.Tensor = None) -> torch.Tensor:
+        """`device_tokens` (int32 [rows], on the device): the rows' tokens, taken instead of the ones
+        in `spans`, for a caller whose tokens are still on the device."""
         B = self.bucket(len(spans))
         graph, static, logits = self.graphs.get(B) or self._capture(B)
         static.fill(spans, tables)
+        if device_tokens is not None:
+            static.tok[1][:len(spans)].copy_(device_tokens)
         graph.replay()
         self.replays += 1
         if hasattr(self.ops, "launches"):

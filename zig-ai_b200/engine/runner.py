@@ -131,16 +131,24 @@ class ModelRunner:
         self.tokens_run += prepared[1]
         return self.graphs.run_prepared(prepared)
 
-    def step(self, entries, trusted: bool = False) -> torch.Tensor:
+    def can_take_device_tokens(self, n_rows: int) -> bool:
+        """Whether a step of `n_rows` single tokens may get its tokens from a device tensor."""
+        return bool(self.use_graphs and self.graphs.bucket(n_rows) is not None)
+
+    def step(self, entries, trusted: bool = False, device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """entries: (request, its next tokens, wanted places among them).  Returns 32-bit logits
         [wanted, vocab] in the order of the entries and of their wanted places.  (A step that ran
-        as a CUDA graph returns a view of that graph's output buffer, valid until the next such step.)"""
+        as a CUDA graph returns a view of that graph's output buffer, valid until the next such step.)
+        `device_tokens`: for a step of single tokens, the tokens as an int32 device tensor in the
+        order of the entries; the tokens in `entries` are then placeholders."""
         spans, tables = self._reserve(entries, trusted)
         n_tokens = sum(len(e[1]) for e in entries)
         graphed = (self.use_graphs and n_tokens == len(entries) and self.graphs.bucket(len(entries)) is not None
                    and all(len(e[2]) <= 1 for e in entries))
+        if device_tokens is not None and not graphed:
+            raise StepError("tokens from the device need a step of single tokens on the graph path")
         if graphed:
-            full = self.graphs.run(spans, tables)            # logits of every row
+            full = self.graphs.run(spans, tables, device_tokens)            # logits of every row
             keep = [i for i, e in enumerate(entries) if len(e[2]) == 1]
             if len(keep) == len(entries):
                 logits = full

@@ -67,9 +67,16 @@ class Sampler:
                histories: Sequence[Sequence[int]]) -> List[int]:
         """`indices[r]` is the index of the token being sampled in row r's output; `histories[r]`
         the tokens generated so far (used by the repetition penalty only)."""
+        if logits.shape[0] == 0:
+            return []
+        return self.sample_device(logits, params, indices, histories).tolist()
+
+    def sample_device(self, logits: torch.Tensor, params: Sequence[SamplingParams], indices: Sequence[int],
+                      histories: Sequence[Sequence[int]]) -> torch.Tensor:
+        """As `sample`, but the token ids stay on the device (int32 [rows]); nothing waits for them."""
         R = logits.shape[0]
         if R == 0:
-            return []
+            return torch.empty((0,), dtype=torch.int32, device=self.device)
         if any(p.repetition_penalty != 1.0 for p in params):
             toks, counts, offsets, pens = [], [], [0], []
             for p, hist in zip(params, histories):
@@ -95,4 +102,4 @@ class Sampler:
             top_p = torch.tensor([p.top_p for p in params], dtype=torch.float32, device=dev)
             u = torch.tensor([uniform(p.seed, i) for p, i in zip(params, indices)], dtype=torch.float32, device=dev)
             ids = self.ops.sample(logits, temperature, top_k, top_p, u)
-        return ids.tolist()
+        return ids
