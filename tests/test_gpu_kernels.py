@@ -57,7 +57,8 @@ def test_embed_and_gather(dtype, N, H, V):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("N,H,eps", [(5, 96, 1e-6), (3, 1000, 1e-5), (17, 4104, 1e-3), (1, 64, 1e-5)])
+@pytest.mark.parametrize("N,H,eps", [(5, 96, 1e-6), (3, 1000, 1e-5), (17, 4104, 1e-3), (1, 64, 1e-5),
+                                     (70, 1024, 1e-5), (100, 1000, 1e-6), (65, 2048, 1e-5), (64, 1540, 1e-3), (300, 96, 1e-5)])
 def test_add_rmsnorm(dtype, N, H, eps):
     o = ops()
     g = torch.Generator().manual_seed(2)
@@ -106,7 +107,8 @@ def test_short_conv_spans_and_state(dtype, C, L, bias):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("Hq,Hkv,D,rot,ps", [(4, 2, 16, 16, 16), (3, 1, 32, 32, 8), (5, 5, 48, 24, 4),
-                                              (6, 2, 80, 80, 32), (16, 8, 64, 64, 16)])
+                                              (6, 2, 80, 80, 32), (16, 8, 64, 64, 16), (2, 1, 128, 128, 16),
+                                              (3, 3, 256, 256, 8)])
 def test_qk_norm_rope_and_page_write(dtype, Hq, Hkv, D, rot, ps):
     o = ops()
     g = torch.Generator().manual_seed(6)

@@ -104,6 +104,117 @@ __global__ void qk_norm_rope_kernel(const T* __restrict__ qkv, int qkv_cols, con
     }
 }
 
+// bfloat16, the whole head rotated (rot == D), D = 8 * TPH with TPH a power of two up to 32: TPH threads
+// share a head, each with four values of the lower half and their four partners of the upper half,
+// and ask for everything they need (the row, the norm's weight, cosines and sines) at once.
+template <int TPH>
+__global__ void __launch_bounds__(256) qk_norm_rope_vec_kernel(
+    const bf16* __restrict__ qkv, int qkv_cols, const float* __restrict__ q_gamma, const float* __restrict__ k_gamma,
+    float eps, const float2* __restrict__ cs_table, const int* __restrict__ positions, const int* __restrict__ seq_idx,
+    const int* __restrict__ block_table, int table_width, bf16* __restrict__ pages, int page_size,
+    bf16* __restrict__ q_out, bf16* __restrict__ k_out, int N, int Hq, int Hkv, int has_kv, int write) {
+    constexpr int D = 8 * TPH, half = 4 * TPH;
+    pdl_trigger();
+    pdl_wait();
+    const int n_heads = Hq + (has_kv ? 2 * Hkv : 0);
+    const long long item = (long long)blockIdx.x * (256 / TPH) + threadIdx.x / TPH;
+    if (item >= (long long)N * n_heads) return;                    // (a whole group of TPH lanes leaves together)
+    const int t = (int)(item / n_heads), h = (int)(item % n_heads), d0 = (threadIdx.x % TPH) * 4;
+    const bf16* x = qkv + (size_t)t * qkv_cols + (size_t)h * D;
+    const uint2 lo2 = *reinterpret_cast<const uint2*>(x + d0), hi2 = *reinterpret_cast<const uint2*>(x + half + d0);
+    const bool is_q = h < Hq, is_v = h >= Hq + Hkv;
+    size_t page_base = 0;
+    int off = 0;
+    if (!is_q && write) {
+        const int pos = positions[t];
+        const int page = block_table[(size_t)seq_idx[t] * table_width + pos / page_size];
+        off = pos % page_size;
+        page_base = (size_t)page * 2 * Hkv * page_size * D;
+    }
+    if (is_v) {
+        if (write) {
+            bf16* dst = pages + page_base + (((size_t)Hkv + (h - Hq - Hkv)) * page_size + off) * D;
+            *reinterpret_cast<uint2*>(dst + d0) = lo2;
+            *reinterpret_cast<uint2*>(dst + half + d0) = hi2;
+        }
+        return;
+    }
+    const float* gamma = is_q ? q_gamma : k_gamma;
+    float4 glo = make_float4(1.f, 1.f, 1.f, 1.f), ghi = glo;
+    if (gamma) {
+        glo = *reinterpret_cast<const float4*>(gamma + d0);
+        ghi = *reinterpret_cast<const float4*>(gamma + half + d0);
+    }
+    const float4 cs01 = *reinterpret_cast<const float4*>(cs_table + (size_t)t * half + d0);        // (cos, sin) of d0, d0+1
+    const float4 cs23 = *reinterpret_cast<const float4*>(cs_table + (size_t)t * half + d0 + 2);
+    float lo[4], hi[4];
+    {
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&lo2.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&lo2.y));
+        const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&hi2.x));
+        const float2 d = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&hi2.y));
+        lo[0] = a.x; lo[1] = a.y; lo[2] = b.x; lo[3] = b.y;
+        hi[0] = c.x; hi[1] = c.y; hi[2] = d.x; hi[3] = d.y;
+    }
+    if (gamma) {
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) ss += lo[e] * lo[e] + hi[e] * hi[e];
+#pragma unroll
+        for (int o = TPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float inv = rsqrtf(ss / (float)D + eps);
+        const float gl[4] = {glo.x, glo.y, glo.z, glo.w}, gh[4] = {ghi.x, ghi.y, ghi.z, ghi.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            lo[e] = lo[e] * inv * gl[e];
+            hi[e] = hi[e] * inv * gh[e];
+        }
+    }
+    const float cs[4] = {cs01.x, cs01.z, cs23.x, cs23.z}, sn[4] = {cs01.y, cs01.w, cs23.y, cs23.w};
+    float rl[4], rh[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        rl[e] = lo[e] * cs[e] - hi[e] * sn[e];
+        rh[e] = lo[e] * sn[e] + hi[e] * cs[e];
+    }
+    uint2 ol, oh;
+    {
+        __nv_bfloat162 a = __floats2bfloat162_rn(rl[0], rl[1]), b = __floats2bfloat162_rn(rl[2], rl[3]);
+        __nv_bfloat162 c = __floats2bfloat162_rn(rh[0], rh[1]), d = __floats2bfloat162_rn(rh[2], rh[3]);
+        ol.x = *reinterpret_cast<uint32_t*>(&a); ol.y = *reinterpret_cast<uint32_t*>(&b);
+        oh.x = *reinterpret_cast<uint32_t*>(&c); oh.y = *reinterpret_cast<uint32_t*>(&d);
+    }
+    if (is_q) {
+        bf16* dst = q_out + ((size_t)t * Hq + h) * D;
+        *reinterpret_cast<uint2*>(dst + d0) = ol;
+        *reinterpret_cast<uint2*>(dst + half + d0) = oh;
+    } else {
+        if (write) {
+            bf16* dst = pages + page_base + ((size_t)(h - Hq) * page_size + off) * D;
+            *reinterpret_cast<uint2*>(dst + d0) = ol;
+            *reinterpret_cast<uint2*>(dst + half + d0) = oh;
+        }
+        if (k_out) {
+            bf16* dst = k_out + ((size_t)t * Hkv + (h - Hq)) * D;
+            *reinterpret_cast<uint2*>(dst + d0) = ol;
+            *reinterpret_cast<uint2*>(dst + half + d0) = oh;
+        }
+    }
+}
+
+template <int TPH>
+static int launch_qk_vec(const void* qkv, int qkv_cols, const float* q_gamma, const float* k_gamma, float eps,
+                         const float2* cs_table, const int* positions, const int* seq_idx, const int* block_table,
+                         int table_width, void* pages, int page_size, void* q_out, void* k_out, int N, int Hq, int Hkv,
+                         int has_kv, int write, cudaStream_t stream) {
+    const long long items = (long long)N * (Hq + (has_kv ? 2 * Hkv : 0));
+    const long long blocks = (items + 256 / TPH - 1) / (256 / TPH);
+    if (blocks > 0x7fffffffLL) return ZAI_BAD_SIZE;
+    return launch_pdl(qk_norm_rope_vec_kernel<TPH>, dim3((unsigned)blocks), dim3(256), 0, stream, (const bf16*)qkv, qkv_cols,
+                      q_gamma, k_gamma, eps, cs_table, positions, seq_idx, block_table, table_width, (bf16*)pages, page_size,
+                      (bf16*)q_out, (bf16*)k_out, N, Hq, Hkv, has_kv, write);
+}
+
 // Writes already prepared k and v rows ([N, Hkv*D], row strides given) into the pages.
 template <typename T>
 __global__ void kv_write_kernel(const T* __restrict__ k, int k_stride, const T* __restrict__ v, int v_stride,
@@ -138,6 +249,16 @@ ZAI_API int zai_qk_norm_rope(const void* qkv, int qkv_cols, int dtype, const flo
                              cudaStream_t stream) {
     if (N <= 0) return ZAI_OK;
     if (rot < 0 || rot > D || (rot & 1) || D < 1) return ZAI_BAD_SIZE;
+    // the vector kernel: bfloat16, the whole head rotated, 16-byte aligned rows and tables
+    const uintptr_t all = reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_gamma) | reinterpret_cast<uintptr_t>(k_gamma) |
+                          reinterpret_cast<uintptr_t>(cs_table) | reinterpret_cast<uintptr_t>(pages) |
+                          reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_out);
+    if (dtype == ZAI_BF16 && rot == D && (D & 7) == 0 && (qkv_cols & 7) == 0 && (all & 15) == 0) {
+#define ZAI_QK_VEC(tph) if (D == 8 * tph) return launch_qk_vec<tph>(qkv, qkv_cols, q_gamma, k_gamma, eps, cs_table, positions, \
+        seq_idx, block_table, table_width, pages, page_size, q_out, k_out, N, Hq, Hkv, has_kv, write, stream);
+        ZAI_QK_VEC(2) ZAI_QK_VEC(4) ZAI_QK_VEC(8) ZAI_QK_VEC(16) ZAI_QK_VEC(32)
+#undef ZAI_QK_VEC
+    }
     const int threads = 128;
     const size_t smem = (size_t)(rot + (threads / 32) * D) * sizeof(float);
     if (smem > 48 * 1024) return ZAI_BAD_SIZE;

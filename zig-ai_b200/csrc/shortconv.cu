@@ -97,6 +97,121 @@ __global__ void conv_rows_bf16x8_kernel(bf16* __restrict__ z, const bf16* __rest
     *reinterpret_cast<uint4*>(z + (size_t)t * C + c) = o4;
 }
 
+// bfloat16, C a multiple of 8, L taps (1..4): one thread per (4 consecutive rows, 8 channels).  The
+// rows' B, C and x~ (twelve 16-byte loads) are asked for at once; the products u = B x~ of earlier
+// rows stay in registers while the thread walks down its rows, so a row is read once; only a
+// thread's first row (or a row that starts a request's span) fetches its L - 1 predecessors or the
+// request's state.
+#define CONV_R 4
+template <int L>
+__global__ void __launch_bounds__(128) conv_rows_bf16x8_walk_kernel(
+    bf16* __restrict__ z, const bf16* __restrict__ bcx, const float* __restrict__ w, const float* __restrict__ bias,
+    const float* __restrict__ state, const int* __restrict__ seq_idx, const int* __restrict__ cu_q,
+    const int* __restrict__ slot_ids, int N, int C, int state_rows) {
+    pdl_trigger();
+    pdl_wait();
+    const int t0 = blockIdx.x * CONV_R;
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+    if (c >= C || t0 >= N) return;
+    const int rows = min(CONV_R, N - t0);
+    uint4 b4[CONV_R], g4[CONV_R], x4[CONV_R];
+    int sq[CONV_R];
+#pragma unroll
+    for (int r = 0; r < CONV_R; ++r) {
+        if (r < rows) {
+            const bf16* row = bcx + (size_t)(t0 + r) * 3 * C + c;
+            b4[r] = *reinterpret_cast<const uint4*>(row);
+            g4[r] = *reinterpret_cast<const uint4*>(row + C);
+            x4[r] = *reinterpret_cast<const uint4*>(row + 2 * C);
+            sq[r] = seq_idx[t0 + r];
+        }
+    }
+    float wt[8][L], bs[8];
+    {
+        float flat[8 * L];
+#pragma unroll
+        for (int q = 0; q < 2 * L; ++q) {
+            const float4 v = *reinterpret_cast<const float4*>(w + (size_t)c * L + 4 * q);
+            flat[4 * q] = v.x; flat[4 * q + 1] = v.y; flat[4 * q + 2] = v.z; flat[4 * q + 3] = v.w;
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+#pragma unroll
+            for (int j = 0; j < L; ++j) wt[e][j] = flat[e * L + j];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) bs[e] = bias ? bias[c + e] : 0.f;
+    }
+    float hist[L > 1 ? L - 1 : 1][8];                         // u of the L-1 rows before the current one, oldest first
+    int prev_seq = -1;
+#pragma unroll
+    for (int r = 0; r < CONV_R; ++r) {
+        if (r >= rows) break;
+        const int t = t0 + r, s = sq[r];
+        const int i = t - cu_q[s];                                // the row's place in its span
+        if (L > 1 && (s != prev_seq || i == 0)) {                // (re)build the history: earlier rows, or the state
+            const float* st = state + ((size_t)slot_ids[s] * state_rows) * C;
+#pragma unroll
+            for (int j = 0; j < L - 1; ++j) {
+                const int rr = i + j - (L - 1);
+                if (rr >= 0) {
+                    const bf16* row = bcx + (size_t)(t - i + rr) * 3 * C + c;
+                    const uint4 pb = *reinterpret_cast<const uint4*>(row), px = *reinterpret_cast<const uint4*>(row + 2 * C);
+                    const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&pb);
+                    const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&px);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 b = __bfloat1622float2(bp[e]), x = __bfloat1622float2(xp[e]);
+                        hist[j][2 * e] = b.x * x.x;
+                        hist[j][2 * e + 1] = b.y * x.y;
+                    }
+                } else {
+                    const float4 a = *reinterpret_cast<const float4*>(st + (size_t)(i + j) * C + c);
+                    const float4 b = *reinterpret_cast<const float4*>(st + (size_t)(i + j) * C + c + 4);
+                    hist[j][0] = a.x; hist[j][1] = a.y; hist[j][2] = a.z; hist[j][3] = a.w;
+                    hist[j][4] = b.x; hist[j][5] = b.y; hist[j][6] = b.z; hist[j][7] = b.w;
+                }
+            }
+        }
+        prev_seq = s;
+        float u[8];
+        {
+            const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&b4[r]);
+            const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&x4[r]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 b = __bfloat1622float2(bp[e]), x = __bfloat1622float2(xp[e]);
+                u[2 * e] = b.x * x.x;
+                u[2 * e + 1] = b.y * x.y;
+            }
+        }
+        float y[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            y[e] = bs[e];
+#pragma unroll
+            for (int j = 0; j < L - 1; ++j) y[e] += wt[e][j] * hist[j][e];
+            y[e] += wt[e][L - 1] * u[e];
+        }
+        const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g4[r]);
+        uint4 o4;
+        __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 gte = __bfloat1622float2(gp[e]);
+            op[e] = __floats2bfloat162_rn(gte.x * y[2 * e], gte.y * y[2 * e + 1]);
+        }
+        *reinterpret_cast<uint4*>(z + (size_t)t * C + c) = o4;
+#pragma unroll
+        for (int j = 0; j + 1 < L - 1; ++j)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) hist[j][e] = hist[j + 1][e];
+        if (L > 1) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) hist[L - 2][e] = u[e];
+        }
+    }
+}
+
 template <typename T>
 __global__ void conv_state_kernel(const T* __restrict__ bcx, float* __restrict__ state,
                                   const int* __restrict__ cu_q, const int* __restrict__ slot_ids,
@@ -168,10 +283,18 @@ ZAI_API int zai_short_conv(void* z, const void* bcx, int dtype, const float* w, 
             (T*)z, (const T*)bcx, w, bias, state, slot_ids, C, L, state_rows, write_state));
     }
     int e = 0;
-    if (dtype == ZAI_BF16 && (C & 7) == 0) {
+    const bool aligned = ((reinterpret_cast<uintptr_t>(z) | reinterpret_cast<uintptr_t>(bcx) | reinterpret_cast<uintptr_t>(w) |
+                           reinterpret_cast<uintptr_t>(state)) & 15) == 0;
+    if (dtype == ZAI_BF16 && (C & 7) == 0 && aligned) {
         const int c8 = C / 8, th = c8 < 128 ? ((c8 + 31) / 32) * 32 : 128;
-        e = launch_pdl(conv_rows_bf16x8_kernel, dim3(N, (c8 + th - 1) / th), dim3(th), 0, stream, (bf16*)z, (const bf16*)bcx, w,
-                       bias, (const float*)state, seq_idx, cu_q, slot_ids, C, L, state_rows);
+        const dim3 walk((N + CONV_R - 1) / CONV_R, (c8 + th - 1) / th);
+#define ZAI_CONV_WALK(l) if (L == l) e = launch_pdl(conv_rows_bf16x8_walk_kernel<l>, walk, dim3(th), 0, stream, (bf16*)z, \
+        (const bf16*)bcx, w, bias, (const float*)state, seq_idx, cu_q, slot_ids, N, C, state_rows);
+        ZAI_CONV_WALK(1) ZAI_CONV_WALK(2) ZAI_CONV_WALK(3) ZAI_CONV_WALK(4)
+#undef ZAI_CONV_WALK
+        if (L > 4)
+            e = launch_pdl(conv_rows_bf16x8_kernel, dim3(N, (c8 + th - 1) / th), dim3(th), 0, stream, (bf16*)z, (const bf16*)bcx, w,
+                           bias, (const float*)state, seq_idx, cu_q, slot_ids, C, L, state_rows);
     } else
     ZAI_DISPATCH(dtype, e = launch_pdl(conv_rows_kernel<T>, dim3(N, bx), dim3(threads), 0, stream,
         (T*)z, (const T*)bcx, w, bias, (const float*)state, seq_idx, cu_q, slot_ids, C, L, state_rows));
