@@ -174,6 +174,28 @@ def test_paged_attention_mixed_spans(dtype, impl, Hq, Hkv, D, ps, window):
     assert torch.allclose(a.float(), b.float(), **tol(dtype))
 
 
+@pytest.mark.parametrize("impl", ["tcgen05", "mma"])
+@pytest.mark.parametrize("Hq,Hkv,ps,window", [(16, 8, 16, None), (4, 1, 64, None), (2, 2, 8, 100), (6, 3, 128, None),
+                                              (3, 1, 32, 300)])
+def test_span_attention_head_size_64(impl, Hq, Hkv, ps, window):
+    """The two span kernels for head size 64 (tcgen05 with TMEM accumulators, and mma.sync): spans of
+    1 to 400 rows (more than three blocks of 128 query rows) at contexts of 0, inside a page, and over
+    a thousand keys (many key tiles), with and without a window; the status word stays clear."""
+    o = ops()
+    dtype, D = torch.bfloat16, 64
+    g = torch.Generator().manual_seed(28)
+    ctx, q_lens = [0, ps - 1, 1100, 301, 5, 127, 640], [400, 2, 130, 1, 37, 129, 128]
+    num_pages = (sum(c + n for c, n in zip(ctx, q_lens)) // ps) + 16
+    step = make_step(o, dtype, ctx, q_lens, ps, num_pages, 29)
+    pages = fill_pages(step, ctx, q_lens, ps, Hkv, D, dtype, num_pages, g)
+    q = torch.randn(sum(q_lens), Hq * D, generator=g).to(dtype).cuda()
+    view = CacheView(0, pages, step.block_tables[0], ps)
+    a = o.paged_attention(q, step, view, Hq, Hkv, D, D ** -0.5, window, impl=impl)
+    b = ref_ops.paged_attention(q, step, view, Hq, Hkv, D, D ** -0.5, window)
+    assert torch.allclose(a.float(), b.float(), **tol(dtype))
+    assert o.tc_status() == 0
+
+
 @pytest.mark.parametrize("Hq,Hkv,D,ps,window", ATT_SHAPES)
 def test_paged_attention_single_tokens(Hq, Hkv, D, ps, window):
     """Every span one token (the split-key kernel in bfloat16): contexts of 0 keys, one short of

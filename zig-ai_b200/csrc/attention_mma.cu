@@ -238,7 +238,7 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_mma_kernel(
             const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
             const float u0 = n0 == -INFINITY ? 0.f : n0 * scale_log2;    // a row with nothing visible yet
             const float u1 = n1 == -INFINITY ? 0.f : n1 * scale_log2;
-            const float c0 = exp2f(m0 * scale_log2 - u0), c1 = exp2f(m1 * scale_log2 - u1);
+            const float c0 = fast_exp2(m0 * scale_log2 - u0), c1 = fast_exp2(m1 * scale_log2 - u1);
             m0 = n0;
             m1 = n1;
             l0 *= c0;
@@ -249,10 +249,10 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_mma_kernel(
             }
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt) {
-                sc[nt][0] = exp2f(sc[nt][0] * scale_log2 - u0);
-                sc[nt][1] = exp2f(sc[nt][1] * scale_log2 - u0);
-                sc[nt][2] = exp2f(sc[nt][2] * scale_log2 - u1);
-                sc[nt][3] = exp2f(sc[nt][3] * scale_log2 - u1);
+                sc[nt][0] = fast_exp2(sc[nt][0] * scale_log2 - u0);
+                sc[nt][1] = fast_exp2(sc[nt][1] * scale_log2 - u0);
+                sc[nt][2] = fast_exp2(sc[nt][2] * scale_log2 - u1);
+                sc[nt][3] = fast_exp2(sc[nt][3] * scale_log2 - u1);
                 l0 += sc[nt][0] + sc[nt][1];
                 l1 += sc[nt][2] + sc[nt][3];
             }
@@ -383,17 +383,17 @@ __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
             mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
             const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);   // finite: the warp has a visible key
             const float u0 = n0 * scale_log2, u1 = n1 * scale_log2;
-            const float c0 = exp2f(m0 * scale_log2 - u0), c1 = exp2f(m1 * scale_log2 - u1);
+            const float c0 = fast_exp2(m0 * scale_log2 - u0), c1 = fast_exp2(m1 * scale_log2 - u1);
             m0 = n0;
             m1 = n1;
 #pragma unroll
             for (int i = 0; i < D / 8; ++i) {
                 o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1;
             }
-            s0[0] = exp2f(s0[0] * scale_log2 - u0); s0[1] = exp2f(s0[1] * scale_log2 - u0);
-            s0[2] = exp2f(s0[2] * scale_log2 - u1); s0[3] = exp2f(s0[3] * scale_log2 - u1);
-            s1[0] = exp2f(s1[0] * scale_log2 - u0); s1[1] = exp2f(s1[1] * scale_log2 - u0);
-            s1[2] = exp2f(s1[2] * scale_log2 - u1); s1[3] = exp2f(s1[3] * scale_log2 - u1);
+            s0[0] = fast_exp2(s0[0] * scale_log2 - u0); s0[1] = fast_exp2(s0[1] * scale_log2 - u0);
+            s0[2] = fast_exp2(s0[2] * scale_log2 - u1); s0[3] = fast_exp2(s0[3] * scale_log2 - u1);
+            s1[0] = fast_exp2(s1[0] * scale_log2 - u0); s1[1] = fast_exp2(s1[1] * scale_log2 - u0);
+            s1[2] = fast_exp2(s1[2] * scale_log2 - u1); s1[3] = fast_exp2(s1[3] * scale_log2 - u1);
             l0 = l0 * c0 + s0[0] + s0[1] + s1[0] + s1[1];
             l1 = l1 * c1 + s0[2] + s0[3] + s1[2] + s1[3];
             uint32_t pf[4];
@@ -439,7 +439,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
             const float mw = wm[w * 16 + r];
-            const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+            const float f = mw == -INFINITY ? 0.f : fast_exp2(mw - M);
             acc += wo[(w * 16 + r) * D + d] * f;
             L += wl[w * 16 + r] * f;
         }
@@ -466,7 +466,7 @@ __global__ void decode_combine_kernel(bf16* __restrict__ out, const float* __res
         for (int c = 0; c < n_chunks; ++c) {
             const float mc = ml[2 * c];
             if (mc == -INFINITY) continue;
-            const float f = exp2f(mc - M);
+            const float f = fast_exp2(mc - M);
             acc += part_o[(bh * n_chunks + c) * D + d] * f;
             L += ml[2 * c + 1] * f;
         }
@@ -612,7 +612,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_fused_kernel(const FusedDecod
             mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
             const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);   // finite: the tile has a visible key
             const float u0 = n0 * a.scale_log2, u1 = n1 * a.scale_log2;
-            const float c0 = exp2f(m0 * a.scale_log2 - u0), c1 = exp2f(m1 * a.scale_log2 - u1);
+            const float c0 = fast_exp2(m0 * a.scale_log2 - u0), c1 = fast_exp2(m1 * a.scale_log2 - u1);
             m0 = n0;
             m1 = n1;
             l0 *= c0;
@@ -623,10 +623,10 @@ __global__ void __launch_bounds__(NTHREADS) decode_fused_kernel(const FusedDecod
             }
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt) {
-                sc[nt][0] = exp2f(sc[nt][0] * a.scale_log2 - u0);
-                sc[nt][1] = exp2f(sc[nt][1] * a.scale_log2 - u0);
-                sc[nt][2] = exp2f(sc[nt][2] * a.scale_log2 - u1);
-                sc[nt][3] = exp2f(sc[nt][3] * a.scale_log2 - u1);
+                sc[nt][0] = fast_exp2(sc[nt][0] * a.scale_log2 - u0);
+                sc[nt][1] = fast_exp2(sc[nt][1] * a.scale_log2 - u0);
+                sc[nt][2] = fast_exp2(sc[nt][2] * a.scale_log2 - u1);
+                sc[nt][3] = fast_exp2(sc[nt][3] * a.scale_log2 - u1);
                 l0 += sc[nt][0] + sc[nt][1];
                 l1 += sc[nt][2] + sc[nt][3];
             }
@@ -649,8 +649,8 @@ __global__ void __launch_bounds__(NTHREADS) decode_fused_kernel(const FusedDecod
         if (has_new && warp == 0) {                             // fold the new key into warp 0's sums
             const float s0 = snew[g], s1 = snew[g + 8];
             const float n0 = fmaxf(m0, s0), n1 = fmaxf(m1, s1);
-            const float c0 = exp2f(m0 * a.scale_log2 - n0 * a.scale_log2), c1 = exp2f(m1 * a.scale_log2 - n1 * a.scale_log2);
-            const float p0 = exp2f(s0 * a.scale_log2 - n0 * a.scale_log2), p1 = exp2f(s1 * a.scale_log2 - n1 * a.scale_log2);
+            const float c0 = fast_exp2(m0 * a.scale_log2 - n0 * a.scale_log2), c1 = fast_exp2(m1 * a.scale_log2 - n1 * a.scale_log2);
+            const float p0 = fast_exp2(s0 * a.scale_log2 - n0 * a.scale_log2), p1 = fast_exp2(s1 * a.scale_log2 - n1 * a.scale_log2);
             m0 = n0;
             m1 = n1;
             l0 = l0 * c0 + (tq == 0 ? p0 : 0.f);                // the row's sum is spread over the four lanes of a quad
@@ -695,7 +695,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_fused_kernel(const FusedDecod
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
                 const float mw = wm[w * 16 + r];
-                const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+                const float f = mw == -INFINITY ? 0.f : fast_exp2(mw - M);
                 acc += wo[(w * 16 + r) * D + d] * f;
                 L += wl[w * 16 + r] * f;
             }
@@ -729,7 +729,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_fused_kernel(const FusedDecod
         for (int c = 0; c < n_chunks; ++c) {
             const float mc = __ldcg(ml + 2 * c);
             if (mc == -INFINITY) continue;
-            const float f = exp2f(mc - M);
+            const float f = fast_exp2(mc - M);
             acc += __ldcg(a.part_o + (bh * n_chunks + c) * D + d) * f;
             L += __ldcg(ml + 2 * c + 1) * f;
         }

@@ -1,0 +1,480 @@
+// Prefill attention for head size 64 on the 5th-generation tensor cores.
+//
+// Same result as prefill_mma_kernel (csrc/attention_mma.cu): causal attention of a step's query rows
+// over their requests' pages (cached positions and the step's own), optionally with a window, by
+// the online-softmax recurrence over tiles of keys (the reference computes the same sums with one
+// thread block per query row, src/cuda/attention_kernels.cu).  What differs is where the products
+// run: a block owns 128 query rows of one head; per tile of 128 keys
+//
+//     S = Q K^T      tcgen05.mma, M = 128 (query rows = TMEM lanes), N = 128 keys, K = 64, into TMEM
+//     P = exp2(..)   four warps, one query row per thread: the row's 128 scores come from TMEM with
+//                    tcgen05.ld (no shuffles: a thread owns its row), P goes to shared memory as the
+//                    next product's A operand (bfloat16, 128-byte swizzle)
+//     O_t = P V      tcgen05.mma, N = 64, K = 128 keys, V read straight from its page layout
+//                    [key][64] as an MN-major operand, accumulated into O in TMEM; the threads
+//                    rescale O there only when a row's reference maximum has to move
+//
+// Q, K and V reach shared memory by TMA (cp.async.bulk.tensor, no multicast), K and V page by page
+// through the block table into two stages.  Roles: warp 0 one lane issues the loads, warp 1 one lane
+// the products, warps 2-5 are the softmax.  The product of the next tile's scores is issued as soon
+// as P of this tile is consumed, so it overlaps the threads' work on O_t.
+// Every wait on an mbarrier is bounded; a block whose wait runs out raises the status word, its roles
+// leave their loops, TMEM is freed and the block returns.
+#include <cuda.h>
+#include "common.cuh"
+
+#define AT_D 64
+#define AT_BM 128
+#define AT_BN 128
+#define AT_THREADS 192
+#define AT_STAGES 2
+#define AT_SPIN_LIMIT 4000000
+#define AT_Q_BYTES (AT_BM * AT_D * 2)                 // 16 KB
+#define AT_KV_BYTES (2 * AT_BN * AT_D * 2)            // keys then values: 32 KB
+#define AT_P_BYTES (AT_BM * AT_BN * 2)                // 32 KB
+#define AT_TMEM_COLS 256                              // scores in columns 0..127, O in 128..191
+
+__device__ __forceinline__ uint32_t at_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void at_mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(at_smem(bar)), "r"(count));
+}
+__device__ __forceinline__ void at_mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(at_smem(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void at_mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(at_smem(bar)) : "memory");
+}
+__device__ __forceinline__ bool at_mbar_wait(uint64_t* bar, uint32_t parity, volatile int* failed) {
+    const uint32_t a = at_smem(bar);
+    for (int it = 0; it < AT_SPIN_LIMIT; ++it) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(a), "r"(parity) : "memory");
+        if (ok) return true;
+        if (*failed) return false;
+    }
+    *failed = 1;
+    return false;
+}
+__device__ __forceinline__ void at_tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(at_smem(dst)), "l"(map), "r"(at_smem(bar)), "r"(c0), "r"(c1) : "memory");
+}
+// Operand tile of 128-byte rows with the 128-byte swizzle, groups of 8 rows 1024 bytes apart.  For a
+// K-major operand a row is a matrix row (64 k); for an MN-major one a row is one k (64 n).
+__device__ __forceinline__ uint64_t at_desc(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void at_umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void at_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(at_smem(bar)) : "memory");
+}
+__device__ __forceinline__ void at_tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// 2^x by the special-function unit (x <= 0 here; -inf gives 0)
+__device__ __forceinline__ float at_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ void at_tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void at_tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+                   "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+                   "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+                 : "memory");
+}
+
+struct AtArgs {
+    bf16* out;                  // [rows of the step, Hq, 64]
+    const int* block_table;     // [S, table_width]
+    const int* cu_q;            // [S + 1] first row of each request's span
+    const int* ctx_lens;        // [S] positions cached before the step
+    int* status;                // raised to 1 by a block whose wait ran out
+    int table_width, S, page_size, page_shift, Hq, Hkv, window;
+    float scale_log2;
+};
+
+__global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                                const __grid_constant__ CUtensorMap map_kv, const AtArgs a) {
+    // All shared memory is dynamic and the tiles come first: 112 KB of tiles, 128 bytes of barriers and
+    // words, and the 1 KB the system reserves per block make 115,840 bytes, so that two blocks fit
+    // an SM's 233,472 (with a kilobyte of static variables or of alignment slack they would not).
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* base = smem_raw;
+    unsigned char* sQ = base;
+    unsigned char* sKV = base + AT_Q_BYTES;
+    unsigned char* sP = sKV + AT_STAGES * AT_KV_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + AT_P_BYTES);
+    uint64_t& q_full = bars[0];
+    uint64_t* kv_full = bars + 1;                               // [AT_STAGES]
+    uint64_t* kv_empty = bars + 1 + AT_STAGES;                  // [AT_STAGES]
+    uint64_t& s_ready = bars[1 + 2 * AT_STAGES];
+    uint64_t& p_ready = bars[2 + 2 * AT_STAGES];
+    uint64_t& o_ready = bars[3 + 2 * AT_STAGES];
+    uint32_t& tmem_base_holder = *reinterpret_cast<uint32_t*>(bars + 4 + 2 * AT_STAGES);
+    int* words = reinterpret_cast<int*>(bars + 5 + 2 * AT_STAGES);
+    int& failed_flag = words[0];
+    int& s_seq = words[1];
+    int& s_i0 = words[2];
+    volatile int* failed = &failed_flag;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    if (tid == 0) {
+        failed_flag = (at_smem(base) & 1023u) ? 1 : 0;          // the swizzled tiles need 1024-byte alignment
+        at_mbar_init(&q_full, 1);
+        for (int s = 0; s < AT_STAGES; ++s) {
+            at_mbar_init(&kv_full[s], 1);
+            at_mbar_init(&kv_empty[s], 1);
+        }
+        at_mbar_init(&s_ready, 1);
+        at_mbar_init(&p_ready, 4);                              // one arrival per softmax warp
+        at_mbar_init(&o_ready, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(at_smem(&tmem_base_holder)), "r"(AT_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_holder;
+    pdl_trigger();
+    pdl_wait();
+    if (tid == 0) {
+        // blocks are numbered from the last rows of the last request backwards: under the causal
+        // mask later rows have more keys to walk, and the longest blocks should start first
+        int t = gridDim.x - 1 - blockIdx.x, s = 0;
+        for (; s < a.S; ++s) {
+            const int nt = (a.cu_q[s + 1] - a.cu_q[s] + AT_BM - 1) / AT_BM;
+            if (t < nt) break;
+            t -= nt;
+        }
+        s_seq = s;
+        s_i0 = t * AT_BM;
+    }
+    __syncthreads();
+    const int s = s_seq, i0 = s_i0;
+    if (s < a.S && !failed_flag) {
+        const int h = blockIdx.y, hk = h / (a.Hq / a.Hkv);
+        const int row0 = a.cu_q[s], q_len = a.cu_q[s + 1] - row0, ctx = a.ctx_lens[s];
+        const int rows = min(AT_BM, q_len - i0);                    // valid query rows of this block
+        const int kend = ctx + i0 + rows;                           // one past the last visible key of the block
+        const int kbeg = a.window > 0 ? max(ctx + i0 - a.window + 1, 0) : 0;
+        const int tile0 = kbeg / AT_BN, tile1 = (kend + AT_BN - 1) / AT_BN, n_tiles = tile1 - tile0;
+
+        if (warp == 0) {
+            if (lane == 0) {
+                // ---- loads: the block's queries, then a stage of keys and values per tile, page by page
+                const int* table = a.block_table + (size_t)s * a.table_width;
+                const int ps = a.page_size, box_rows = ps < AT_BN ? ps : AT_BN, per_tile = AT_BN / box_rows;
+                at_mbar_expect_tx(&q_full, AT_Q_BYTES);
+                at_tma_load_2d(sQ, &map_q, h * AT_D, row0 + i0, &q_full);
+                int issued = 0;
+                for (int i = 0; i < n_tiles; ++i) {
+                    const int st = i % AT_STAGES;
+                    if (!at_mbar_wait(&kv_empty[st], ((i / AT_STAGES) & 1) ^ 1, failed)) break;
+                    at_mbar_expect_tx(&kv_full[st], AT_KV_BYTES);
+                    unsigned char* dst = sKV + (size_t)st * AT_KV_BYTES;
+                    for (int p = 0; p < per_tile; ++p) {
+                        const int key0 = (tile0 + i) * AT_BN + p * box_rows;
+                        const int idx = key0 >> a.page_shift, off = key0 & (ps - 1);
+                        const int page = idx < a.table_width ? table[idx] : 0;        // beyond the table: the null page
+                        const int krow = ((page * 2 + 0) * a.Hkv + hk) * ps + off;
+                        const int vrow = ((page * 2 + 1) * a.Hkv + hk) * ps + off;
+                        at_tma_load_2d(dst + (size_t)p * box_rows * 128, &map_kv, 0, krow, &kv_full[st]);
+                        at_tma_load_2d(dst + AT_BN * 128 + (size_t)p * box_rows * 128, &map_kv, 0, vrow, &kv_full[st]);
+                    }
+                    issued = i + 1;
+                }
+                if (*failed) {                                  // loads already issued still land here: wait for them
+                    for (int i = max(issued - AT_STAGES, 0); i < issued; ++i) {
+                        const uint32_t addr = at_smem(&kv_full[i % AT_STAGES]);
+                        const uint32_t ph = (i / AT_STAGES) & 1;
+                        for (int spin = 0; spin < AT_SPIN_LIMIT; ++spin) {
+                            uint32_t done;
+                            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                                         : "=r"(done) : "r"(addr), "r"(ph) : "memory");
+                            if (done) break;
+                        }
+                    }
+                    const uint32_t addr = at_smem(&q_full);
+                    for (int spin = 0; spin < AT_SPIN_LIMIT; ++spin) {
+                        uint32_t done;
+                        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                                     : "=r"(done) : "r"(addr), "r"(0u) : "memory");
+                        if (done) break;
+                    }
+                }
+            }
+        } else if (warp == 1) {
+            if (lane == 0) {
+                // ---- products.  Instruction descriptors: D 32-bit, A and B bfloat16, M = 128; the scores
+                // have N = 128 and both operands K-major; O_t has N = 64 and B (the values) MN-major.
+                constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(AT_BN >> 3) << 17) | ((uint32_t)(AT_BM >> 4) << 24);
+                constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(AT_D >> 3) << 17) |
+                                             ((uint32_t)(AT_BM >> 4) << 24);
+                const uint32_t tS = tmem_base, tO = tmem_base + AT_BN;
+                const uint32_t aQ = at_smem(sQ), aP = at_smem(sP);
+                bool ok = at_mbar_wait(&q_full, 0, failed);
+                auto scores = [&](int i) {                      // S = Q K^T of tile i
+                    const int st = i % AT_STAGES;
+                    if (!at_mbar_wait(&kv_full[st], (i / AT_STAGES) & 1, failed)) return false;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t aK = at_smem(sKV + (size_t)st * AT_KV_BYTES);
+#pragma unroll
+                    for (int k = 0; k < AT_D / 16; ++k) at_umma(tS, at_desc(aQ + k * 32), at_desc(aK + k * 32), idesc_s, k > 0 ? 1u : 0u);
+                    at_commit(&s_ready);
+                    return true;
+                };
+                if (ok && n_tiles > 0) ok = scores(0);
+                for (int i = 0; i < n_tiles && ok; ++i) {
+                    const int st = i % AT_STAGES;
+                    ok = at_mbar_wait(&p_ready, i & 1, failed);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t aV = at_smem(sKV + (size_t)st * AT_KV_BYTES + AT_BN * 128);
+#pragma unroll
+                    for (int kk = 0; kk < AT_BN / 16; ++kk)     // 16 keys a step: P 32 bytes along its rows, V two groups of 8 keys
+                        at_umma(tO, at_desc(aP + (kk >> 2) * (AT_BM * 128) + (kk & 3) * 32), at_desc(aV + kk * 2048), idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+                    at_commit(&o_ready);
+                    at_commit(&kv_empty[st]);
+                    if (i + 1 < n_tiles) ok = scores(i + 1);
+                }
+            }
+        } else {
+            // ---- softmax: thread = query row.  O stays in TMEM (the products add to it); the row's
+            // reference maximum is only moved, and O and the sum rescaled, when a tile's maximum exceeds
+            // it by more than 2^8 (P then stays below 256, exact enough in bfloat16 and 32-bit sums; the
+            // result O / l does not depend on the reference).
+            const int qd = warp & 3;                            // this warp's quarter of the TMEM lanes
+            const int row = qd * 32 + lane;
+            const bool valid = row < rows;
+            const int qpos = ctx + i0 + row;                    // the row's position: keys 0..qpos are visible
+            const int klo = a.window > 0 ? max(qpos - a.window + 1, 0) : 0;
+            const uint32_t tS = tmem_base + ((uint32_t)(qd * 32) << 16), tO = tS + AT_BN;
+            const float c = a.scale_log2;
+            float m = -INFINITY, l = 0.f;                       // m: the reference, in units of the scores
+            unsigned char* prow = sP + (size_t)row * 128;
+            bool alive = true;
+            for (int i = 0; i < n_tiles && alive; ++i) {
+                const int key0 = (tile0 + i) * AT_BN;
+                if (!__all_sync(0xffffffffu, at_mbar_wait(&s_ready, i & 1, failed))) { alive = false; break; }    // (the warp leaves together)
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                // keys of this tile that the row sees: [lo, hi)
+                const int lo = valid ? max(klo - key0, 0) : AT_BN, hi = valid ? min(qpos + 1 - key0, AT_BN) : 0;
+                const bool full = lo <= 0 && hi >= AT_BN;       // the row sees the whole tile: no masking needed
+                float mx = -INFINITY;
+#pragma unroll 1
+                for (int c0 = 0; c0 < AT_BN; c0 += 64) {
+                    uint32_t r[2][32];
+                    at_tmem_ld32_nowait(tS + c0, r[0]);
+                    at_tmem_ld32_nowait(tS + c0 + 32, r[1]);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh) {
+                        if (full) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(r[hh][j]));
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (c0 + hh * 32 + j >= lo && c0 + hh * 32 + j < hi) mx = fmaxf(mx, __uint_as_float(r[hh][j]));
+                        }
+                    }
+                }
+                // move the reference?  (warp-wide decision: the TMEM accesses below are the whole warp's)
+                float alpha = 1.f;
+                if (m == -INFINITY) {
+                    m = mx;                                     // nothing summed so far (O and l are 0, or this is the first tile)
+                } else if (mx * c > m * c + 8.f) {
+                    alpha = at_exp2(m * c - mx * c);
+                    m = mx;
+                }
+                if (i > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                    if (!__all_sync(0xffffffffu, at_mbar_wait(&o_ready, (i - 1) & 1, failed))) { alive = false; break; }   // the product before has added to O
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                    for (int c0 = 0; c0 < AT_D; c0 += 32) {
+                        uint32_t r[32];
+                        at_tmem_ld32(tO + c0, r);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
+                        at_tmem_st32(tO + c0, r);
+                    }
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                    l *= alpha;
+                }
+                const float ref = m == -INFINITY ? 0.f : m * c;              // no key seen so far: every p is 0
+                float lt = 0.f;
+#pragma unroll 1
+                for (int c0 = 0; c0 < AT_BN; c0 += 64) {
+                    uint32_t r[2][32];
+                    at_tmem_ld32_nowait(tS + c0, r[0]);
+                    at_tmem_ld32_nowait(tS + c0 + 32, r[1]);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    unsigned char* half = prow + (c0 >> 6) * (AT_BM * 128);  // the half of P that holds these 64 keys
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh) {
+                        uint32_t pk[16];
+                        if (full) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 2) {
+                                const float p0 = at_exp2(__uint_as_float(r[hh][j]) * c - ref), p1 = at_exp2(__uint_as_float(r[hh][j + 1]) * c - ref);
+                                lt += p0 + p1;
+                                __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
+                                pk[j >> 1] = *reinterpret_cast<uint32_t*>(&v);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 2) {
+                                // (a hidden score may be anything, also NaN: it is replaced before the exponential)
+                                const int k0 = c0 + hh * 32 + j;
+                                const float s0 = (k0 >= lo && k0 < hi) ? __uint_as_float(r[hh][j]) * c - ref : -INFINITY;
+                                const float s1 = (k0 + 1 >= lo && k0 + 1 < hi) ? __uint_as_float(r[hh][j + 1]) * c - ref : -INFINITY;
+                                const float p0 = at_exp2(s0), p1 = at_exp2(s1);
+                                lt += p0 + p1;
+                                __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
+                                pk[j >> 1] = *reinterpret_cast<uint32_t*>(&v);
+                            }
+                        }
+                        // 32 keys = four 16-byte pieces of the row
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4)
+                            *reinterpret_cast<uint4*>(half + (((hh * 4 + q4) ^ (row & 7)) << 4)) =
+                                make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+                    }
+                }
+                l += lt;
+                // P is written by these threads and read by the tensor core's (asynchronous) proxy
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) at_mbar_arrive(&p_ready);
+            }
+            if (alive && n_tiles > 0 && __all_sync(0xffffffffu, at_mbar_wait(&o_ready, (n_tiles - 1) & 1, failed))) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const float inv = l > 0.f ? 1.f / l : 0.f;
+                bf16* dst = a.out + ((size_t)(row0 + i0 + row) * a.Hq + h) * AT_D;
+#pragma unroll
+                for (int c0 = 0; c0 < AT_D; c0 += 32) {
+                    uint32_t r[32];
+                    at_tmem_ld32(tO + c0, r);
+                    if (valid) {
+#pragma unroll
+                        for (int d = 0; d < 32; d += 8) {
+                            uint4 v;
+                            __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[d]) * inv, __uint_as_float(r[d + 1]) * inv);
+                            __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[d + 2]) * inv, __uint_as_float(r[d + 3]) * inv);
+                            __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[d + 4]) * inv, __uint_as_float(r[d + 5]) * inv);
+                            __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[d + 6]) * inv, __uint_as_float(r[d + 7]) * inv);
+                            v.x = *reinterpret_cast<uint32_t*>(&p0); v.y = *reinterpret_cast<uint32_t*>(&p1);
+                            v.z = *reinterpret_cast<uint32_t*>(&p2); v.w = *reinterpret_cast<uint32_t*>(&p3);
+                            *reinterpret_cast<uint4*>(dst + c0 + d) = v;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(AT_TMEM_COLS) : "memory");
+    }
+    if (tid == 0 && failed_flag) atomicExch(a.status, 1);
+}
+
+// ------------------------------------------------------------------------------------------ host side
+typedef CUresult (*AtEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static AtEncodeTiledFn at_encode_tiled() {
+    static AtEncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (AtEncodeTiledFn)p;
+    }
+    return fn;
+}
+static int at_make_map(CUtensorMap* map, const void* ptr, cuuint64_t cols, cuuint64_t rows, cuuint32_t box_rows) {
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {AT_D, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return at_encode_tiled()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS ? 0 : -6;
+}
+
+// 1 if this kernel takes the sizes: head size 64, a page size that is a power of two from 8 to 128
+ZAI_API int zai_prefill_attention_tc_supports(int D, int Hq, int Hkv, int page_size) {
+    if (D != AT_D || Hkv < 1 || Hq % Hkv != 0 || Hq > 65535) return 0;
+    if (page_size < 8 || page_size > AT_BN || (page_size & (page_size - 1))) return 0;
+    return at_encode_tiled() != nullptr;
+}
+
+// out [N, Hq, 64] = attention of q [N, Hq, 64] (N rows in all, `n_tiles` blocks of 128 rows over the
+// requests' spans) over the pages [num_pages, 2, Hkv, page_size, 64]; arguments as
+// zai_prefill_attention_mma, plus the row and page counts and a status word that a block raises to 1
+// if one of its waits ran out.
+ZAI_API int zai_prefill_attention_tc(void* out, const void* q, const void* pages, int num_pages, int* status,
+                                     const int* block_table, int table_width, const int* cu_q, const int* ctx_lens, int N,
+                                     int S, int n_tiles, int page_size, int Hq, int Hkv, int D, float scale, int window,
+                                     cudaStream_t stream) {
+    if (N <= 0 || S <= 0 || n_tiles <= 0) return ZAI_OK;
+    if (!zai_prefill_attention_tc_supports(D, Hq, Hkv, page_size)) return ZAI_BAD_SIZE;
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(pages) | reinterpret_cast<uintptr_t>(out)) & 15) return ZAI_BAD_SIZE;
+    CUtensorMap mq, mkv;
+    int e = at_make_map(&mq, q, (cuuint64_t)Hq * AT_D, (cuuint64_t)N, AT_BM);
+    if (e) return e;
+    e = at_make_map(&mkv, pages, AT_D, (cuuint64_t)num_pages * 2 * Hkv * page_size, (cuuint32_t)(page_size < AT_BN ? page_size : AT_BN));
+    if (e) return e;
+    AtArgs a;
+    a.out = (bf16*)out; a.block_table = block_table; a.cu_q = cu_q; a.ctx_lens = ctx_lens; a.status = status;
+    a.table_width = table_width; a.S = S; a.page_size = page_size; a.Hq = Hq; a.Hkv = Hkv; a.window = window;
+    a.scale_log2 = scale * 1.4426950408889634f;
+    a.page_shift = 0;
+    while ((1 << a.page_shift) < page_size) ++a.page_shift;
+    const size_t smem = AT_Q_BYTES + (size_t)AT_STAGES * AT_KV_BYTES + AT_P_BYTES + 128;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) return (int)err;
+        // two blocks per SM: ask for the largest shared-memory carve-out
+        err = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        if (err != cudaSuccess) return (int)err;
+        configured = true;
+    }
+    return launch_pdl(prefill_tc_kernel, dim3(n_tiles, Hq), dim3(AT_THREADS), smem, stream, mq, mkv, a);
+}

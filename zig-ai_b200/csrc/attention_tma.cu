@@ -262,7 +262,7 @@ __global__ void __maxnreg__(128) decode_tma_kernel(const __grid_constant__ CUten
                 mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
                 const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);       // finite: the tile has a visible key
                 const float u0 = n0 * a.scale_log2, u1 = n1 * a.scale_log2;
-                const float c0 = exp2f(m0 * a.scale_log2 - u0), c1 = exp2f(m1 * a.scale_log2 - u1);
+                const float c0 = fast_exp2(m0 * a.scale_log2 - u0), c1 = fast_exp2(m1 * a.scale_log2 - u1);
                 m0 = n0;
                 m1 = n1;
                 l0 *= c0;
@@ -274,10 +274,10 @@ __global__ void __maxnreg__(128) decode_tma_kernel(const __grid_constant__ CUten
 #pragma unroll
                 for (int nt = 0; nt < 8; ++nt) {
                     // a masked score is -inf: exp2f gives 0 (a value row of a never-written page is zeros, finite)
-                    sc[nt][0] = exp2f(sc[nt][0] * a.scale_log2 - u0);
-                    sc[nt][1] = exp2f(sc[nt][1] * a.scale_log2 - u0);
-                    sc[nt][2] = exp2f(sc[nt][2] * a.scale_log2 - u1);
-                    sc[nt][3] = exp2f(sc[nt][3] * a.scale_log2 - u1);
+                    sc[nt][0] = fast_exp2(sc[nt][0] * a.scale_log2 - u0);
+                    sc[nt][1] = fast_exp2(sc[nt][1] * a.scale_log2 - u0);
+                    sc[nt][2] = fast_exp2(sc[nt][2] * a.scale_log2 - u1);
+                    sc[nt][3] = fast_exp2(sc[nt][3] * a.scale_log2 - u1);
                     l0 += sc[nt][0] + sc[nt][1];
                     l1 += sc[nt][2] + sc[nt][3];
                 }
@@ -299,8 +299,8 @@ __global__ void __maxnreg__(128) decode_tma_kernel(const __grid_constant__ CUten
             if (has_new && cw == 0) {                                          // fold the new key into this warp's sums
                 const float s0 = snew[g], s1 = snew[g + 8];
                 const float n0 = fmaxf(m0, s0), n1 = fmaxf(m1, s1);
-                const float c0 = exp2f(m0 * a.scale_log2 - n0 * a.scale_log2), c1 = exp2f(m1 * a.scale_log2 - n1 * a.scale_log2);
-                const float p0 = exp2f(s0 * a.scale_log2 - n0 * a.scale_log2), p1 = exp2f(s1 * a.scale_log2 - n1 * a.scale_log2);
+                const float c0 = fast_exp2(m0 * a.scale_log2 - n0 * a.scale_log2), c1 = fast_exp2(m1 * a.scale_log2 - n1 * a.scale_log2);
+                const float p0 = fast_exp2(s0 * a.scale_log2 - n0 * a.scale_log2), p1 = fast_exp2(s1 * a.scale_log2 - n1 * a.scale_log2);
                 m0 = n0;
                 m1 = n1;
                 l0 = l0 * c0 + (tq == 0 ? p0 : 0.f);
@@ -342,7 +342,7 @@ __global__ void __maxnreg__(128) decode_tma_kernel(const __grid_constant__ CUten
 #pragma unroll
                 for (int w = 0; w < TT_CONSUMERS; ++w) {
                     const float mw = wm[w * 16 + r];
-                    const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+                    const float f = mw == -INFINITY ? 0.f : fast_exp2(mw - M);
                     acc += wo[(w * 16 + r) * D + d] * f;
                     L += wl[w * 16 + r] * f;
                 }
@@ -382,7 +382,7 @@ __global__ void __maxnreg__(128) decode_tma_kernel(const __grid_constant__ CUten
         for (int c = 0; c < n_chunks; ++c) {
             const float mc = __ldcg(ml + 2 * c);
             if (mc == -INFINITY) continue;
-            const float f = exp2f(mc - M);
+            const float f = fast_exp2(mc - M);
             acc += __ldcg(a.part_o + (bh * n_chunks + c) * D + d) * f;
             L += __ldcg(ml + 2 * c + 1) * f;
         }

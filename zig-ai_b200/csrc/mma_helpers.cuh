@@ -33,6 +33,15 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 
+// 2^x by the special-function unit (2 ulp; x = -inf gives 0, which the masked scores rely on).  The
+// library's exp2f costs tens of cycles more per value, which showed as the largest part of a key
+// tile's time in the attention kernels.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // one head row: RMSNorm (if gamma) and rotation of the first `rot` dims; `tmp` holds D floats.  The
 // row, the norm's weight and the rotation's cosines and sines are all asked for before the first
 // of them is used, so the three loads cost one trip to memory, not three.

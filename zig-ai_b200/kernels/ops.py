@@ -63,6 +63,10 @@ _SIGNATURES = {
         "zai_decode_attention_tma": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _F, _P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I,
                                      _I, _F, _I, _I, _I, _P],
     },
+    "attention_tc": {
+        "zai_prefill_attention_tc_supports": [_I, _I, _I, _I],
+        "zai_prefill_attention_tc": [_P, _P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+    },
     "sampling": {
         "zai_argmax": [_P, _P, _I, _I, _P],
         "zai_repetition_penalty": [_P, _P, _P, _P, _P, _I, _I, _P],
@@ -104,7 +108,7 @@ def _check(code: int, what: str, n: int = 1) -> None:
 
 
 CORE_LIBS = ("embed", "norm", "activation", "shortconv", "rope_kv", "attention", "sampling")
-BF16_LIBS = ("attention_mma", "attention_tma", "decode_gemm")
+BF16_LIBS = ("attention_mma", "attention_tma", "attention_tc", "decode_gemm")
 
 
 def require(dtype=None) -> None:
@@ -464,11 +468,14 @@ def kv_write(k, v, step, cache, kv_heads, head_dim):
         head_dim, _stream()), "kv_write")
 
 
+USE_TC_ATTENTION = os.environ.get("ZAI_TC_ATTENTION", "1") == "1"     # tcgen05 prefill attention where the sizes allow
+
+
 def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=None, impl=None):
     """Causal attention of the step's rows over their requests' pages.  bfloat16 runs on the
     tensor cores (a split-key kernel when every span is one token, else the flash-style kernel)
     for the head sizes those kernels have; everything else, and `impl="general"`, runs the
-    general kernel."""
+    general kernel.  `impl="mma"` / `impl="tcgen05"` pick between the two span kernels."""
     _cuda(q)
     N = q.shape[0]
     out = torch.empty((N, heads * head_dim), dtype=q.dtype, device=q.device)
@@ -489,6 +496,16 @@ def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=Non
         else:
             block_rows = _fn("attention_mma", "zai_prefill_block_rows")()
             n_tiles = sum(-(-n // block_rows) for n in step.q_lens)
+            if (impl != "mma" and (USE_TC_ATTENTION or impl == "tcgen05") and q.is_contiguous()
+                    and _fn("attention_tc", "zai_prefill_attention_tc_supports")(head_dim, heads, kv_heads, cache.page_size)):
+                global _tc_status
+                if _tc_status is None:
+                    _tc_status = torch.zeros(1, dtype=torch.int32, device=q.device)
+                _check(_fn("attention_tc", "zai_prefill_attention_tc")(
+                    _ptr(out), _ptr(q), _ptr(cache.pages), cache.pages.shape[0], _ptr(_tc_status), _ptr(bt), bt.shape[1],
+                    _ptr(step.cu_q), _ptr(step.ctx_lens), N, step.n_seqs, n_tiles, cache.page_size, heads, kv_heads,
+                    head_dim, float(scale), int(window or 0), _stream()), "prefill attention (tcgen05)")
+                return out
             _check(_fn("attention_mma", "zai_prefill_attention_mma")(
                 _ptr(out), _ptr(q), _ptr(cache.pages), _ptr(bt), bt.shape[1], _ptr(step.cu_q), _ptr(step.ctx_lens),
                 step.n_seqs, n_tiles, cache.page_size, heads, kv_heads, head_dim, float(scale), int(window or 0),
