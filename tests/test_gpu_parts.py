@@ -1,8 +1,9 @@
 """Each part alone against the plain functions, at sizes and options the LFM2 configurations do not
 use (a window, a partial rotation, no q/k norm, a conv width that differs from the model width),
 and a toy architecture defined here: a mixer with a state of its own, a layer that runs twice, and
-a layer that reads the cache another layer wrote; registered, built, loaded and stepped without a
-change to the engine's files."""
+a layer that reads the cache another layer wrote; and a second one with a routed feed-forward and a
+position encoding that is no rotation; registered, built, loaded and stepped without a change to the
+engine's files."""
 import math
 import os
 import random
@@ -16,8 +17,8 @@ from zig_ai_b200.cache import CacheManager
 from zig_ai_b200.config import ModelConfig, register_architecture, unregister_architecture
 from zig_ai_b200.engine.batch import pack_step
 from zig_ai_b200.engine.runner import load_runner
-from zig_ai_b200.parts import (LayerCall, LayerSpec, Mixer, ModelSpec, ParamDecl, PartSpec, StateNeed, make_part,
-                               register_part, unregister_part)
+from zig_ai_b200.parts import (FeedForward, LayerCall, LayerSpec, Mixer, ModelSpec, ParamDecl, PartSpec, PositionEncoding,
+                               StateNeed, make_part, register_part, unregister_part)
 from zig_ai_b200.weights import write_random_model
 from zig_ai_b200.weights.random_init import random_tensors
 
@@ -258,3 +259,147 @@ def test_toy_architecture_is_registered_built_and_stepped(toy_registered, tmp_pa
     for k in reqs:
         err = (torch.cat(got[k]) - want[k]).abs().max() / want[k].abs().max()
         assert err < (5e-5 if dtype == "float32" else 3e-2), (k, float(err))
+
+
+# ------------------------------------------------- a second toy: routed experts, a position encoding of its own
+class ToyRoutedFeedForward(FeedForward):
+    """Two experts, the router's softmax in 32-bit, every token through its best expert, the result
+    weighted with the router's probability.  Torch operations; a state-free part."""
+
+    def __init__(self, hidden, ff_dim, experts):
+        self.hidden, self.ff_dim, self.experts = hidden, ff_dim, experts
+
+    def params(self):
+        p = {"router.weight": ParamDecl((self.experts, self.hidden))}
+        for e in range(self.experts):
+            p[f"expert{e}.up.weight"] = ParamDecl((self.ff_dim, self.hidden))
+            p[f"expert{e}.down.weight"] = ParamDecl((self.hidden, self.ff_dim))
+        return p
+
+    def bind(self, tensors, dtype):
+        self.t = tensors
+
+    def forward(self, x, step):
+        probs = torch.softmax(x.float() @ self.t["router.weight"].float().T, dim=-1)
+        best = probs.argmax(-1)
+        out = torch.zeros_like(x)
+        for e in range(self.experts):
+            rows = (best == e).nonzero().flatten()
+            if rows.numel():
+                hid = torch.relu(step.ops.linear(x[rows].contiguous(), self.t[f"expert{e}.up.weight"]))
+                y = step.ops.linear(hid, self.t[f"expert{e}.down.weight"])
+                out[rows] = (y.float() * probs[rows, e][:, None]).to(x.dtype)
+        return out
+
+
+class ToyScaledPositions(PositionEncoding):
+    """Not a rotation: q and k are multiplied by 1 + position / 64 in their first dimensions.  Applied
+    by the part itself (`rotary()` stays None), so the attention part runs its unfused path."""
+
+    def __init__(self, dims):
+        self.dims = dims
+
+    def apply(self, q, k, positions, step):
+        f = (1 + positions.float() / 64)[:, None]
+        q, k = q.clone(), (k.clone() if k is not None else None)
+        qv = q.view(q.shape[0], -1, TOY2["head_dim"])
+        qv[..., :self.dims] = (qv[..., :self.dims].float() * f[..., None]).to(q.dtype)
+        if k is not None:
+            kv = k.view(k.shape[0], -1, TOY2["head_dim"])
+            kv[..., :self.dims] = (kv[..., :self.dims].float() * f[..., None]).to(k.dtype)
+        return q, k
+
+
+TOY2 = dict(hidden=48, heads=3, kv_heads=3, head_dim=16, ff_dim=40, experts=2, eps=1e-5, dims=4, vocab=61)
+
+
+@dataclass
+class Toy2Config(ModelConfig):
+    @classmethod
+    def from_dict(cls, d):
+        return cls("Toy2ForTests")
+
+    def to_dict(self):
+        return {"architectures": ["Toy2ForTests"]}
+
+
+def toy2_spec(cfg):
+    a, H = TOY2, TOY2["hidden"]
+    norm = lambda name: PartSpec("rmsnorm", dict(size=H, eps=a["eps"], weight=name))
+    att = PartSpec("attention", dict(hidden=H, heads=a["heads"], kv_heads=a["kv_heads"], head_dim=a["head_dim"],
+                                     qk_norm=False, eps=a["eps"], position=PartSpec("toy_scaled", dict(dims=a["dims"]))))
+    ff = PartSpec("toy_routed", dict(hidden=H, ff_dim=a["ff_dim"], experts=a["experts"]))
+    layers = [LayerSpec(prefix=f"l{i}.", block=PartSpec("prenorm_residual"), mixer=att, feed_forward=ff,
+                        mixer_norm=norm("a.weight"), ff_norm=norm("b.weight")) for i in range(2)]
+    return ModelSpec("Toy2ForTests", H, a["vocab"], 256, PartSpec("embedding", dict(weight="emb.weight")),
+                     layers, [LayerCall(0), LayerCall(1)], norm("final.weight"),
+                     PartSpec("linear_head", dict(weight="emb.weight", tied=True)))
+
+
+def toy2_plain(W, tokens):
+    a = TOY2
+    T = len(tokens)
+    f = (1 + torch.arange(T, dtype=F64) / 64)[:, None, None]
+    h = W["emb.weight"][torch.tensor(tokens)]
+    for i in range(2):
+        pre = f"l{i}."
+        r = P.rms_norm(h, W[pre + "a.weight"], a["eps"])
+        q = (r @ W[pre + "attn_q.weight"].T).view(T, a["heads"], a["head_dim"]).clone()
+        k = (r @ W[pre + "attn_k.weight"].T).view(T, a["kv_heads"], a["head_dim"]).clone()
+        v = (r @ W[pre + "attn_v.weight"].T).view(T, a["kv_heads"], a["head_dim"])
+        q[..., :a["dims"]] *= f
+        k[..., :a["dims"]] *= f
+        o = P.causal_attention(q, k, v, 1 / math.sqrt(a["head_dim"]), None)
+        h = h + o.reshape(T, -1) @ W[pre + "attn_output.weight"].T
+        r = P.rms_norm(h, W[pre + "b.weight"], a["eps"])
+        probs = torch.softmax(r @ W[pre + "router.weight"].T, dim=-1)
+        best = probs.argmax(-1)
+        y = torch.zeros_like(r)
+        for t in range(T):
+            e = int(best[t])
+            y[t] = (torch.relu(r[t] @ W[pre + f"expert{e}.up.weight"].T) @ W[pre + f"expert{e}.down.weight"].T) * probs[t, e]
+        h = h + y
+    return P.rms_norm(h, W["final.weight"], a["eps"]) @ W["emb.weight"].T
+
+
+@pytest.fixture
+def toy2_registered():
+    register_part("feed_forward", "toy_routed", ToyRoutedFeedForward)
+    register_part("position", "toy_scaled", ToyScaledPositions)
+    register_architecture("Toy2ForTests", Toy2Config, toy2_spec)
+    yield
+    unregister_part("feed_forward", "toy_routed")
+    unregister_part("position", "toy_scaled")
+    unregister_architecture("Toy2ForTests")
+
+
+def test_toy_routed_feed_forward_and_position_encoding(toy2_registered, tmp_path):
+    """A feed-forward with routing and a position encoding that is no rotation, both defined here,
+    in a model that is built, loaded and stepped in portions beside another request; 32-bit, so that
+    the comparison with the plain formulas is tight (a token near a tie of the router aside)."""
+    cfg = Toy2Config("Toy2ForTests")
+    d = write_random_model(cfg, 37, str(tmp_path / "toy2"), matrix_std="fan_in")
+    runner = load_runner(d, "float32", max_tokens=256, max_requests=3, page_size=4)
+    W = P.read_weights(d)
+    g = random.Random(6)
+    reqs = {k: [g.randrange(TOY2["vocab"]) for _ in range(n)] for k, n in (("x", 33), ("y", 12))}
+    want = {k: toy2_plain(W, t) for k, t in reqs.items()}
+    got, at = {k: [] for k in reqs}, {k: 0 for k in reqs}
+    for k in reqs:
+        runner.add_request(k)
+    while any(at[k] < len(reqs[k]) for k in reqs):
+        entries = []
+        for k in reqs:
+            left = len(reqs[k]) - at[k]
+            if left:
+                n = min(g.choice([1, 1, 3, 7]), left)
+                entries.append((k, reqs[k][at[k]:at[k] + n], list(range(n))))
+        out = runner.step(entries)
+        row = 0
+        for k, t, w in entries:
+            got[k].append(out[row:row + len(w)].double().cpu())
+            row += len(w)
+            at[k] += len(t)
+    for k in reqs:
+        err = (torch.cat(got[k]) - want[k]).abs().max() / want[k].abs().max()
+        assert err < 5e-5, (k, float(err))
