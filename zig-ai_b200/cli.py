@@ -107,6 +107,7 @@ def main(argv=None) -> int:
         if t_first is None and eng.n_generated > 0:
             torch.cuda.synchronize()
             t_first = time.perf_counter()
+    eng.flush()
     torch.cuda.synchronize()
     t1 = time.perf_counter()
     for i in ids:
