@@ -161,3 +161,24 @@ def test_a_step_ahead_of_the_host_changes_no_token(tiny_models, dtype, temperatu
         assert [o[-1] for o in base_eos] == [w[-1] if e is None else e for w, e in zip(base_eos, eos)]
     got, reasons, stats = run(True, eos)
     assert got == base_eos and reasons[1] == "eos" and stats["steps_ahead"] >= 1
+
+
+def test_a_step_ahead_with_preemptions(tiny_models):
+    """So few pages that running requests are preempted and recomputed: the engine that keeps a step
+    ahead gives the same tokens as the one that does not, and both saw preemptions."""
+    import zig_ai_b200 as z
+    name = "B"
+    g = random.Random(12)
+    V = TINY[name][0]["vocab_size"]
+    prompts = [[g.randrange(V) for _ in range(n)] for n in (20, 11, 17, 6)]
+
+    def run(pipeline):
+        eng = z.Engine(tiny_models[name], "float32", max_num_seqs=4, max_batched_tokens=24, max_model_len=64,
+                       max_tokens=11 * PAGE_SIZE[name], page_size=PAGE_SIZE[name], pipeline=pipeline)
+        out = eng.generate(prompts, max_new_tokens=24, temperature=0.8, top_p=0.9, seed=3)
+        return out, eng.stats()
+
+    base, st0 = run(False)
+    got, st1 = run(True)
+    assert got == base and all(len(o) == 24 for o in got)
+    assert st0["preemptions"] > 0 and st1["preemptions"] > 0 and st1["steps_ahead"] > 0
