@@ -11,10 +11,13 @@ from __future__ import annotations
 
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import os
+
 import numpy as np
 import torch
 
 from ..cache import CacheManager, OutOfPages
+from ..cache.manager import NULL_PAGE, NULL_SLOT
 from ..models import build_model
 from .batch import StepBatch, pack_step
 
@@ -131,6 +134,26 @@ class ModelRunner:
         self.tokens_run += prepared[1]
         return self.graphs.run_prepared(prepared)
 
+    def _pad_rows(self, spans, tables):
+        """Round a step's row count up (to a multiple of 32 up to 256 rows, of 64 beyond) with a span of
+        the null request (null slot, null page, nothing wanted), so that the library's matrix products
+        see few distinct row counts: it plans every new shape once, at a millisecond each, and a
+        serving run would otherwise meet thousands of them."""
+        if self.device.type != "cuda" or os.environ.get("ZAI_PAD_ROWS", "1") == "0":
+            return spans, tables
+        n = sum(len(s[2]) for s in spans)
+        if n <= 16:                                            # the few-rows kernels: no library product
+            return spans, tables
+        step = 32 if n <= 256 else 64
+        pad = -n % step
+        if pad == 0:
+            return spans, tables
+        spans = list(spans) + [(None, 0, [0] * pad, [], NULL_SLOT)]
+        tables = {g: np.vstack([np.asarray(t, dtype=np.int32).reshape(len(spans) - 1, -1),
+                                np.full((1, max(np.asarray(t).reshape(len(spans) - 1, -1).shape[1], 1)), NULL_PAGE, dtype=np.int32)])
+                  for g, t in tables.items()}
+        return spans, tables
+
     def can_take_device_tokens(self, n_rows: int) -> bool:
         """Whether a step of `n_rows` single tokens may get its tokens from a device tensor."""
         return bool(self.use_graphs and self.graphs.bucket(n_rows) is not None)
@@ -155,6 +178,7 @@ class ModelRunner:
             else:
                 logits = full[torch.tensor(keep, dtype=torch.long, device=self.device)] if keep else full[:0]
         else:
+            spans, tables = self._pad_rows(spans, tables)
             logits = self.shape_graphs.run(spans, tables) if self.use_graphs else None
             if logits is None:
                 batch = pack_step(self.ops, self.dtype, self.device, spans, tables, pin=True)
