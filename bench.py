@@ -420,7 +420,8 @@ def run_mixed(args, cfg):
            "prompt_tokens": n_prompt, "prompt_tokens_per_s": round(n_prompt / dt, 1), "steps": eng.n_steps - steps0,
            "mean_step_ms": round(dt * 1e3 / max(eng.n_steps - steps0, 1), 3),
            "pages_high_water": max(v for k, v in st.items() if k.endswith("pages_high_water")),
-           "preemptions": st["preemptions"], "dtype": "bf16", "data": "synthetic", "impl": "ours"}
+           "preemptions": st["preemptions"], "step_graph_replays": eng.runner.shape_graphs.replays,
+           "step_graphs_kept": len(eng.runner.shape_graphs.graphs), "dtype": "bf16", "data": "synthetic", "impl": "ours"}
     print(json.dumps(out))
     return 0
 

@@ -120,6 +120,50 @@ def test_repeated_step_shapes_run_as_graphs_and_agree(tiny_models, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_of_one_bucket_share_a_graph_and_agree(tiny_models, dtype):
+    """Steps whose shapes differ but round to the same counts (17 to 32 rows, two to five spans, some
+    of one token beside prompt portions, up to eight wanted rows) are replayed from one graph once it
+    is captured; logits as from the runner without graphs; the requests go on across the steps, so a
+    padded row that touched a request's pages or state would show."""
+    from zig_ai_b200.engine.runner import load_runner
+    d = tiny_models["A"]
+    c, W = plain_lfm2.read_config(d), plain_lfm2.read_weights(d)
+    g = random.Random(23)
+    V = c["vocab_size"]
+    runner = load_runner(d, dtype, max_tokens=2048, page_size=PAGE_SIZE["A"], max_requests=8)
+    eager = load_runner(d, dtype, max_tokens=2048, page_size=PAGE_SIZE["A"], max_requests=8, graphs=False)
+    toks = {k: [] for k in range(5)}
+    for r in (runner, eager):
+        for k in toks:
+            r.add_request(k)
+    worst = 0.0
+    for step in range(14):
+        n_spans = g.randint(2, 5)
+        ks = g.sample(range(5), n_spans)
+        sizes = [1] * (n_spans - 1) + [0]
+        sizes[-1] = g.randint(17, 32) - sum(sizes)                  # the step's rows: 17..32
+        entries = []
+        for k, n in zip(ks, sizes):
+            new = [g.randrange(V) for _ in range(n)]
+            want = sorted(g.sample(range(n), min(n, g.randint(0, 2))))
+            entries.append((k, new, want))
+            toks[k] += new
+        a = runner.step(entries).cpu().numpy().copy()
+        b = eager.step(entries).cpu().numpy().copy()
+        assert a.shape == b.shape
+        if a.size:
+            worst = max(worst, float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-6)))
+    assert len(runner.shape_graphs.graphs) == 1 and runner.shape_graphs.replays >= 10
+    assert worst < (2e-5 if dtype == "float32" else 4e-2), worst
+    # and the requests' caches are what the plain implementation expects: one more token each
+    for k in toks:
+        nxt = [(k, [3], [0])]
+        got = runner.step(nxt).cpu().numpy()[0]
+        want = plain_lfm2.forward(c, W, toks[k] + [3]).numpy()[-1]
+        traces.check_request(got[None], want[None], dtype, f"{dtype} request {k} after bucketed steps")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("temperature", [0.0, 0.9])
 def test_a_step_ahead_of_the_host_changes_no_token(tiny_models, dtype, temperature):
     """With `pipeline` the engine launches a decode step before it has read the tokens of the step

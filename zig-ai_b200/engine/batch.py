@@ -8,7 +8,7 @@ token.  The spans are flattened into N rows.  (The reference runs one sequence:
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, List, Sequence
+from typing import Dict, List, Optional, Sequence
 
 import numpy as np
 import torch
@@ -34,6 +34,8 @@ class StepBatch:
     decode_only: bool = False      # every span is one token
     q_lens: Sequence[int] = ()
     request_ids: Sequence = ()
+    attn_tiles: Optional[int] = None   # blocks of query rows to launch for span attention (default: from q_lens);
+    #                                    a captured graph launches an upper bound for its bucket of step shapes
     scratch: Dict = field(default_factory=dict)   # what kernels compute once per step (rotation tables)
 
 
@@ -50,9 +52,10 @@ class PackedLayout:
     request_ids: List
 
 
-def pack_host(spans, tables: Dict[int, "np.ndarray"], widths: Dict[int, int] = None):
+def pack_host(spans, tables: Dict[int, "np.ndarray"], widths: Dict[int, int] = None, pad_wanted: int = 0):
     """Flatten a step's description into one int32 array: tokens, positions, row->request, span
-    starts, context lengths, slots, wanted rows, then each group's block tables [S, width].
+    starts, context lengths, slots, wanted rows, then each group's block tables [S, width].  (A span
+    may have no tokens.)
     `spans` is a list of (request_id, ctx_len, tokens, wanted offsets, slot); `widths` fixes the
     table widths (a captured graph needs them constant), default: as wide as the tables given."""
     S = len(spans)
@@ -73,6 +76,7 @@ def pack_host(spans, tables: Dict[int, "np.ndarray"], widths: Dict[int, int] = N
                 raise ValueError(f"wanted place {w} is outside the {n} tokens of request {rid!r}")
             rows.append(at + w)
         at += n
+    rows += [0] * max(pad_wanted - len(rows), 0)              # (`pad_wanted`: the wanted rows are filled up with row 0)
     parts = tok + pos + sidx + [np.array(cu + ctx + slots + rows, dtype=np.int32)]
     N, R = at, len(rows)
     off = 3 * N + (S + 1) + 2 * S + R

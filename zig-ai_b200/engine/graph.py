@@ -89,12 +89,28 @@ class StaticDecodeStep:
         self.dev.copy_(host, non_blocking=True)
 
 
-class ShapeGraphs:
-    """Graphs for steps that are not single-token steps but come again with exactly the same shape
-    (the same span lengths and wanted rows): a prompt cut into portions of the token budget, equal
-    prompts.  A shape is captured the third time it is seen; a few shapes are kept."""
+def round_rows(n: int) -> int:
+    """The row counts that steps outside the single-token graphs are rounded up to: 8, 16, then
+    multiples of 32 up to 256, then multiples of 64."""
+    if n <= 8:
+        return 8
+    if n <= 16:
+        return 16
+    step = 32 if n <= 256 else 64
+    return -(-n // step) * step
 
-    KEEP = 6
+
+class ShapeGraphs:
+    """Graphs for steps that are not single-token steps (prompt portions, alone or beside decoded
+    tokens).  A graph serves every step of its bucket: the row count rounded up (`round_rows`), the
+    number of spans and of wanted rows rounded up to multiples of 8.  A step is brought to its bucket
+    with a span of the null request for the spare rows (null slot and page), spans without tokens,
+    and wanted rows that repeat row 0; what the kernels launch depends on those rounded counts only
+    (span attention launches an upper bound of its blocks of query rows).  A bucket is captured the
+    third time it is seen (a capture costs two passes and the instantiation, some tens of milliseconds
+    for a full step); the most recently used graphs are kept."""
+
+    KEEP = 16
     SEEN_BEFORE_CAPTURE = 2
 
     def __init__(self, model, cache, ops, dtype, device, widths: Dict[int, int]):
@@ -105,12 +121,34 @@ class ShapeGraphs:
 
     @staticmethod
     def key(spans) -> tuple:
-        return tuple((len(s[2]), tuple(s[3])) for s in spans)
+        n = sum(len(s[2]) for s in spans)
+        r = sum(len(s[3]) for s in spans)
+        return round_rows(n), -(-(len(spans) + 1) // 8) * 8, -(-r // 8) * 8
+
+    def _fill(self, k, spans, tables):
+        """The step in its bucket's layout: (spans, tables) with the padding spans added."""
+        n_rows, n_spans, _ = k
+        n = sum(len(s[2]) for s in spans)
+        extra = n_spans - len(spans)
+        spans = list(spans) + [(None, 0, [0] * (n_rows - n), [], NULL_SLOT)] + [(None, 0, [], [], NULL_SLOT)] * (extra - 1)
+        out = {}
+        for g, t in tables.items():
+            m = np.asarray(t, dtype=np.int32).reshape(len(spans) - extra, -1)
+            out[g] = np.vstack([m, np.full((extra, m.shape[1]), NULL_PAGE, dtype=np.int32)])
+        return spans, out
+
+    def _views(self, k, dev, lay):
+        from .batch import batch_views
+        batch = batch_views(self.ops, self.dtype, dev, lay)
+        batch.max_kv_len = max(self.widths.values(), default=1) * self.cache.page_size
+        batch.attn_tiles = k[0] // 128 + k[1]                  # every span may end with a partial block of query rows
+        return batch
 
     def run(self, spans, tables):
-        """Logits if this shape has a graph or has earned one, else None (the caller runs it eagerly)."""
-        from .batch import batch_views, pack_host
+        """Logits if this step's bucket has a graph or has earned one, else None (the caller runs it eagerly)."""
+        from .batch import pack_host
         k = self.key(spans)
+        n_wanted = sum(len(s[3]) for s in spans)
         entry = self.graphs.get(k)
         if entry is None:
             n = self.seen.get(k, 0)
@@ -119,18 +157,19 @@ class ShapeGraphs:
                 self.seen.clear()
             if n < self.SEEN_BEFORE_CAPTURE:
                 return None
-            flat, lay = pack_host(spans, tables, self.widths)
+            spans_p, tables_p = self._fill(k, spans, tables)
+            flat, lay = pack_host(spans_p, tables_p, self.widths, pad_wanted=k[2])
             host = torch.empty(lay.total, dtype=torch.int32).pin_memory()
             host.numpy()[:] = flat
             dev = host.to(self.device)
-            batch = batch_views(self.ops, self.dtype, dev, lay)
-            batch.max_kv_len = max(self.widths.values(), default=1) * self.cache.page_size
+            batch = self._views(k, dev, lay)
             # the capture's own warm-up would run the step three times; state that a step changes in
             # place (conv state, pages) must see it once.  So this step runs eagerly now, and the
             # graph is captured from a dry run on the null request's slot and page afterwards.
-            return self._capture_later(k, spans, tables, lay, host, dev, batch)
+            return self._capture_later(k, spans_p, tables_p, lay, host, dev, batch)[:n_wanted]
         graph, host, dev, logits, launches = entry
-        flat, _ = pack_host(spans, tables, self.widths)
+        spans_p, tables_p = self._fill(k, spans, tables)
+        flat, _ = pack_host(spans_p, tables_p, self.widths, pad_wanted=k[2])
         host.numpy()[:] = flat
         dev.copy_(host, non_blocking=True)
         graph.replay()
@@ -138,25 +177,19 @@ class ShapeGraphs:
         if hasattr(self.ops, "launches"):
             self.ops.launches += launches
         self.graphs[k] = self.graphs.pop(k)           # most recently used last
-        return logits
+        return logits[:n_wanted]
 
     def _capture_later(self, k, spans, tables, lay, host, dev, batch):
         from .batch import pack_host
-        from ..cache.manager import NULL_PAGE, NULL_SLOT
-        # dry-run description: same shape, every span on the null slot and the null page at position 0
+        # dry-run description: same bucket, every span on the null slot and the null page at position 0
         dry = [(None, 0, s[2], s[3], NULL_SLOT) for s in spans]
         dry_tables = {g: np.zeros((len(spans), 1), dtype=np.int32) for g in tables}
-        flat, _ = pack_host(dry, dry_tables, self.widths)
+        flat, _ = pack_host(dry, dry_tables, self.widths, pad_wanted=k[2])
         # 1. the real step, eagerly, on the static buffers
         logits_now = self.model.forward(batch, self.cache)
-        # 2. warm-up and capture on the dry description
+        # 2. capture on the dry description (the pass above was the warm-up)
         host.numpy()[:] = flat
         dev.copy_(host)
-        stream = torch.cuda.Stream(device=self.device)
-        stream.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(stream):
-            self.model.forward(batch, self.cache)
-        torch.cuda.current_stream().wait_stream(stream)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         before = getattr(self.ops, "launches", 0)

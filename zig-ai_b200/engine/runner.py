@@ -178,9 +178,9 @@ class ModelRunner:
             else:
                 logits = full[torch.tensor(keep, dtype=torch.long, device=self.device)] if keep else full[:0]
         else:
-            spans, tables = self._pad_rows(spans, tables)
             logits = self.shape_graphs.run(spans, tables) if self.use_graphs else None
             if logits is None:
+                spans, tables = self._pad_rows(spans, tables)
                 batch = pack_step(self.ops, self.dtype, self.device, spans, tables, pin=True)
                 logits = self.model.forward(batch, self.cache)
         for rid, tokens, _ in entries:

@@ -478,6 +478,8 @@ def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=Non
     general kernel.  `impl="mma"` / `impl="tcgen05"` pick between the two span kernels."""
     _cuda(q)
     N = q.shape[0]
+    if N != step.n_tokens:
+        raise KernelError(f"{N} query rows for a step of {step.n_tokens} rows")
     out = torch.empty((N, heads * head_dim), dtype=q.dtype, device=q.device)
     if cache.pages.dtype != q.dtype:
         raise KernelError("the pages and the queries should have one dtype")
@@ -495,7 +497,7 @@ def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=Non
                 int(window or 0), _stream()), "decode attention", 2)
         else:
             block_rows = _fn("attention_mma", "zai_prefill_block_rows")()
-            n_tiles = sum(-(-n // block_rows) for n in step.q_lens)
+            n_tiles = step.attn_tiles if getattr(step, "attn_tiles", None) else sum(-(-n // block_rows) for n in step.q_lens)
             if (impl != "mma" and (USE_TC_ATTENTION or impl == "tcgen05") and q.is_contiguous()
                     and _fn("attention_tc", "zai_prefill_attention_tc_supports")(head_dim, heads, kv_heads, cache.page_size)):
                 global _tc_status
@@ -534,6 +536,8 @@ def decode_attention_fused(qkv, q_w, k_w, eps, rotary_dim, theta, step, cache, h
     of keys, and the combination of the chunks.  Every row of the step is one token."""
     _cuda(qkv, q_w, k_w)
     B, cols = qkv.shape
+    if B != step.n_tokens:
+        raise KernelError(f"{B} rows for a step of {step.n_tokens} rows")
     dev = qkv.device
     out = torch.empty((B, heads * head_dim), dtype=qkv.dtype, device=dev)
     # keys per block: about DECODE_BLOCKS_WANTED blocks (a little more than the SMs hold at once), so
