@@ -12,7 +12,7 @@ from tiny_configs import PAGE_SIZE, TINY
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [70, 45, 128, 33, 7, 1, 2, 96], "B": [130, 61, 257, 40, 5, 1, 33, 90]}
+LENGTHS = {"A": [70, 45, 128, 33, 7, 1, 2, 96], "B": [130, 61, 257, 40, 5, 1, 33, 90], "C": [300, 129, 64, 410, 1, 35]}
 
 
 @pytest.fixture(scope="module")
@@ -41,7 +41,7 @@ def compare_schedules(got, reqs, tag_a, tag_b, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_schedules_agree_with_plain(tiny_models, plain, tmp_path, name, dtype):
     reqs, want = plain[name]
     vocab = TINY[name][0]["vocab_size"]
@@ -55,7 +55,7 @@ def test_schedules_agree_with_plain(tiny_models, plain, tmp_path, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_mixed_batches_in_a_small_pool(tiny_models, plain, tmp_path, name, dtype):
     reqs, want = plain[name]
     vocab = TINY[name][0]["vocab_size"]

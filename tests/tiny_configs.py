@@ -23,6 +23,20 @@ TINY_B = {
     "use_qk_norm": True, "norm_eps": 1e-6, "tie_embedding": False, "max_position_embeddings": 4096,
 }
 
+# A third one with the head size of the LFM2 checkpoints (64), two query heads per key/value head and
+# a feed-forward wide enough for the long-row product: the whole-model tests reach through it the
+# kernels that only that head size has (keys and values by TMA in decoding, the tcgen05 span
+# attention) and the product that splits K across a cluster.
+SMALL_C = {
+    "architectures": ["Lfm2ForCausalLM"],
+    "hidden_size": 256, "num_hidden_layers": 4,
+    "layer_types": ["conv", "full_attention", "full_attention", "conv"],
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64,
+    "block_ff_dim": 2304, "block_auto_adjust_ff_dim": True, "block_multiple_of": 256,
+    "vocab_size": 1000, "rope_theta": 1000000.0, "conv_L_cache": 3, "conv_bias": False,
+    "use_qk_norm": True, "norm_eps": 1e-5, "tie_embedding": True, "max_position_embeddings": 4096,
+}
+
 # name -> (config, seed of the random weights)
-TINY = {"A": (TINY_A, 11), "B": (TINY_B, 23)}
-PAGE_SIZE = {"A": 16, "B": 8}
+TINY = {"A": (TINY_A, 11), "B": (TINY_B, 23), "C": (SMALL_C, 29)}
+PAGE_SIZE = {"A": 16, "B": 8, "C": 64}

@@ -140,13 +140,15 @@ __global__ void __maxnreg__(128) decode_tma_kernel(const __grid_constant__ CUten
     // table, the cached keys and values), so it does not wait for the kernel before this one: its
     // loads fly while that kernel (the qkv projection) still runs.  The consumers need its result.
     // (A layer that only reads a cache which another layer wrote earlier in this step waits, too.)
+    // A block without keys waits as a whole: what it stores (its empty partial sum) may lie in memory
+    // that a kernel further back in the chain still uses, and nothing is stored before the wait.
     const int pos = a.positions[b];
-    if (warp != 0 || !a.write_kv) pdl_wait();
     const int kstart = a.window > 0 ? max(pos - a.window + 1, 0) : 0;
     const bool has_new = a.write_kv && chunk == pos / a.chunk_keys;
     const int kend = a.write_kv ? pos : pos + 1;
     const int lo = max(chunk * a.chunk_keys, kstart), hi = min((chunk + 1) * a.chunk_keys, kend);
     const bool any_paged = lo < hi;
+    if (warp != 0 || !a.write_kv || !(any_paged || has_new)) pdl_wait();
     const int* table = a.block_table + (size_t)b * a.table_width;
     const int tile0 = lo / TT_TILE, tile1 = any_paged ? (hi + TT_TILE - 1) / TT_TILE : tile0;
     const int cw = warp - 1;                                         // consumer index 0..3 (warp 0 produces)
