@@ -24,7 +24,7 @@ def plain_greedy(model_dir, prompt, n):
     return toks[len(prompt):]
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_greedy_generation_float32_matches_plain(tiny_models, name):
     import zig_ai_b200 as z
     g = random.Random(3)
@@ -37,7 +37,7 @@ def test_greedy_generation_float32_matches_plain(tiny_models, name):
         assert out == plain_greedy(tiny_models[name], p, 8)
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_greedy_generation_bfloat16_picks_a_plain_maximum(tiny_models, name):
     """In bfloat16 a near-tie may fall the other way: every generated token must be within the
     bfloat16 tolerance of the plain implementation's best logit at its place."""
