@@ -114,6 +114,9 @@ def model_numbers(cfg):
                 state_bytes=state_bytes, n_attn=n_attn, attn_dims=(Hq, D))
 
 
+PROFILE_RANGE = False      # --profile-range: the timed decode steps lie between cudaProfilerStart and cudaProfilerStop
+
+
 def decode_requests(eng, B, steps_needed, seed):
     """Add B requests with contexts spread over 2048..CONTEXT and run until all of them decode."""
     from zig_ai_b200.sampling import SamplingParams
@@ -155,6 +158,8 @@ def time_decode(eng, B, steps, warmup, clocks=None):
     if clocks:
         clocks.mark()
     marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps - 1)]
+    if PROFILE_RANGE:
+        torch.cuda.profiler.start()          # a profiler started with --profile-from-start off sees only these steps
     start.record()
     for k in range(steps):
         ops.argmax(runner.run_prepared(prepared[warmup + k]))
@@ -162,6 +167,8 @@ def time_decode(eng, B, steps, warmup, clocks=None):
             marks[k].record()
     stop.record()
     torch.cuda.synchronize()
+    if PROFILE_RANGE:
+        torch.cuda.profiler.stop()
     dev_ms = start.elapsed_time(stop) / steps
     edges = [start] + marks + [stop]
     per_step = [edges[k].elapsed_time(edges[k + 1]) for k in range(steps)]
@@ -336,6 +343,7 @@ def run_gemm_table(cfg):
     from zig_ai_b200.kernels import ops
     ops.require()
     fn = ops._fn("gemm_tc", "zai_gemm_tc")
+    fn2 = ops._fn("gemm_tc_pair", "zai_gemm_pair")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     H, F = cfg.hidden_size, cfg.ff_dim
     qkv = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim
@@ -383,8 +391,18 @@ def run_gemm_table(cfg):
                     ops.silu_mul(torch.matmul(x, w.t()), O // 2)
                 else:
                     torch.matmul(x, w.t())
+            def pair(wide):
+                def f():
+                    w = ws[it[0] % len(ws)]
+                    it[0] += 1
+                    fn2(y.data_ptr(), w.data_ptr(), x.data_ptr(), status.data_ptr(), N, O, K, epi, wide, ops._stream())
+                return f
             t, t2 = graph_time(tc), graph_time(lib)
-            rows.append({"rows": N, "product": name, "O": O, "K": K, "tcgen05_us": round(t, 1),
+            tw, tn = graph_time(pair(1)), graph_time(pair(0))
+            tp = min(tw, tn)
+            rows.append({"rows": N, "product": name, "O": O, "K": K, "pair_us": round(tp, 1), "pair_wide_us": round(tw, 1),
+                         "pair_narrow_us": round(tn, 1), "pair_tflops": round(2 * N * O * K / tp / 1e6),
+                         "tcgen05_us": round(t, 1),
                          "tcgen05_tflops": round(2 * N * O * K / t / 1e6), "library_us": round(t2, 1),
                          "library_tflops": round(2 * N * O * K / t2 / 1e6)})
             print(json.dumps(rows[-1]))
@@ -435,11 +453,15 @@ def main():
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "gemm", "timeline"],
                     help="profiling aid: run only the batch-8 decode steps or only the prefill (prints a short line)")
     ap.add_argument("--batch", type=int, default=8, help="with --only decode: the batch size")
+    ap.add_argument("--profile-range", action="store_true",
+                    help="mark the device-timed decode steps for a profiler (ncu --profile-from-start off)")
     ap.add_argument("--page-size", type=int, default=64, help="positions per cache page")
     ap.add_argument("--model", default="350m", choices=sorted(SHAPES), help="which LFM2 shape (default: the 350M shape)")
     ap.add_argument("--workload", default="steps", choices=["steps", "mixed"],
                     help="mixed: 64 requests, chunked prefill interleaved with decoding, end to end")
     args = ap.parse_args()
+    global PROFILE_RANGE
+    PROFILE_RANGE = args.profile_range
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "the reference is a Zig 0.16 program (build.zig); no Zig compiler exists in this image and it "

@@ -430,6 +430,61 @@ def _tc_call(o, y, w, x, epilogue):
     assert code == 0 and int(status.item()) == 0, (code, int(status.item()))
 
 
+def _pair_call(o, y, w, x, epilogue, wide):
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    fn = o._fn("gemm_tc_pair", "zai_gemm_pair")
+    code = fn(y.data_ptr(), w.data_ptr(), x.data_ptr(), status.data_ptr(), x.shape[0], w.shape[0], w.shape[1], epilogue,
+              wide, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert code == 0 and int(status.item()) == 0, (code, int(status.item()))
+
+
+@pytest.mark.parametrize("wide", [1, 0, -1])
+@pytest.mark.parametrize("N,O,K", [(256, 256, 64), (128, 128, 64), (512, 512, 1024), (300, 517, 1000), (2048, 1024, 1024),
+                                   (1000, 3072, 1024), (129, 96, 96), (4096, 256, 136), (640, 1536, 4608),
+                                   (5000, 2048, 512)])
+def test_two_block_tensor_core_gemm_bf16_and_f32(N, O, K, wide):
+    """The product whose tiles span two blocks: tiles that end inside the matrix in every direction
+    (also a pair whose second block has no token at all), K that is no multiple of 64, more tiles
+    than pairs, few tiles, both tile widths.  The inputs differ by token and by weight row, so a
+    half of a tile that landed in the wrong block's rows or columns shows."""
+    o = ops()
+    g = torch.Generator().manual_seed(33)
+    x = torch.randn(N, K, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(O, K, generator=g) * K ** -0.5).to(torch.bfloat16).cuda()
+    want = x.float() @ w.float().t()
+    y = torch.full((N, O), float("nan"), dtype=torch.bfloat16, device="cuda")
+    _pair_call(o, y, w, x, 0, wide)
+    assert torch.allclose(y.float(), want, atol=2e-2, rtol=2e-2)
+    y32 = torch.full((N, O), float("nan"), dtype=torch.float32, device="cuda")
+    _pair_call(o, y32, w, x, 1, wide)
+    assert torch.allclose(y32, want, atol=2e-3, rtol=2e-3)
+
+
+@pytest.mark.parametrize("wide", [1, 0])
+@pytest.mark.parametrize("N,F,K", [(256, 128, 64), (2048, 4608, 1024), (130, 100, 96), (700, 1000, 520), (3000, 1536, 256)])
+def test_two_block_tensor_core_gemm_swiglu(N, F, K, wide):
+    o = ops()
+    g = torch.Generator().manual_seed(34)
+    x = torch.randn(N, K, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(2 * F, K, generator=g) * K ** -0.5).to(torch.bfloat16).cuda()
+    gu = x.float() @ w.float().t()
+    want = torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]
+    y = torch.full((N, F), float("nan"), dtype=torch.bfloat16, device="cuda")
+    _pair_call(o, y, w, x, 2, wide)
+    assert torch.allclose(y.float(), want, atol=3e-2, rtol=3e-2)
+    if wide and N >= o.PAIR_SWIGLU_MIN_ROWS:
+        # and through the op the parts call, with the switch that sends gate/up products to this kernel
+        old, o.USE_PAIR_GEMM = o.USE_PAIR_GEMM, True
+        try:
+            before = o.launches
+            got = o.linear_swiglu(x, w, F)
+            assert o.launches == before + 1 and torch.allclose(got.float(), want, atol=3e-2, rtol=3e-2)
+        finally:
+            o.USE_PAIR_GEMM = old
+        assert o.tc_status() == 0
+
+
 @pytest.mark.parametrize("N,O,K", [(128, 128, 64), (256, 256, 1024), (300, 517, 1000), (2048, 1024, 1024),
                                    (1000, 3072, 1024), (129, 96, 96), (4096, 256, 136), (640, 1536, 4608)])
 def test_tensor_core_gemm_bf16_and_f32(N, O, K):

@@ -58,6 +58,10 @@ _SIGNATURES = {
         "zai_gemm_tc_supports": [_I, _I, _I, _I],
         "zai_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
     },
+    "gemm_tc_pair": {
+        "zai_gemm_pair_supports": [_I, _I, _I, _I],
+        "zai_gemm_pair": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    },
     "attention_tma": {
         "zai_decode_attention_tma_supports": [_I, _I, _I, _I],
         "zai_decode_attention_tma": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _F, _P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I,
@@ -122,6 +126,8 @@ def require(dtype=None) -> None:
         libs += list(BF16_LIBS)
         if dtype is None or USE_TC_GEMM:
             libs.append("gemm_tc")
+        if dtype is None or USE_PAIR_GEMM:
+            libs.append("gemm_tc_pair")
     build.build_some(libs, verbose=True)
     for lib in libs:
         build.load(lib)
@@ -339,6 +345,32 @@ def linear(x, w, out_dtype=None):
     return torch.matmul(x, w.t())
 
 
+# The two-block tcgen05 kernel (csrc/gemm_tc_pair.cu) runs the gate/up product with SwiGLU in its
+# epilogue in the time the library's product and the activation kernel take together at the 350M
+# shape (38 us against 36-41 us at 2048 rows) and is 3 % behind them at the 1.2B shape, so it is an
+# option, not the default: ZAI_PAIR_GEMM=1 sends gate/up products of this many rows or more to it.
+PAIR_SWIGLU_MIN_ROWS = int(os.environ.get("ZAI_PAIR_SWIGLU_MIN_ROWS", "1024"))
+USE_PAIR_GEMM = os.environ.get("ZAI_PAIR_GEMM", "0") == "1"
+
+
+def gemm_pair(x, w, epilogue, out_cols, out_dtype, wide=-1):
+    """The two-block tcgen05 product kernel: x [N, K] times w [O, K] transposed with the epilogue
+    (0 bfloat16, 1 32-bit, 2 SwiGLU over stacked gate|up rows); None if it does not take the operands."""
+    global _tc_status
+    _cuda(x, w)
+    N, (O, K) = x.shape[0], w.shape
+    if w.dtype != torch.bfloat16 or x.dtype != torch.bfloat16 or not x.is_contiguous() or not w.is_contiguous():
+        return None
+    if not _fn("gemm_tc_pair", "zai_gemm_pair_supports")(N, O, K, epilogue):
+        return None
+    if _tc_status is None:
+        _tc_status = torch.zeros(1, dtype=torch.int32, device=w.device)
+    y = torch.empty((N, out_cols), dtype=out_dtype, device=w.device)
+    _check(_fn("gemm_tc_pair", "zai_gemm_pair")(_ptr(y), _ptr(w), _ptr(x), _ptr(_tc_status), N, O, K, epilogue, wide,
+                                                _stream()), "gemm_pair")
+    return y
+
+
 def linear_swiglu(x, w_gate_up, ff_dim):
     """silu(x . Wgate^T) * (x . Wup^T) with the two matrices stacked as [2F, K]."""
     if x.dtype == torch.bfloat16:
@@ -350,6 +382,10 @@ def linear_swiglu(x, w_gate_up, ff_dim):
         y = _tensor_core(x, w_gate_up, _EPI_SWIGLU, ff_dim, torch.bfloat16)
         if y is not None:
             return y
+        if USE_PAIR_GEMM and x.shape[0] >= PAIR_SWIGLU_MIN_ROWS:
+            y = gemm_pair(x, w_gate_up, _EPI_SWIGLU, ff_dim, torch.bfloat16)
+            if y is not None:
+                return y
     return silu_mul(linear(x, w_gate_up), ff_dim)
 
 
