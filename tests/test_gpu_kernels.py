@@ -332,6 +332,29 @@ def test_skinny_gemm_swiglu(M, F, K):
     assert got.shape == (M, F) and torch.allclose(got.float(), want, atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("M", [2, 9, 16, 17, 33, 64])
+@pytest.mark.parametrize("F,K,eps", [(4608, 1024, 1e-5), (100, 1000, 1e-3), (192, 64, 1e-6), (1536, 256, 1e-5)])
+def test_norm_and_swiglu(M, F, K, eps):
+    """Residual addition, norm, the gate/up product and SwiGLU: one kernel up to 16 rows, the norm
+    kernel, the library's product and the activation kernel beyond."""
+    o = ops()
+    g = torch.Generator().manual_seed(24)
+    h = (torch.randn(M, K, generator=g) * 3).cuda()
+    delta = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    gamma = (1 + 0.1 * torch.randn(K, generator=g)).cuda()
+    w = (torch.randn(2 * F, K, generator=g) * K ** -0.5).to(torch.bfloat16).cuda()
+    hsum = h + delta.float()
+    xn = (hsum * torch.rsqrt((hsum * hsum).mean(-1, keepdim=True) + eps) * gamma).to(torch.bfloat16)
+    gu = xn.float() @ w.float().t()
+    want = torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]
+    lazy = _lazy(h.clone(), delta, gamma, eps)
+    before = o.launches
+    got = o.linear_swiglu(lazy, w, F)
+    assert o.launches == before + (1 if M <= 16 else 2)        # (the library's product is not counted)
+    assert got.shape == (M, F) and torch.allclose(got.float(), want, atol=3e-2, rtol=3e-2)
+    assert torch.equal(lazy.residual.data, hsum)
+
+
 @pytest.mark.parametrize("M", [1, 5, 8, 24, 64])
 @pytest.mark.parametrize("O,K,eps", [(3072, 1024, 1e-5), (288, 96, 1e-6), (517, 1000, 1e-3)])
 def test_skinny_gemm_with_norm_residual_and_gathered_rows(M, O, K, eps):
