@@ -100,10 +100,20 @@ def round_rows(n: int) -> int:
     return -(-n // step) * step
 
 
+def round_count(n: int) -> int:
+    """The counts of spans and of wanted rows that a bucket is made for: 8, 16, 32, 64, then multiples
+    of 64.  (Coarse on purpose: a spare span or wanted row costs next to nothing, a bucket that is
+    met too rarely to be captured costs a step launched kernel by kernel.)"""
+    for c in (8, 16, 32, 64):
+        if n <= c:
+            return c
+    return -(-n // 64) * 64
+
+
 class ShapeGraphs:
     """Graphs for steps that are not single-token steps (prompt portions, alone or beside decoded
     tokens).  A graph serves every step of its bucket: the row count rounded up (`round_rows`), the
-    number of spans and of wanted rows rounded up to multiples of 8.  A step is brought to its bucket
+    number of spans and of wanted rows rounded up (`round_count`).  A step is brought to its bucket
     with a span of the null request for the spare rows (null slot and page), spans without tokens,
     and wanted rows that repeat row 0; what the kernels launch depends on those rounded counts only
     (span attention launches an upper bound of its blocks of query rows).  A bucket is captured the
@@ -123,7 +133,7 @@ class ShapeGraphs:
     def key(spans) -> tuple:
         n = sum(len(s[2]) for s in spans)
         r = sum(len(s[3]) for s in spans)
-        return round_rows(n), -(-(len(spans) + 1) // 8) * 8, -(-r // 8) * 8
+        return round_rows(n), round_count(len(spans) + 1), round_count(r)
 
     def _fill(self, k, spans, tables):
         """The step in its bucket's layout: (spans, tables) with the padding spans added."""
