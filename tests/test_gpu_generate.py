@@ -163,6 +163,71 @@ def test_steps_of_one_bucket_share_a_graph_and_agree(tiny_models, dtype):
         traces.check_request(got[None], want[None], dtype, f"{dtype} request {k} after bucketed steps")
 
 
+@pytest.mark.parametrize("name", ["B", "C"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decoding_requests_beside_prompt_portions(tiny_models, name, dtype):
+    """Steps with 9 to 12 decoding requests in front and one or two prompt portions behind them: in
+    bfloat16 the first 8 one-token spans go through the single-token attention kernel, the rest
+    through the span kernel.  Every wanted row against the plain implementation, run eagerly and
+    (from the third step of the bucket on) from a graph; the contexts differ, cross page edges and
+    grow from step to step."""
+    from zig_ai_b200.engine.runner import load_runner
+    d = tiny_models[name]
+    c, W = plain_lfm2.read_config(d), plain_lfm2.read_weights(d)
+    g = random.Random(31)
+    V, ps = c["vocab_size"], PAGE_SIZE[name]
+    runner = load_runner(d, dtype, max_tokens=16 * 256, page_size=ps, max_requests=16)
+    n_dec = 12
+    toks = {k: [g.randrange(V) for _ in range(ps * (k % 3) + 3 + 5 * k)] for k in range(n_dec)}
+    for k in toks:
+        runner.add_request(k)
+        runner.step([(k, toks[k], [])])
+    prompts = {100 + i: [g.randrange(V) for _ in range(400)] for i in range(3)}
+    for k in prompts:
+        runner.add_request(k)
+    plain_cache = {}
+
+    def plain_row(k, seq):
+        key = (k, len(seq))
+        if key not in plain_cache:
+            plain_cache[key] = plain_lfm2.forward(c, W, seq).numpy()
+        return plain_cache[key]
+
+    done = {k: 0 for k in prompts}
+    pairs = {}
+    for step in range(8):
+        live = list(range(n_dec)) if step % 2 == 0 else list(range(n_dec - 3))
+        entries, checks = [], []
+        for k in live:
+            t = g.randrange(V)
+            toks[k].append(t)
+            entries.append((k, [t], [0]))
+            checks.append((k, list(toks[k]), [len(toks[k]) - 1]))
+        for k in list(prompts)[: 1 + step % 2]:
+            n = g.randint(30, 40) if step % 2 == 0 else g.randint(15, 20)      # 39 to 52 rows a step: one bucket
+            part = prompts[k][done[k]:done[k] + n]
+            want = sorted({0, n - 1})
+            entries.append((k, part, want))
+            checks.append((k, prompts[k][:done[k] + n], [done[k] + w for w in want]))
+            done[k] += n
+        got = runner.step(entries).cpu().numpy()
+        at = 0
+        for k, seq, rows in checks:
+            ref = plain_row(k, seq)
+            for r in rows:
+                assert np.isfinite(got[at]).all(), (step, k, r)
+                pairs.setdefault(k, ([], []))
+                pairs[k][0].append(got[at])
+                pairs[k][1].append(ref[r])
+                at += 1
+        assert at == got.shape[0]
+    for k, (a, b) in pairs.items():               # a request's rows of all steps together, as in the replay tests
+        traces.check_request(np.stack(a), np.stack(b), dtype, f"{dtype} request {k}")
+    if dtype == "bfloat16":
+        assert runner.shape_graphs.replays >= 2
+        assert any(k[3] == 8 for k in runner.shape_graphs.graphs)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("temperature", [0.0, 0.9])
 def test_a_step_ahead_of_the_host_changes_no_token(tiny_models, dtype, temperature):

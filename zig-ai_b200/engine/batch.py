@@ -34,6 +34,8 @@ class StepBatch:
     decode_only: bool = False      # every span is one token
     q_lens: Sequence[int] = ()
     request_ids: Sequence = ()
+    single_first: int = 0          # this many leading spans (0, 8, 16, 32, ...) are one token each: in a step that also
+    #                                holds longer spans, attention may run them through the kernel for single tokens
     attn_tiles: Optional[int] = None   # blocks of query rows to launch for span attention (default: from q_lens);
     #                                    a captured graph launches an upper bound for its bucket of step shapes
     scratch: Dict = field(default_factory=dict)   # what kernels compute once per step (rotation tables)
@@ -96,6 +98,20 @@ def pack_host(spans, tables: Dict[int, "np.ndarray"], widths: Dict[int, int] = N
     return flat, PackedLayout(N, S, R, layout_tables, off, q_lens, ctx, rids)
 
 
+def leading_singles(q_lens) -> int:
+    """How many spans at the front of a step are one token each, rounded down to 8, 16, 32, 64, ...
+    (0 below 8: few values, since a step's graph is made for one of them); 0 if that is all of the
+    spans (a step of single tokens has its own path)."""
+    n = 0
+    for q in q_lens:
+        if q != 1:
+            break
+        n += 1
+    if n == len(q_lens) or n < 8:
+        return 0
+    return 1 << (n.bit_length() - 1)
+
+
 def batch_views(ops, dtype, dev: torch.Tensor, lay: PackedLayout) -> StepBatch:
     """A StepBatch whose tensors are views of the flat device buffer `dev`."""
     N, S, R = lay.N, lay.S, lay.R
@@ -106,7 +122,7 @@ def batch_views(ops, dtype, dev: torch.Tensor, lay: PackedLayout) -> StepBatch:
         at += n
     bt = {g: (dev[o:o + S * w].view(S, w) if S else dev[o:o].view(0, 1)) for g, (o, w) in lay.tables.items()}
     return StepBatch(
-        ops=ops, dtype=dtype, n_tokens=N, n_seqs=S, n_wanted=R,
+        single_first=leading_singles(lay.q_lens), ops=ops, dtype=dtype, n_tokens=N, n_seqs=S, n_wanted=R,
         token_ids=views[0], positions=views[1], seq_idx=views[2], cu_q=views[3], ctx_lens=views[4],
         slot_ids=views[5], logit_rows=views[6], block_tables=bt,
         max_q_len=max(lay.q_lens) if lay.q_lens else 0,

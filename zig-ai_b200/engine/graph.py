@@ -113,7 +113,8 @@ def round_count(n: int) -> int:
 class ShapeGraphs:
     """Graphs for steps that are not single-token steps (prompt portions, alone or beside decoded
     tokens).  A graph serves every step of its bucket: the row count rounded up (`round_rows`), the
-    number of spans and of wanted rows rounded up (`round_count`).  A step is brought to its bucket
+    number of spans and of wanted rows rounded up (`round_count`), and the number of leading one-token
+    spans rounded down to 0, 8, 16, 32, ... (attention runs those through its single-token kernel).  A step is brought to its bucket
     with a span of the null request for the spare rows (null slot and page), spans without tokens,
     and wanted rows that repeat row 0; what the kernels launch depends on those rounded counts only
     (span attention launches an upper bound of its blocks of query rows).  A bucket is captured the
@@ -133,11 +134,12 @@ class ShapeGraphs:
     def key(spans) -> tuple:
         n = sum(len(s[2]) for s in spans)
         r = sum(len(s[3]) for s in spans)
-        return round_rows(n), round_count(len(spans) + 1), round_count(r)
+        from .batch import leading_singles
+        return round_rows(n), round_count(len(spans) + 1), round_count(r), leading_singles([len(s[2]) for s in spans] + [0])
 
     def _fill(self, k, spans, tables):
         """The step in its bucket's layout: (spans, tables) with the padding spans added."""
-        n_rows, n_spans, _ = k
+        n_rows, n_spans = k[0], k[1]
         n = sum(len(s[2]) for s in spans)
         extra = n_spans - len(spans)
         spans = list(spans) + [(None, 0, [0] * (n_rows - n), [], NULL_SLOT)] + [(None, 0, [], [], NULL_SLOT)] * (extra - 1)
@@ -152,6 +154,7 @@ class ShapeGraphs:
         batch = batch_views(self.ops, self.dtype, dev, lay)
         batch.max_kv_len = max(self.widths.values(), default=1) * self.cache.page_size
         batch.attn_tiles = k[0] // 128 + k[1]                  # every span may end with a partial block of query rows
+        batch.single_first = k[3]
         return batch
 
     def run(self, spans, tables):

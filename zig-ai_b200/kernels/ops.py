@@ -522,18 +522,29 @@ def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=Non
     bt = cache.block_table
     if (impl != "general" and q.dtype == torch.bfloat16
             and _fn("attention_mma", "zai_attention_mma_supports")(head_dim, heads, kv_heads)):
-        if step.decode_only:
+        def single_tokens(n):
+            # rows 0..n-1 are one token each, row i of span i: keys split over blocks, then combined
             chunk = _fn("attention_mma", "zai_decode_chunk_keys")()
             n_chunks = max(-(-int(step.max_kv_len) // chunk), 1)
-            part_o = torch.empty((N, heads, n_chunks, head_dim), dtype=torch.float32, device=q.device)
-            part_ml = torch.empty((N, heads, n_chunks, 2), dtype=torch.float32, device=q.device)
+            part_o = torch.empty((n, heads, n_chunks, head_dim), dtype=torch.float32, device=q.device)
+            part_ml = torch.empty((n, heads, n_chunks, 2), dtype=torch.float32, device=q.device)
             _check(_fn("attention_mma", "zai_decode_attention_mma")(
                 _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(q), _ptr(cache.pages), _ptr(bt), bt.shape[1],
-                _ptr(step.positions), N, n_chunks, cache.page_size, heads, kv_heads, head_dim, float(scale),
+                _ptr(step.positions), n, n_chunks, cache.page_size, heads, kv_heads, head_dim, float(scale),
                 int(window or 0), _stream()), "decode attention", 2)
+
+        if step.decode_only:
+            single_tokens(N)
         else:
+            # the one-token spans at the front of a mixed step (decoding requests beside prompt portions)
+            # would each fill a whole block of query rows of the span kernel: they go to the other one
+            ns = int(getattr(step, "single_first", 0)) if (SPLIT_MIXED_ATTENTION and q.is_contiguous()) else 0
+            if ns:
+                single_tokens(ns)
+            S = step.n_seqs - ns
+            cu_q, ctx_lens, bt = step.cu_q[ns:], step.ctx_lens[ns:], bt[ns:]
             block_rows = _fn("attention_mma", "zai_prefill_block_rows")()
-            n_tiles = step.attn_tiles if getattr(step, "attn_tiles", None) else sum(-(-n // block_rows) for n in step.q_lens)
+            n_tiles = (step.attn_tiles - ns) if getattr(step, "attn_tiles", None) else sum(-(-n // block_rows) for n in step.q_lens[ns:])
             if (impl != "mma" and (USE_TC_ATTENTION or impl == "tcgen05") and q.is_contiguous()
                     and _fn("attention_tc", "zai_prefill_attention_tc_supports")(head_dim, heads, kv_heads, cache.page_size)):
                 global _tc_status
@@ -541,12 +552,12 @@ def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=Non
                     _tc_status = torch.zeros(1, dtype=torch.int32, device=q.device)
                 _check(_fn("attention_tc", "zai_prefill_attention_tc")(
                     _ptr(out), _ptr(q), _ptr(cache.pages), cache.pages.shape[0], _ptr(_tc_status), _ptr(bt), bt.shape[1],
-                    _ptr(step.cu_q), _ptr(step.ctx_lens), N, step.n_seqs, n_tiles, cache.page_size, heads, kv_heads,
+                    _ptr(cu_q), _ptr(ctx_lens), N, S, n_tiles, cache.page_size, heads, kv_heads,
                     head_dim, float(scale), int(window or 0), _stream()), "prefill attention (tcgen05)")
                 return out
             _check(_fn("attention_mma", "zai_prefill_attention_mma")(
-                _ptr(out), _ptr(q), _ptr(cache.pages), _ptr(bt), bt.shape[1], _ptr(step.cu_q), _ptr(step.ctx_lens),
-                step.n_seqs, n_tiles, cache.page_size, heads, kv_heads, head_dim, float(scale), int(window or 0),
+                _ptr(out), _ptr(q), _ptr(cache.pages), _ptr(bt), bt.shape[1], _ptr(cu_q), _ptr(ctx_lens),
+                S, n_tiles, cache.page_size, heads, kv_heads, head_dim, float(scale), int(window or 0),
                 _stream()), "prefill attention")
         return out
     _check(_fn("attention", "zai_paged_attention_general")(
@@ -557,6 +568,7 @@ def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=Non
 
 
 _tickets = {}
+SPLIT_MIXED_ATTENTION = os.environ.get("ZAI_SPLIT_MIXED_ATTENTION", "1") == "1"
 USE_TMA_ATTENTION = os.environ.get("ZAI_TMA_ATTENTION", "1") == "1"   # keys and values by TMA where the sizes allow
 DECODE_BLOCKS_WANTED = 500
 
