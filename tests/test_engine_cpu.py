@@ -101,3 +101,18 @@ def test_mixed_batches_with_page_reuse(tiny_models, name):
     for k in reqs:
         diff = (torch.cat(got[k]).double() - want[k]).abs().max()
         assert diff < 2e-4, (k, diff)
+
+
+def test_step_graph_buckets():
+    """What a step's bucket is made of: rows rounded up, spans and wanted rows rounded up coarsely,
+    the leading one-token spans rounded down (and none for a step of single tokens only)."""
+    from zig_ai_b200.engine.batch import leading_singles
+    from zig_ai_b200.engine.graph import ShapeGraphs, round_count, round_rows
+    assert [round_rows(n) for n in (1, 8, 9, 16, 17, 32, 33, 256, 257, 2048)] == [8, 8, 16, 16, 32, 32, 64, 256, 320, 2048]
+    assert [round_count(n) for n in (0, 1, 8, 9, 16, 17, 33, 64, 65, 129)] == [8, 8, 8, 16, 16, 32, 64, 64, 128, 192]
+    assert [leading_singles([1] * n + [5]) for n in (0, 7, 8, 9, 15, 16, 31, 33, 64, 65)] == [0, 0, 8, 8, 8, 16, 16, 32, 64, 64]
+    assert leading_singles([1] * 9) == 0 and leading_singles([]) == 0 and leading_singles([3, 1, 1, 1, 1, 1, 1, 1, 1, 1]) == 0
+    span = lambda n, wanted: ("r", 0, [0] * n, list(range(wanted)), 0)
+    assert ShapeGraphs.key([span(1, 1)] * 9 + [span(30, 2)]) == (64, 16, 16, 8)
+    assert ShapeGraphs.key([span(1, 1)] * 12 + [span(20, 1), span(18, 1)]) == (64, 16, 16, 8)
+    assert ShapeGraphs.key([span(2000, 1)]) == (2048, 8, 8, 0)
