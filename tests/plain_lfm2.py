@@ -184,15 +184,17 @@ def block(h, W, i, kind, c):
     return h + swiglu(r2, W, pre)
 
 
-def forward(c, W, tokens):
-    """Logits [T, vocab] for one whole sequence: embedding row lookup without scaling
-    (src/transformer/embedding.zig:6-31), the blocks, the final norm `token_embd_norm` and the
-    head, which is the embedding table when tied (src/loader/gguf_model.zig:47-54,68-78;
-    src/main.zig:867-878)."""
+def forward(c, W, tokens, rows=None):
+    """Logits [T, vocab] for one whole sequence (only at the positions `rows` if given): embedding
+    row lookup without scaling (src/transformer/embedding.zig:6-31), the blocks, the final norm
+    `token_embd_norm` and the head, which is the embedding table when tied
+    (src/loader/gguf_model.zig:47-54,68-78; src/main.zig:867-878)."""
     ids = torch.as_tensor(tokens, dtype=torch.long)
     h = W["token_embd.weight"][ids]
     for i, kind in enumerate(layer_kinds(c)):
         h = block(h, W, i, kind, c)
+    if rows is not None:
+        h = h[torch.as_tensor(list(rows), dtype=torch.long)]
     n = rms_norm(h, W["token_embd_norm.weight"], c.get("norm_eps", 1e-5))
     tied = c.get("tie_embedding", c.get("tie_word_embeddings", True))
     head = W["token_embd.weight"] if tied else W["output.weight"]

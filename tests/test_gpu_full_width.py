@@ -1,0 +1,78 @@
+"""The layer sizes that the benchmark runs (hidden 1024, 16 query and 8 key/value heads of 64,
+feed-forward 4608, vocabulary 65536), four layers deep, against the plain implementation: the kernels
+are tested one by one at these sizes elsewhere; here they run as the model's chain of dependent
+launches (prompt portions beside decoding requests, then decode steps replayed from graphs), where
+one kernel's early start can meet another kernel's data."""
+import random
+
+import numpy as np
+import pytest
+
+import plain_lfm2
+import traces
+
+pytestmark = pytest.mark.gpu
+
+FULL_WIDTH = {
+    "architectures": ["Lfm2ForCausalLM"], "hidden_size": 1024, "num_hidden_layers": 4,
+    "layer_types": ["conv", "full_attention", "full_attention", "conv"],
+    "num_attention_heads": 16, "num_key_value_heads": 8, "head_dim": 64,
+    "block_ff_dim": 6656, "block_auto_adjust_ff_dim": True, "block_multiple_of": 256, "vocab_size": 65536,
+    "rope_theta": 1000000.0, "conv_L_cache": 3, "conv_bias": False, "use_qk_norm": True, "norm_eps": 1e-5,
+    "tie_embedding": True, "max_position_embeddings": 4096,
+}
+
+
+@pytest.fixture(scope="module")
+def full_width_model(tmp_path_factory):
+    from zig_ai_b200.config import config_from_dict
+    from zig_ai_b200.weights import write_random_model
+    d = str(tmp_path_factory.mktemp("full_width"))
+    write_random_model(config_from_dict(FULL_WIDTH), 41, d, matrix_std="fan_in")
+    return d
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_benchmark_layer_sizes_against_plain(full_width_model, dtype):
+    from zig_ai_b200.engine.runner import load_runner
+    d = full_width_model
+    c, W = plain_lfm2.read_config(d), plain_lfm2.read_weights(d)
+    g = random.Random(43)
+    V = c["vocab_size"]
+    lengths = {"a": 600, "b": 40, "c": 1, "d": 257, "e": 130}
+    toks = {k: [g.randrange(V) for _ in range(n)] for k, n in lengths.items()}
+    runner = load_runner(d, dtype, max_tokens=4096, page_size=64, max_requests=8)
+    for k in toks:
+        runner.add_request(k)
+    got, rows = {k: [] for k in toks}, {k: [] for k in toks}
+
+    def run(entries):
+        out = runner.step(entries).cpu().numpy()
+        at = 0
+        for k, new, want in entries:
+            base = runner.processed[k] - len(new)
+            for w in want:
+                assert np.isfinite(out[at]).all(), (k, base + w)
+                got[k].append(out[at].copy())
+                rows[k].append(base + w)
+                at += 1
+        assert at == out.shape[0]
+
+    # the prompts in portions: a in three (320, 200, 80), the others whole beside them
+    run([("a", toks["a"][:320], [0, 255, 256, 319]), ("b", toks["b"], [39])])
+    run([("c", toks["c"], [0]), ("a", toks["a"][320:520], [0, 199]), ("d", toks["d"], [0, 256])])
+    run([("a", toks["a"][520:], [79]), ("e", toks["e"], [129])])
+    # decode steps of all five (a graph of single tokens), some with a request left out
+    for step in range(12):
+        live = [k for k in toks if not (step % 5 == 3 and k == "b")]
+        entries = []
+        for k in live:
+            t = g.randrange(V)
+            toks[k].append(t)
+            entries.append((k, [t], [0]))
+        run(entries)
+    if dtype == "bfloat16":
+        assert runner.graphs.replays >= 10
+    for k in toks:
+        want = plain_lfm2.forward(c, W, toks[k], rows=rows[k]).numpy()
+        traces.check_request(np.stack(got[k]), want, dtype, f"{dtype} request {k}")
