@@ -23,19 +23,35 @@ FULL_WIDTH = {
 }
 
 
+# the widths of the three model sizes that bench.py knows (its --model), the larger two with two layers
+WIDTHS = {
+    "350m": {},
+    "700m": dict(hidden_size=1536, num_attention_heads=24, block_ff_dim=10752, num_hidden_layers=2,
+                 layer_types=["conv", "full_attention"]),
+    "1.2b": dict(hidden_size=2048, num_attention_heads=32, block_ff_dim=12288, num_hidden_layers=2,
+                 layer_types=["full_attention", "conv"]),
+}
+
+
 @pytest.fixture(scope="module")
-def full_width_model(tmp_path_factory):
+def full_width_models(tmp_path_factory):
     from zig_ai_b200.config import config_from_dict
     from zig_ai_b200.weights import write_random_model
-    d = str(tmp_path_factory.mktemp("full_width"))
-    write_random_model(config_from_dict(FULL_WIDTH), 41, d, matrix_std="fan_in")
-    return d
+    made = {}
+
+    def get(width):
+        if width not in made:
+            d = str(tmp_path_factory.mktemp("full_width_" + width.replace(".", "_")))
+            write_random_model(config_from_dict(dict(FULL_WIDTH, **WIDTHS[width])), 41, d, matrix_std="fan_in")
+            made[width] = d
+        return made[width]
+    return get
 
 
-@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
-def test_benchmark_layer_sizes_against_plain(full_width_model, dtype):
+@pytest.mark.parametrize("width,dtype", [("350m", "bfloat16"), ("350m", "float32"), ("700m", "bfloat16"), ("1.2b", "bfloat16")])
+def test_benchmark_layer_sizes_against_plain(full_width_models, width, dtype):
     from zig_ai_b200.engine.runner import load_runner
-    d = full_width_model
+    d = full_width_models(width)
     c, W = plain_lfm2.read_config(d), plain_lfm2.read_weights(d)
     g = random.Random(43)
     V = c["vocab_size"]
