@@ -24,8 +24,43 @@ def _f(x):
     return x.to(torch.float32)
 
 
+# ---- the status word, as the kernels keep it (csrc/common.cuh: ZaiStatusBit): an id outside its bound is
+# replaced by id 0 and a bit is raised; the step's results are then void.
+STATUS_BITS = {1: "a bounded wait inside a kernel ran out", 2: "a token id outside the vocabulary",
+               4: "a block-table entry outside the page pool", 8: "a state slot outside the slots",
+               16: "a position outside its request's block-table row"}
+_status = torch.zeros(1, dtype=torch.int32)
+
+
+def status_tensor(device=None):
+    return _status
+
+
+def read_status(device=None) -> int:
+    v = int(_status.item())
+    _status.zero_()
+    return v
+
+
+def describe_status(code: int) -> str:
+    return "; ".join(text for bit, text in STATUS_BITS.items() if code & bit) or f"status {code}"
+
+
+def _raise(bit: int) -> None:
+    _status[0] |= bit
+
+
+def _checked(ids, bound: int, bit: int):
+    """`ids` with every entry outside [0, bound) replaced by 0 (and the bit raised if there is one)."""
+    bad = (ids < 0) | (ids >= bound)
+    if bool(bad.any()):
+        _raise(bit)
+        ids = torch.where(bad, torch.zeros_like(ids), ids)
+    return ids
+
+
 def embed(ids, table):
-    return _f(table[ids.long()])
+    return _f(table[_checked(ids.long(), table.shape[0], 2)])
 
 
 def add_rmsnorm(h, delta, w, eps, out_dtype):
@@ -57,7 +92,7 @@ def short_conv(bcx, conv_w, conv_b, state, step, taps, write_state=True):
     L = taps
     out = torch.empty((N, C), dtype=bcx.dtype, device=bcx.device)
     cu = step.cu_q.tolist()
-    slots = step.slot_ids.tolist()
+    slots = _checked(step.slot_ids.long(), state.shape[0], 8).tolist()
     for s in range(step.n_seqs):
         a, b = cu[s], cu[s + 1]
         x = _f(bcx[a:b])
@@ -105,7 +140,12 @@ def _page_rows(step, cache):
     ps = cache.page_size
     pos = step.positions.long()
     bt = cache.block_table.long()
-    page = bt[step.seq_idx.long(), pos // ps]
+    idx = pos // ps
+    outside = (idx < 0) | (idx >= bt.shape[1])
+    if bool(outside.any()):
+        _raise(16)
+    page = bt[step.seq_idx.long(), torch.where(outside, torch.zeros_like(idx), idx)]
+    page = torch.where(outside, torch.zeros_like(page), _checked(page, cache.pages.shape[0], 4))
     return page, pos % ps
 
 
@@ -150,7 +190,10 @@ def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=Non
         a, b = cu[s], cu[s + 1]
         total = ctx[s] + (b - a)
         n_pages = -(-total // ps)
-        ids = cache.block_table[s, :n_pages].long()
+        if n_pages > cache.block_table.shape[1]:
+            _raise(16)
+        ids = _checked(cache.block_table[s, :n_pages].long(), cache.pages.shape[0], 4)
+        ids = torch.cat([ids, ids.new_zeros(n_pages - ids.shape[0])])
         kv = _f(cache.pages[ids])                                  # [pages, 2, Hkv, ps, D]
         k = kv[:, 0].permute(1, 0, 2, 3).reshape(kv_heads, n_pages * ps, D)[:, :total]
         v = kv[:, 1].permute(1, 0, 2, 3).reshape(kv_heads, n_pages * ps, D)[:, :total]

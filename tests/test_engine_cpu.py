@@ -116,3 +116,87 @@ def test_step_graph_buckets():
     assert ShapeGraphs.key([span(1, 1)] * 9 + [span(30, 2)]) == (64, 16, 16, 8)
     assert ShapeGraphs.key([span(1, 1)] * 12 + [span(20, 1), span(18, 1)]) == (64, 16, 16, 8)
     assert ShapeGraphs.key([span(2000, 1)]) == (2048, 8, 8, 0)
+
+
+@pytest.mark.parametrize("page_size", [8, 16, 64])
+def test_padding_spans_stay_inside_their_table_rows(page_size):
+    """The span of the null request that rounds a step's rows up lies at positions 0..pad-1; its row of
+    every block table covers those positions (with null pages), in eager steps and in step graphs'
+    buckets, also when the real requests are short and the pages small."""
+    import numpy as np
+    from zig_ai_b200.engine.batch import pack_host
+    from zig_ai_b200.engine.graph import ShapeGraphs
+    from zig_ai_b200.engine.runner import pad_rows
+
+    def check(spans, tables, widths=None):
+        flat, lay = pack_host(spans, tables, widths)
+        for g, (off, w) in lay.tables.items():
+            table = flat[off:off + lay.S * w].reshape(lay.S, w)
+            for s, (c, n) in enumerate(zip(lay.ctx, lay.q_lens)):
+                if n:
+                    assert (c + n - 1) // page_size < w, (s, c, n, w)
+            assert (table[len(spans_in):] == 0).all()              # the added spans see null pages only
+        assert lay.total == flat.shape[0]
+
+    for n_req, n_tok in [(4, 9), (3, 6), (17, 1), (1, 20), (2, 130), (5, 60)]:
+        spans_in = [(f"r{i}", 0, [1] * n_tok, [n_tok - 1], i + 1) for i in range(n_req)]
+        width = max(-(-n_tok // page_size), 1)
+        tables_in = {0: np.arange(1, n_req * width + 1, dtype=np.int32).reshape(n_req, width)}
+        spans, tables = pad_rows(spans_in, tables_in, page_size)
+        assert sum(len(s[2]) for s in spans) % 32 == 0 or sum(len(s[2]) for s in spans) <= 16
+        check(spans, tables)
+
+        class Pool:
+            pass
+        pool = Pool()
+        pool.page_size = page_size
+        sg = ShapeGraphs(None, pool, None, None, None, {0: width})       # a pool of few positions: narrow tables
+        k = sg.key(spans_in)
+        spans, tables = sg._fill(k, spans_in, tables_in)
+        assert sum(len(s[2]) for s in spans) == k[0] and len(spans) == k[1]
+        check(spans, tables, sg.widths)
+
+
+def test_a_raised_status_word_voids_the_step(tiny_models):
+    """An id outside its bound is replaced by id 0 by the kernel that meets it and raises the status word;
+    the step function reads the word with the step's results and raises (here on the plain stand-ins
+    of the kernels, which keep the same word)."""
+    from zig_ai_b200.engine.runner import StepError
+    r = make_runner(tiny_models["A"], "A")
+    V = r.model.vocab_size
+    r.add_request("a")
+    r.step([("a", random_tokens(V, 20, 3), [19])])
+    # a block-table entry that points outside the pool (the host mirror of the request's table is spoilt)
+    rc = r.cache.requests["a"]
+    g = r.cache.paged_groups()[0]
+    keep = int(r.cache._rows[g][rc.slot, 0])
+    r.cache._rows[g][rc.slot, 0] = r.cache.num_pages + 7
+    with pytest.raises(StepError, match="outside the page pool"):
+        r.step([("a", [1], [0])])
+    r.cache._rows[g][rc.slot, 0] = keep
+    r.step([("a", [2], [0])])                                   # the word was cleared by the read: the next step is fine
+    # a slot outside the slots
+    slot, rc.slot = rc.slot, r.cache.max_requests + 3
+    r.cache._rows[g] = __import__("numpy").vstack([r.cache._rows[g], r.cache._rows[g][:4]])
+    with pytest.raises(StepError, match="slot outside"):
+        r.step([("a", [3], [0])])
+    rc.slot = slot
+    # a token id outside the vocabulary that the host check was told to trust
+    with pytest.raises(StepError, match="outside the vocabulary"):
+        r.step([("a", [V + 5], [0])], trusted=True)
+    assert ref_ops.read_status() == 0
+
+
+def test_the_engine_reads_the_status_word_with_the_token_ids(tiny_models):
+    from zig_ai_b200.engine.engine import Engine
+    from zig_ai_b200.engine.runner import StepError
+    from zig_ai_b200.sampling.sampler import SamplingParams
+    eng = Engine(tiny_models["A"], "float32", max_num_seqs=2, max_tokens=256, page_size=16, device="cpu", ops=ref_ops)
+    eng.add_request([1, 2, 3, 4, 5], SamplingParams(temperature=0.0, max_new_tokens=8))
+    eng.step()
+    eng.step()
+    ref_ops._raise(1)                                             # as a kernel whose bounded wait ran out would
+    with pytest.raises(StepError, match="bounded wait"):
+        for _ in range(3):
+            eng.step()
+    assert ref_ops.read_status() == 0

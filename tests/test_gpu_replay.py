@@ -63,6 +63,11 @@ def test_mixed_batches_in_a_small_pool(tiny_models, plain, tmp_path, name, dtype
     max_tokens = longest + 128                       # a few requests at most: pages must be used again
     steps = traces.number(traces.mixed(reqs, 5, max_tokens))
     assert max(len(s["entries"]) for s in steps) >= 2
+    stats = {}
     got = traces.run_trace(tiny_models[name], dtype, steps, max_tokens=max_tokens, out_dir=str(tmp_path / "o"),
-                           vocab=vocab, page_size=PAGE_SIZE[name])
+                           vocab=vocab, page_size=PAGE_SIZE[name], stats=stats)
     compare(got, reqs, want, "m", dtype)
+    # the pool is as small as asked for, every page of it was in use at some time, and pages that one
+    # request gave back were handed to another
+    assert stats["num_pages"] * stats["page_size"] == -(-max_tokens // PAGE_SIZE[name]) * PAGE_SIZE[name]
+    assert stats["pages_reused"] > 0 and stats["group0_pages_used"] == 0 and stats["slots_used"] == 0

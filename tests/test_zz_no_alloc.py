@@ -80,3 +80,7 @@ def test_static_scratch_entry_point_refuses_what_does_not_fit():
     assert torch.isnan(out.float()).all()                 # nothing was launched
     code, _ = call_static(fn, q, step, view, 16, 8, 64, n_chunks=1)
     assert code == 0
+    # a head count of zero is a size the kernel does not take: refused before any arithmetic with it
+    code, out = call_static(fn, q, step, view, 16, 0, 64, n_chunks=1)
+    assert code == -2 and b"size" in msg(code)
+    assert torch.isnan(out.float()).all()

@@ -93,12 +93,15 @@ def number(steps, first=0):
     return [dict(s, step=first + i) for i, s in enumerate(steps)]
 
 
-def run_trace(model_dir, dtype, steps, max_tokens, out_dir, vocab, page_size=16, timeout=900):
-    """Run bin/trace_run on the numbered steps; returns {(request id, position): logits row}."""
+def run_trace(model_dir, dtype, steps, max_tokens, out_dir, vocab, page_size=16, timeout=900, stats=None):
+    """Run bin/trace_run on the numbered steps; returns {(request id, position): logits row}.  `stats`:
+    a dict that receives the counters the program writes when its input ends."""
     os.makedirs(out_dir, exist_ok=True)
     env = dict(os.environ)
     cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype,
            "--out", out_dir, "--max-tokens", str(max_tokens), "--page-size", str(page_size)]
+    if stats is not None:
+        cmd += ["--stats", os.path.join(out_dir, "stats.json")]
     p = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, env=env)
     got, pos = {}, {}
     try:
@@ -123,6 +126,9 @@ def run_trace(model_dir, dtype, steps, max_tokens, out_dir, vocab, page_size=16,
                 pos.pop(k, None)
         p.stdin.close()
         assert p.wait(timeout=timeout) == 0
+        if stats is not None:
+            with open(os.path.join(out_dir, "stats.json")) as f:
+                stats.update(json.load(f))
     finally:
         if p.poll() is None:
             p.kill()

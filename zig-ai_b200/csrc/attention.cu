@@ -18,14 +18,15 @@ template <typename T, int MAXR>
 __global__ void paged_attention_warp_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __restrict__ pages,
                                             const int* __restrict__ block_table, int table_width,
                                             const int* __restrict__ positions, const int* __restrict__ seq_idx,
-                                            int page_size, int Hq, int Hkv, int D, float scale, int window) {
+                                            int page_size, int Hq, int Hkv, int D, float scale, int window,
+                                            int num_pages, int* __restrict__ status) {
     extern __shared__ float qs[];                 // [D]
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
     const int kvh = h / (Hq / Hkv);
     const int pos = positions[t];
-    const int* table = block_table + (size_t)seq_idx[t] * table_width;
+    const ZaiTableRow table{block_table + (size_t)seq_idx[t] * table_width, table_width, num_pages, status};
     const T* qrow = q + ((size_t)t * Hq + h) * D;
     for (int d = lane; d < D; d += 32) qs[d] = to_float(qrow[d]) * scale;
     __syncwarp();
@@ -43,7 +44,7 @@ __global__ void paged_attention_warp_kernel(T* __restrict__ out, const T* __rest
         float s = -INFINITY;
         size_t krow = 0;
         if (valid) {
-            const int page = table[j / page_size];
+            const int page = table.page(j / page_size);
             krow = (size_t)page * page_stride + ((size_t)kvh * page_size + (j % page_size)) * D;
             const T* kp = pages + krow;
             float dot = 0.f;
@@ -80,7 +81,8 @@ __global__ void paged_attention_warp_kernel(T* __restrict__ out, const T* __rest
 
 ZAI_API int zai_paged_attention_general(void* out, const void* q, const void* pages, int dtype, const int* block_table,
                                         int table_width, const int* positions, const int* seq_idx, int page_size,
-                                        int N, int Hq, int Hkv, int D, float scale, int window, cudaStream_t stream) {
+                                        int N, int Hq, int Hkv, int D, float scale, int window, int num_pages, int* status,
+                                        cudaStream_t stream) {
     if (N <= 0) return ZAI_OK;
     if (D < 1 || D > 256 || Hkv < 1 || Hq % Hkv != 0 || Hq > 65535) return ZAI_BAD_SIZE;
     const dim3 grid(N, Hq);
@@ -88,11 +90,11 @@ ZAI_API int zai_paged_attention_general(void* out, const void* q, const void* pa
     if (D <= 64) {
         ZAI_DISPATCH(dtype, return launch_pdl(paged_attention_warp_kernel<T, 2>, grid, dim3(32), smem, stream,
             (T*)out, (const T*)q, (const T*)pages, block_table, table_width, positions, seq_idx, page_size, Hq, Hkv,
-            D, scale, window));
+            D, scale, window, num_pages, status));
     } else {
         ZAI_DISPATCH(dtype, return launch_pdl(paged_attention_warp_kernel<T, 8>, grid, dim3(32), smem, stream,
             (T*)out, (const T*)q, (const T*)pages, block_table, table_width, positions, seq_idx, page_size, Hq, Hkv,
-            D, scale, window));
+            D, scale, window, num_pages, status));
     }
     return launch_status();
 }

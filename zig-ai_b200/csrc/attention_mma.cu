@@ -35,7 +35,7 @@
 // stride D + 8 elements; rows outside [kstart, kend) are filled with zeros.  `page_shift` is
 // log2(page_size) if that is a power of two, else -1.
 template <int D, int NT>
-__device__ __forceinline__ void load_kv_tile(bf16* dst, const bf16* __restrict__ pages, const int* __restrict__ table,
+__device__ __forceinline__ void load_kv_tile(bf16* dst, const bf16* __restrict__ pages, const ZaiTableRow& table,
                                              int t0, int kstart, int kend, int page_size, int page_shift,
                                              size_t page_stride, size_t head_off, int tid) {
     constexpr int CH = D / 8;
@@ -47,10 +47,10 @@ __device__ __forceinline__ void load_kv_tile(bf16* dst, const bf16* __restrict__
         if (valid) {
             int page, off;
             if (page_shift >= 0) {
-                page = table[j >> page_shift];
+                page = table.page(j >> page_shift);
                 off = j & (page_size - 1);
             } else {
-                page = table[j / page_size];
+                page = table.page(j / page_size);
                 off = j % page_size;
             }
             src = pages + (size_t)page * page_stride + head_off + (size_t)off * D + c * 8;
@@ -63,7 +63,7 @@ __device__ __forceinline__ void load_kv_tile(bf16* dst, const bf16* __restrict__
 // looked up once for both.
 template <int D>
 __device__ __forceinline__ void load_kv_tile_warp(bf16* kdst, bf16* vdst, const bf16* __restrict__ pages,
-                                                  const int* __restrict__ table, int t0, int kstart, int kend,
+                                                  const ZaiTableRow& table, int t0, int kstart, int kend,
                                                   int page_size, int page_shift, size_t page_stride, size_t k_off,
                                                   size_t v_off, int lane) {
     constexpr int CH = D / 8;
@@ -75,10 +75,10 @@ __device__ __forceinline__ void load_kv_tile_warp(bf16* kdst, bf16* vdst, const 
         if (valid) {
             int page, off;
             if (page_shift >= 0) {
-                page = table[j >> page_shift];
+                page = table.page(j >> page_shift);
                 off = j & (page_size - 1);
             } else {
-                page = table[j / page_size];
+                page = table.page(j / page_size);
                 off = j % page_size;
             }
             src = pages + (size_t)page * page_stride + (size_t)off * D + c * 8;
@@ -125,7 +125,8 @@ template <int D>
 __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_mma_kernel(
     bf16* __restrict__ out, const bf16* __restrict__ q, const bf16* __restrict__ pages,
     const int* __restrict__ block_table, int table_width, const int* __restrict__ cu_q,
-    const int* __restrict__ ctx_lens, int S, int page_size, int Hq, int Hkv, float scale_log2, int window) {
+    const int* __restrict__ ctx_lens, int S, int page_size, int Hq, int Hkv, float scale_log2, int window,
+    int num_pages, int* __restrict__ status) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int ST = D + 8, NT = PREFILL_WARPS * 32, QR = PREFILL_ROWS;
     bf16* sq = reinterpret_cast<bf16*>(smem_raw);           // [QR][ST]
@@ -154,7 +155,7 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_mma_kernel(
     const int h = blockIdx.y, hk = h / (Hq / Hkv);
     const int row0 = cu_q[s], q_len = cu_q[s + 1] - row0, ctx = ctx_lens[s];
     const int rows = min(QR, q_len - i0);                   // valid query rows of this block
-    const int* table = block_table + (size_t)s * table_width;
+    const ZaiTableRow table{block_table + (size_t)s * table_width, table_width, num_pages, status};
     const size_t page_stride = (size_t)2 * Hkv * page_size * D;
     const size_t k_off = (size_t)hk * page_size * D, v_off = ((size_t)Hkv + hk) * page_size * D;
     const int kend = ctx + i0 + rows;                       // one past the last visible key of the block
@@ -293,7 +294,8 @@ template <int D>
 __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
     float* __restrict__ part_o, float* __restrict__ part_ml, const bf16* __restrict__ q,
     const bf16* __restrict__ pages, const int* __restrict__ block_table, int table_width,
-    const int* __restrict__ positions, int page_size, int Hq, int Hkv, float scale_log2, int window) {
+    const int* __restrict__ positions, int page_size, int Hq, int Hkv, float scale_log2, int window,
+    int num_pages, int* __restrict__ status) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int ST = D + 8, NS = DecodeStages<D>::N;
     bf16* sq = reinterpret_cast<bf16*>(smem_raw);           // [16][ST]
@@ -317,7 +319,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
         }
         return;
     }
-    const int* table = block_table + (size_t)b * table_width;
+    const ZaiTableRow table{block_table + (size_t)b * table_width, table_width, num_pages, status};
     const size_t page_stride = (size_t)2 * Hkv * page_size * D;
     const size_t k_off = (size_t)hk * page_size * D, v_off = ((size_t)Hkv + hk) * page_size * D;
     const int tile0 = lo / TILE, tile1 = (hi + TILE - 1) / TILE;
@@ -502,6 +504,8 @@ struct FusedDecodeArgs {
     const int* positions;
     float eps, scale_log2;
     int qkv_cols, rot, table_width, page_size, Hq, Hkv, window, write_kv;
+    int num_pages;             // pages in `pages`: a table entry outside is read as page 0 and raises the status word
+    int* status;
     int chunk_keys;            // keys per block: a multiple of 64
 };
 
@@ -529,7 +533,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_fused_kernel(const FusedDecod
     const int kend = a.write_kv ? pos : pos + 1;                    // keys read from the pages
     const int lo = max(chunk * a.chunk_keys, kstart), hi = min((chunk + 1) * a.chunk_keys, kend);
     const bool any_paged = lo < hi;
-    const int* table = a.block_table + (size_t)b * a.table_width;
+    const ZaiTableRow table{a.block_table + (size_t)b * a.table_width, a.table_width, a.num_pages, a.status};
     const size_t page_stride = (size_t)2 * Hkv * page_size * D;
     const size_t k_off = (size_t)hk * page_size * D, v_off = ((size_t)Hkv + hk) * page_size * D;
     const int tile0 = lo / TILE, tile1 = any_paged ? (hi + TILE - 1) / TILE : tile0;
@@ -559,8 +563,8 @@ __global__ void __launch_bounds__(NTHREADS) decode_fused_kernel(const FusedDecod
             norm_rotate_row<D>(row + (size_t)(Hq + hk) * D, a.k_gamma, a.eps, cs, a.rot, tmp, knew, lane);
             const bf16* vraw = row + (size_t)(Hq + Hkv + hk) * D;
             int page, off;
-            if (page_shift >= 0) { page = table[pos >> page_shift]; off = pos & (page_size - 1); }
-            else { page = table[pos / page_size]; off = pos % page_size; }
+            if (page_shift >= 0) { page = table.page(pos >> page_shift); off = pos & (page_size - 1); }
+            else { page = table.page(pos / page_size); off = pos % page_size; }
             bf16* kdst = a.pages + (size_t)page * page_stride + k_off + (size_t)off * D;
             bf16* vdst = a.pages + (size_t)page * page_stride + v_off + (size_t)off * D;
             for (int d = lane; d < D; d += 32) {
@@ -765,7 +769,7 @@ template <int D> size_t decode_smem() {
 template <int D>
 static int launch_prefill(bf16* out, const bf16* q, const bf16* pages, const int* block_table, int table_width,
                           const int* cu_q, const int* ctx_lens, int S, int n_tiles, int page_size, int Hq, int Hkv,
-                          float scale, int window, cudaStream_t stream) {
+                          float scale, int window, int num_pages, int* status, cudaStream_t stream) {
     const size_t smem = prefill_smem<D>();
     static bool configured = false;
     if (!configured) {
@@ -775,13 +779,14 @@ static int launch_prefill(bf16* out, const bf16* q, const bf16* pages, const int
     }
     return launch_pdl(prefill_mma_kernel<D>, dim3(n_tiles, Hq), dim3(PREFILL_WARPS * 32), smem, stream,
                       out, q, pages, block_table, table_width, cu_q, ctx_lens, S, page_size, Hq, Hkv,
-                      scale * 1.4426950408889634f, window);
+                      scale * 1.4426950408889634f, window, num_pages, status);
 }
 
 template <int D>
 static int launch_decode(bf16* out, float* part_o, float* part_ml, const bf16* q, const bf16* pages,
                          const int* block_table, int table_width, const int* positions, int B, int n_chunks,
-                         int page_size, int Hq, int Hkv, float scale, int window, cudaStream_t stream) {
+                         int page_size, int Hq, int Hkv, float scale, int window, int num_pages, int* status,
+                         cudaStream_t stream) {
     const size_t smem = decode_smem<D>();
     static bool configured = false;
     if (!configured) {
@@ -791,7 +796,7 @@ static int launch_decode(bf16* out, float* part_o, float* part_ml, const bf16* q
     }
     int e = launch_pdl(decode_mma_kernel<D>, dim3(n_chunks, Hkv, B), dim3(NTHREADS), smem, stream,
                        part_o, part_ml, q, pages, block_table, table_width, positions, page_size, Hq, Hkv,
-                       scale * 1.4426950408889634f, window);
+                       scale * 1.4426950408889634f, window, num_pages, status);
     if (e) return e;
     return launch_pdl(decode_combine_kernel<D>, dim3(B * Hq), dim3(D <= 64 ? 64 : 128), 0, stream,
                       out, (const float*)part_o, (const float*)part_ml, n_chunks);
@@ -811,11 +816,11 @@ ZAI_API int zai_attention_mma_supports(int D, int Hq, int Hkv) {
 ZAI_API int zai_prefill_attention_mma(void* out, const void* q, const void* pages, const int* block_table,
                                       int table_width, const int* cu_q, const int* ctx_lens, int S, int n_tiles,
                                       int page_size, int Hq, int Hkv, int D, float scale, int window,
-                                      cudaStream_t stream) {
+                                      int num_pages, int* status, cudaStream_t stream) {
     if (S <= 0 || n_tiles <= 0) return ZAI_OK;
     if (Hq > 65535) return ZAI_BAD_SIZE;
 #define X(d) if (D == d) return launch_prefill<d>((bf16*)out, (const bf16*)q, (const bf16*)pages, block_table, table_width, \
-                                                  cu_q, ctx_lens, S, n_tiles, page_size, Hq, Hkv, scale, window, stream);
+                                                  cu_q, ctx_lens, S, n_tiles, page_size, Hq, Hkv, scale, window, num_pages, status, stream);
     ZAI_HEAD_DIMS(X)
 #undef X
     return ZAI_BAD_SIZE;
@@ -826,11 +831,11 @@ ZAI_API int zai_prefill_attention_mma(void* out, const void* q, const void* page
 ZAI_API int zai_decode_attention_mma(void* out, float* part_o, float* part_ml, const void* q, const void* pages,
                                      const int* block_table, int table_width, const int* positions, int B,
                                      int n_chunks, int page_size, int Hq, int Hkv, int D, float scale, int window,
-                                     cudaStream_t stream) {
+                                     int num_pages, int* status, cudaStream_t stream) {
     if (B <= 0) return ZAI_OK;
-    if (n_chunks < 1 || Hkv > 65535 || B > 65535 || Hq % Hkv != 0 || Hq / Hkv > 16) return ZAI_BAD_SIZE;
+    if (n_chunks < 1 || Hkv < 1 || Hkv > 65535 || B > 65535 || Hq % Hkv != 0 || Hq / Hkv > 16) return ZAI_BAD_SIZE;
 #define X(d) if (D == d) return launch_decode<d>((bf16*)out, part_o, part_ml, (const bf16*)q, (const bf16*)pages, block_table, \
-                                                 table_width, positions, B, n_chunks, page_size, Hq, Hkv, scale, window, stream);
+                                                 table_width, positions, B, n_chunks, page_size, Hq, Hkv, scale, window, num_pages, status, stream);
     ZAI_HEAD_DIMS(X)
 #undef X
     return ZAI_BAD_SIZE;
@@ -843,16 +848,17 @@ ZAI_API int zai_decode_attention_fused(void* out, float* part_o, float* part_ml,
                                        const float2* cs_table, int rot, void* pages, const int* block_table,
                                        int table_width, const int* positions, int B, int n_chunks, int page_size,
                                        int Hq, int Hkv, int D, float scale, int window, int write_kv, int chunk_keys,
-                                       cudaStream_t stream) {
+                                       int num_pages, int* status, cudaStream_t stream) {
     if (B <= 0) return ZAI_OK;
     if (chunk_keys < TILE || chunk_keys % TILE) return ZAI_BAD_SIZE;
-    if (n_chunks < 1 || Hkv > 65535 || B > 65535 || Hq % Hkv != 0 || Hq / Hkv > 16 || rot < 0 || rot > D || (rot & 1))
+    if (n_chunks < 1 || Hkv < 1 || Hkv > 65535 || B > 65535 || Hq % Hkv != 0 || Hq / Hkv > 16 || rot < 0 || rot > D || (rot & 1))
         return ZAI_BAD_SIZE;
     FusedDecodeArgs a;
     a.out = (bf16*)out; a.part_o = part_o; a.part_ml = part_ml; a.tickets = tickets; a.qkv = (const bf16*)qkv;
     a.q_gamma = q_gamma; a.k_gamma = k_gamma; a.cs_table = cs_table; a.pages = (bf16*)pages; a.block_table = block_table;
     a.positions = positions; a.eps = eps; a.scale_log2 = scale * 1.4426950408889634f; a.qkv_cols = qkv_cols; a.rot = rot;
     a.table_width = table_width; a.page_size = page_size; a.Hq = Hq; a.Hkv = Hkv; a.window = window; a.write_kv = write_kv; a.chunk_keys = chunk_keys;
+    a.num_pages = num_pages; a.status = status;
 #define X(d) if (D == d) return launch_decode_fused<d>(a, B, n_chunks, stream);
     ZAI_HEAD_DIMS(X)
 #undef X
@@ -893,7 +899,7 @@ ZAI_API int zai_decode_attention_static(void* out, const void* q, const void* pa
                                         int table_width, const int* positions, int B, int n_chunks, int page_size,
                                         int Hq, int Hkv, int D, float scale, int window, cudaStream_t stream) {
     if (B <= 0) return ZAI_OK;
-    if (n_chunks < 1 || Hq < 1 || D < 1) return ZAI_BAD_SIZE;
+    if (n_chunks < 1 || Hq < 1 || Hkv < 1 || D < 1) return ZAI_BAD_SIZE;
     const unsigned long long rows = (unsigned long long)B * Hq * n_chunks;
     if (rows * (unsigned long long)(D + 2) > (unsigned long long)ZAI_STATIC_SCRATCH_FLOATS) return ZAI_SCRATCH_TOO_SMALL;
     float* scratch = nullptr;
@@ -901,8 +907,9 @@ ZAI_API int zai_decode_attention_static(void* out, const void* q, const void* pa
     if (e != ZAI_OK) return e;
     float* part_o = scratch;                              // [B, Hq, n_chunks, D]
     float* part_ml = scratch + rows * D;                  // [B, Hq, n_chunks, 2]
+    // (this entry point's caller vouches for its block tables: no bound on the page ids, no status word)
     return zai_decode_attention_mma(out, part_o, part_ml, q, pages, block_table, table_width, positions, B, n_chunks,
-                                    page_size, Hq, Hkv, D, scale, window, stream);
+                                    page_size, Hq, Hkv, D, scale, window, 0x7fffffff, nullptr, stream);
 }
 
 ZAI_API const char* zai_decode_attention_static_error(int code) {

@@ -3,7 +3,7 @@
 // Same result as prefill_mma_kernel (csrc/attention_mma.cu): causal attention of a step's query rows
 // over their requests' pages (cached positions and the step's own), optionally with a window, by
 // the online-softmax recurrence over tiles of keys (the reference computes the same sums with one
-// thread block per query row, src/cuda/attention_kernels.cu).  What differs is where the products
+// thread block per query row and head, src/cuda/paged_attention.cu:230-337).  What differs is where the products
 // run: a block owns 128 query rows of one head; per tile of 128 keys
 //
 //     S = Q K^T      tcgen05.mma, M = 128 (query rows = TMEM lanes), N = 128 keys, K = 64, into TMEM
@@ -115,7 +115,8 @@ struct AtArgs {
     const int* block_table;     // [S, table_width]
     const int* cu_q;            // [S + 1] first row of each request's span
     const int* ctx_lens;        // [S] positions cached before the step
-    int* status;                // raised to 1 by a block whose wait ran out
+    int* status;                // the step's status word: a wait that ran out, a page id outside the pool
+    int num_pages;
     int table_width, S, page_size, page_shift, Hq, Hkv, window;
     float scale_log2;
 };
@@ -206,7 +207,11 @@ __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_con
                     for (int p = 0; p < per_tile; ++p) {
                         const int key0 = (tile0 + i) * AT_BN + p * box_rows;
                         const int idx = key0 >> a.page_shift, off = key0 & (ps - 1);
-                        const int page = idx < a.table_width ? table[idx] : 0;        // beyond the table: the null page
+                        int page = idx < a.table_width ? table[idx] : 0;              // beyond the table: the null page
+                        if ((unsigned)page >= (unsigned)a.num_pages) {                // outside the pool: page 0, and the step is void
+                            zai_raise(a.status, ZAI_ST_PAGE);
+                            page = 0;
+                        }
                         const int krow = ((page * 2 + 0) * a.Hkv + hk) * ps + off;
                         const int vrow = ((page * 2 + 1) * a.Hkv + hk) * ps + off;
                         at_tma_load_2d(dst + (size_t)p * box_rows * 128, &map_kv, 0, krow, &kv_full[st]);
@@ -409,7 +414,7 @@ __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_con
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(AT_TMEM_COLS) : "memory");
     }
-    if (tid == 0 && failed_flag) atomicExch(a.status, 1);
+    if (tid == 0 && failed_flag) zai_raise(a.status, ZAI_ST_WAIT);
 }
 
 // ------------------------------------------------------------------------------------------ host side
@@ -461,7 +466,7 @@ ZAI_API int zai_prefill_attention_tc(void* out, const void* q, const void* pages
     e = at_make_map(&mkv, pages, AT_D, (cuuint64_t)num_pages * 2 * Hkv * page_size, (cuuint32_t)(page_size < AT_BN ? page_size : AT_BN));
     if (e) return e;
     AtArgs a;
-    a.out = (bf16*)out; a.block_table = block_table; a.cu_q = cu_q; a.ctx_lens = ctx_lens; a.status = status;
+    a.out = (bf16*)out; a.block_table = block_table; a.cu_q = cu_q; a.ctx_lens = ctx_lens; a.status = status; a.num_pages = num_pages;
     a.table_width = table_width; a.S = S; a.page_size = page_size; a.Hq = Hq; a.Hkv = Hkv; a.window = window;
     a.scale_log2 = scale * 1.4426950408889634f;
     a.page_shift = 0;

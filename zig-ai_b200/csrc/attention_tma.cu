@@ -85,7 +85,8 @@ struct TmaDecodeArgs {
     float* part_o;             // [B, Hq, n_chunks, 64]
     float* part_ml;            // [B, Hq, n_chunks, 2]
     int* tickets;              // [B * Hkv], zero before and after
-    int* status;               // raised to 1 by a block whose wait ran out
+    int* status;               // the step's status word: a wait that ran out, a page id or position out of bounds
+    int num_pages;
     const bf16* qkv;           // [B, qkv_cols]
     const float* q_gamma;
     const float* k_gamma;
@@ -179,7 +180,11 @@ __global__ void __maxnreg__(128) decode_tma_kernel(const __grid_constant__ CUten
                     const int p = lane >> 1, kv = lane & 1;
                     unsigned char* st = ring + (size_t)s * TT_STAGE_BYTES;
                     const int idx = ((t * TT_TILE) >> a.page_shift) + p;
-                    const int page = idx < a.table_width ? table[idx] : 0;         // beyond the table: the null page
+                    int page = idx < a.table_width ? table[idx] : 0;               // beyond the table: the null page
+                    if ((unsigned)page >= (unsigned)a.num_pages) {                 // outside the pool: page 0, and the step is void
+                        zai_raise(a.status, ZAI_ST_PAGE);
+                        page = 0;
+                    }
                     const int row = ((page * 2 + kv) * Hkv + hk) * ps;
                     tt_tma_load_2d(st + (size_t)kv * TT_TILE * 128 + (size_t)p * ps * 128, &map, 0, row, &full_bar[s]);
                 }
@@ -209,7 +214,9 @@ __global__ void __maxnreg__(128) decode_tma_kernel(const __grid_constant__ CUten
             if (has_new && cw == G % TT_CONSUMERS) {
                 norm_rotate_row<D>(row + (size_t)(Hq + hk) * D, a.k_gamma, a.eps, cs, a.rot, tmp + cw * D, knew, lane);
                 const bf16* vraw = row + (size_t)(Hq + Hkv + hk) * D;
-                const int page = table[pos >> a.page_shift], off = pos & (ps - 1);
+                const int page = zai_checked_page(table, a.table_width, pos < 0 ? -1 : pos >> a.page_shift, a.num_pages,
+                                                  lane == 0 ? a.status : nullptr);
+                const int off = pos & (ps - 1);
                 const size_t page_stride = (size_t)2 * Hkv * ps * D;
                 bf16* kdst = a.pages + (size_t)page * page_stride + ((size_t)hk * ps + off) * D;
                 bf16* vdst = a.pages + (size_t)page * page_stride + ((size_t)(Hkv + hk) * ps + off) * D;
@@ -365,7 +372,7 @@ __global__ void __maxnreg__(128) decode_tma_kernel(const __grid_constant__ CUten
         ml[0] = -INFINITY;
         ml[1] = 0.f;
     }
-    if (tid == 0 && failed_flag) atomicExch(a.status, 1);
+    if (tid == 0 && failed_flag) zai_raise(a.status, ZAI_ST_WAIT);
 
     // ---- the last block of this (request, key/value head) combines the chunks
     __threadfence();
@@ -451,7 +458,7 @@ ZAI_API int zai_decode_attention_tma(void* out, float* part_o, float* part_ml, i
                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return -6;
     TmaDecodeArgs a;
-    a.out = (bf16*)out; a.part_o = part_o; a.part_ml = part_ml; a.tickets = tickets; a.status = status; a.qkv = (const bf16*)qkv;
+    a.out = (bf16*)out; a.part_o = part_o; a.part_ml = part_ml; a.tickets = tickets; a.status = status; a.num_pages = num_pages; a.qkv = (const bf16*)qkv;
     a.q_gamma = q_gamma; a.k_gamma = k_gamma; a.cs_table = cs_table; a.pages = (bf16*)pages; a.block_table = block_table;
     a.positions = positions; a.eps = eps; a.scale_log2 = scale * 1.4426950408889634f; a.qkv_cols = qkv_cols; a.rot = rot;
     a.table_width = table_width; a.page_size = page_size; a.Hq = Hq; a.Hkv = Hkv; a.window = window; a.write_kv = write_kv;

@@ -48,6 +48,49 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 
 static inline int launch_status() { return (int)cudaGetLastError(); }
 
+// ---- the status word of a step: one device int that kernels OR bits into and the host reads with the
+// step's results.  A kernel never traps and never touches memory outside the tensors it was given: an
+// id outside its bound is replaced by id 0 (page 0 and slot 0 are never handed to a request, padding
+// rows use them), the bit is raised and the step's results are to be thrown away by the host.
+enum ZaiStatusBit {
+    ZAI_ST_WAIT = 1,        // a bounded wait (mbarrier, ticket) ran out
+    ZAI_ST_TOKEN = 2,       // a token id outside the vocabulary
+    ZAI_ST_PAGE = 4,        // a block-table entry outside the pool
+    ZAI_ST_SLOT = 8,        // a state slot outside the slots
+    ZAI_ST_POSITION = 16    // a position outside the request's block-table row
+};
+__device__ __forceinline__ void zai_raise(int* status, int bit) {
+    if (status) atomicOr(status, bit);
+}
+// The page that holds logical page `idx` of a request whose block-table row is `table_row`.
+__device__ __forceinline__ int zai_checked_page(const int* __restrict__ table_row, int table_width, int idx,
+                                                int num_pages, int* status) {
+    if ((unsigned)idx >= (unsigned)table_width) {
+        zai_raise(status, ZAI_ST_POSITION);
+        return 0;
+    }
+    const int page = table_row[idx];
+    if ((unsigned)page >= (unsigned)num_pages) {
+        zai_raise(status, ZAI_ST_PAGE);
+        return 0;
+    }
+    return page;
+}
+// A request's row of a block table with its bounds: page(idx) is the checked lookup above.
+struct ZaiTableRow {
+    const int* row;
+    int width, num_pages;
+    int* status;
+    __device__ __forceinline__ int page(int idx) const { return zai_checked_page(row, width, idx, num_pages, status); }
+};
+__device__ __forceinline__ int zai_checked_slot(int slot, int num_slots, int* status) {
+    if ((unsigned)slot >= (unsigned)num_slots) {
+        zai_raise(status, ZAI_ST_SLOT);
+        return 0;
+    }
+    return slot;
+}
+
 // ---- programmatic dependent launch: a kernel launched this way may start while the kernel before
 // it on the stream still runs.  It must call pdl_wait() before it reads anything an earlier kernel
 // wrote and before it writes anything an earlier kernel may still read (so: before its first global

@@ -51,6 +51,8 @@ struct SkinnyArgs {
     const float* conv_b;  // [F] or null
     float* conv_state;    // [slots, state_rows, F]
     const int* slot_ids;  // [M]
+    int num_slots;        // slots in conv_state: a slot id outside is read as slot 0 and raises the status word
+    int* status;
     int taps, state_rows, write_state;
     int l2_prefetch_bytes; // how much of its weight rows a block asks into L2 before it waits for the kernel before it
 };
@@ -223,7 +225,7 @@ __global__ void __launch_bounds__(SG_WARPS * 32, 2) skinny_gemm_kernel(const Ski
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int tok = nt * 8 + 2 * t + e;
-                cv_slot[nt][e] = tok < a.M ? a.slot_ids[tok] : 0;
+                cv_slot[nt][e] = tok < a.M ? zai_checked_slot(a.slot_ids[tok], a.num_slots, a.status) : 0;
 #pragma unroll
                 for (int j = 0; j < SG_CONV_TAPS - 1; ++j)
                     cv_prev[nt][e][j] = (vc && tok < a.M && j < a.taps - 1)
@@ -814,7 +816,7 @@ ZAI_API int zai_skinny_gemm(void* y, const void* W, const void* x, const float* 
 ZAI_API int zai_skinny_conv(void* z, const void* W, const void* x, const float* h, const void* delta, const float* gamma,
                             float* h_out, float eps, const float* conv_w, const float* conv_b, float* state,
                             const int* slot_ids, int M, int F, int K, int taps, int state_rows, int write_state,
-                            cudaStream_t stream) {
+                            int num_slots, int* status, cudaStream_t stream) {
     if (F < 1 || taps < 1 || taps > SG_CONV_TAPS || state_rows < taps - 1) return ZAI_BAD_SIZE;
     if (!zai_skinny_gemm_supports(M, 3 * F, K, EPI_CONV, h != nullptr)) return ZAI_BAD_SIZE;
     SkinnyArgs a = {};
@@ -823,6 +825,7 @@ ZAI_API int zai_skinny_conv(void* z, const void* W, const void* x, const float* 
     a.F = F;
     a.ldy = F;
     a.conv_w = conv_w; a.conv_b = conv_b; a.conv_state = state; a.slot_ids = slot_ids;
+    a.num_slots = num_slots; a.status = status;
     a.taps = taps; a.state_rows = state_rows; a.write_state = write_state;
     skinny_plan(F, false, K, &a.n_tiles, &a.half_tiles, &a.tpc, &a.sk, &a.units, 8);   // 8 channels per tile
     return skinny_run(a, EPI_CONV, stream);

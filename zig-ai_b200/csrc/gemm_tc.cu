@@ -247,7 +247,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
-    if (threadIdx.x == 0 && failed_flag) atomicExch(a.status, 1);
+    if (threadIdx.x == 0 && failed_flag) zai_raise(a.status, ZAI_ST_WAIT);
 }
 
 // ------------------------------------------------------------------------------------------ host side

@@ -321,7 +321,7 @@ __global__ void __launch_bounds__(TP_THREADS) gemm_pair_kernel(const __grid_cons
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
-    if (threadIdx.x == 0 && failed_flag) atomicExch(a.status, 1);
+    if (threadIdx.x == 0 && failed_flag) zai_raise(a.status, ZAI_ST_WAIT);
 }
 
 // ------------------------------------------------------------------------------------------ host side

@@ -34,7 +34,7 @@ __global__ void qk_norm_rope_kernel(const T* __restrict__ qkv, int qkv_cols, con
                                     int rot, const int* __restrict__ positions, const int* __restrict__ seq_idx,
                                     const int* __restrict__ block_table, int table_width, T* __restrict__ pages,
                                     int page_size, T* __restrict__ q_out, T* __restrict__ k_out, int Hq, int Hkv,
-                                    int D, int has_kv, int write) {
+                                    int D, int has_kv, int write, int num_pages, int* __restrict__ status) {
     extern __shared__ float smem[];
     const int half = rot / 2;
     float* cs = smem;                       // [half] cos
@@ -54,8 +54,9 @@ __global__ void qk_norm_rope_kernel(const T* __restrict__ qkv, int qkv_cols, con
     size_t page_base = 0;
     int off = 0;
     if (has_kv && write) {
-        const int page = block_table[(size_t)seq_idx[t] * table_width + pos / page_size];
-        off = pos % page_size;
+        const int page = zai_checked_page(block_table + (size_t)seq_idx[t] * table_width, table_width,
+                                          pos < 0 ? -1 : pos / page_size, num_pages, status);
+        off = pos < 0 ? 0 : pos % page_size;
         page_base = (size_t)page * 2 * Hkv * page_size * D;
     }
     const int n_heads = Hq + (has_kv ? 2 * Hkv : 0);
@@ -112,7 +113,8 @@ __global__ void __launch_bounds__(256) qk_norm_rope_vec_kernel(
     const bf16* __restrict__ qkv, int qkv_cols, const float* __restrict__ q_gamma, const float* __restrict__ k_gamma,
     float eps, const float2* __restrict__ cs_table, const int* __restrict__ positions, const int* __restrict__ seq_idx,
     const int* __restrict__ block_table, int table_width, bf16* __restrict__ pages, int page_size,
-    bf16* __restrict__ q_out, bf16* __restrict__ k_out, int N, int Hq, int Hkv, int has_kv, int write) {
+    bf16* __restrict__ q_out, bf16* __restrict__ k_out, int N, int Hq, int Hkv, int has_kv, int write, int num_pages,
+    int* __restrict__ status) {
     constexpr int D = 8 * TPH, half = 4 * TPH;
     pdl_trigger();
     pdl_wait();
@@ -127,8 +129,9 @@ __global__ void __launch_bounds__(256) qk_norm_rope_vec_kernel(
     int off = 0;
     if (!is_q && write) {
         const int pos = positions[t];
-        const int page = block_table[(size_t)seq_idx[t] * table_width + pos / page_size];
-        off = pos % page_size;
+        const int page = zai_checked_page(block_table + (size_t)seq_idx[t] * table_width, table_width,
+                                          pos < 0 ? -1 : pos / page_size, num_pages, status);
+        off = pos < 0 ? 0 : pos % page_size;
         page_base = (size_t)page * 2 * Hkv * page_size * D;
     }
     if (is_v) {
@@ -206,13 +209,13 @@ template <int TPH>
 static int launch_qk_vec(const void* qkv, int qkv_cols, const float* q_gamma, const float* k_gamma, float eps,
                          const float2* cs_table, const int* positions, const int* seq_idx, const int* block_table,
                          int table_width, void* pages, int page_size, void* q_out, void* k_out, int N, int Hq, int Hkv,
-                         int has_kv, int write, cudaStream_t stream) {
+                         int has_kv, int write, int num_pages, int* status, cudaStream_t stream) {
     const long long items = (long long)N * (Hq + (has_kv ? 2 * Hkv : 0));
     const long long blocks = (items + 256 / TPH - 1) / (256 / TPH);
     if (blocks > 0x7fffffffLL) return ZAI_BAD_SIZE;
     return launch_pdl(qk_norm_rope_vec_kernel<TPH>, dim3((unsigned)blocks), dim3(256), 0, stream, (const bf16*)qkv, qkv_cols,
                       q_gamma, k_gamma, eps, cs_table, positions, seq_idx, block_table, table_width, (bf16*)pages, page_size,
-                      (bf16*)q_out, (bf16*)k_out, N, Hq, Hkv, has_kv, write);
+                      (bf16*)q_out, (bf16*)k_out, N, Hq, Hkv, has_kv, write, num_pages, status);
 }
 
 // Writes already prepared k and v rows ([N, Hkv*D], row strides given) into the pages.
@@ -220,13 +223,14 @@ template <typename T>
 __global__ void kv_write_kernel(const T* __restrict__ k, int k_stride, const T* __restrict__ v, int v_stride,
                                 const int* __restrict__ positions, const int* __restrict__ seq_idx,
                                 const int* __restrict__ block_table, int table_width, T* __restrict__ pages,
-                                int page_size, int Hkv, int D) {
+                                int page_size, int Hkv, int D, int num_pages, int* __restrict__ status) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
     const int pos = positions[t];
-    const int page = block_table[(size_t)seq_idx[t] * table_width + pos / page_size];
-    const int off = pos % page_size;
+    const int page = zai_checked_page(block_table + (size_t)seq_idx[t] * table_width, table_width,
+                                      pos < 0 ? -1 : pos / page_size, num_pages, threadIdx.x == 0 ? status : nullptr);
+    const int off = pos < 0 ? 0 : pos % page_size;
     const size_t base = (size_t)page * 2 * Hkv * page_size * D;
     for (int i = threadIdx.x; i < Hkv * D; i += blockDim.x) {
         const int h = i / D, d = i % D;
@@ -245,8 +249,8 @@ ZAI_API int zai_rope_table(float2* table, const int* positions, const double* in
 ZAI_API int zai_qk_norm_rope(const void* qkv, int qkv_cols, int dtype, const float* q_gamma, const float* k_gamma,
                              float eps, const float2* cs_table, int rot, const int* positions, const int* seq_idx,
                              const int* block_table, int table_width, void* pages, int page_size, void* q_out,
-                             void* k_out, int N, int Hq, int Hkv, int D, int has_kv, int write,
-                             cudaStream_t stream) {
+                             void* k_out, int N, int Hq, int Hkv, int D, int has_kv, int write, int num_pages,
+                             int* status, cudaStream_t stream) {
     if (N <= 0) return ZAI_OK;
     if (rot < 0 || rot > D || (rot & 1) || D < 1) return ZAI_BAD_SIZE;
     // the vector kernel: bfloat16, the whole head rotated, 16-byte aligned rows and tables
@@ -255,7 +259,7 @@ ZAI_API int zai_qk_norm_rope(const void* qkv, int qkv_cols, int dtype, const flo
                           reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_out);
     if (dtype == ZAI_BF16 && rot == D && (D & 7) == 0 && (qkv_cols & 7) == 0 && (all & 15) == 0) {
 #define ZAI_QK_VEC(tph) if (D == 8 * tph) return launch_qk_vec<tph>(qkv, qkv_cols, q_gamma, k_gamma, eps, cs_table, positions, \
-        seq_idx, block_table, table_width, pages, page_size, q_out, k_out, N, Hq, Hkv, has_kv, write, stream);
+        seq_idx, block_table, table_width, pages, page_size, q_out, k_out, N, Hq, Hkv, has_kv, write, num_pages, status, stream);
         ZAI_QK_VEC(2) ZAI_QK_VEC(4) ZAI_QK_VEC(8) ZAI_QK_VEC(16) ZAI_QK_VEC(32)
 #undef ZAI_QK_VEC
     }
@@ -264,14 +268,14 @@ ZAI_API int zai_qk_norm_rope(const void* qkv, int qkv_cols, int dtype, const flo
     if (smem > 48 * 1024) return ZAI_BAD_SIZE;
     ZAI_DISPATCH(dtype, return launch_pdl(qk_norm_rope_kernel<T>, dim3(N), dim3(threads), smem, stream,
         (const T*)qkv, qkv_cols, q_gamma, k_gamma, eps, cs_table, rot, positions, seq_idx, block_table,
-        table_width, (T*)pages, page_size, (T*)q_out, (T*)k_out, Hq, Hkv, D, has_kv, write));
+        table_width, (T*)pages, page_size, (T*)q_out, (T*)k_out, Hq, Hkv, D, has_kv, write, num_pages, status));
 }
 
 ZAI_API int zai_kv_write(const void* k, int k_stride, const void* v, int v_stride, int dtype, const int* positions,
                          const int* seq_idx, const int* block_table, int table_width, void* pages, int page_size,
-                         int N, int Hkv, int D, cudaStream_t stream) {
+                         int N, int Hkv, int D, int num_pages, int* status, cudaStream_t stream) {
     if (N <= 0) return ZAI_OK;
     ZAI_DISPATCH(dtype, return launch_pdl(kv_write_kernel<T>, dim3(N), dim3(128), 0, stream,
         (const T*)k, k_stride, (const T*)v, v_stride, positions, seq_idx, block_table, table_width, (T*)pages,
-        page_size, Hkv, D));
+        page_size, Hkv, D, num_pages, status));
 }

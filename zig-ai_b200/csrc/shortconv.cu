@@ -21,7 +21,7 @@ template <typename T>
 __global__ void conv_rows_kernel(T* __restrict__ z, const T* __restrict__ bcx, const float* __restrict__ w,
                                  const float* __restrict__ bias, const float* __restrict__ state,
                                  const int* __restrict__ seq_idx, const int* __restrict__ cu_q,
-                                 const int* __restrict__ slot_ids, int C, int L, int state_rows) {
+                                 const int* __restrict__ slot_ids, int C, int L, int state_rows, int num_slots, int* __restrict__ status) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
@@ -29,7 +29,7 @@ __global__ void conv_rows_kernel(T* __restrict__ z, const T* __restrict__ bcx, c
     if (c >= C) return;
     const int s = seq_idx[t];
     const int i = t - cu_q[s];
-    const float* st = state + ((size_t)slot_ids[s] * state_rows) * C;
+    const float* st = state + ((size_t)zai_checked_slot(slot_ids[s], num_slots, status) * state_rows) * C;
     float y = bias ? bias[c] : 0.f;
     for (int j = 0; j < L; ++j) {
         const int r = i + j - (L - 1);                    // row of the span, negative: from the state
@@ -50,7 +50,7 @@ __global__ void conv_rows_kernel(T* __restrict__ z, const T* __restrict__ bcx, c
 __global__ void conv_rows_bf16x8_kernel(bf16* __restrict__ z, const bf16* __restrict__ bcx, const float* __restrict__ w,
                                         const float* __restrict__ bias, const float* __restrict__ state,
                                         const int* __restrict__ seq_idx, const int* __restrict__ cu_q,
-                                        const int* __restrict__ slot_ids, int C, int L, int state_rows) {
+                                        const int* __restrict__ slot_ids, int C, int L, int state_rows, int num_slots, int* __restrict__ status) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
@@ -58,7 +58,7 @@ __global__ void conv_rows_bf16x8_kernel(bf16* __restrict__ z, const bf16* __rest
     if (c >= C) return;
     const int s = seq_idx[t];
     const int i = t - cu_q[s];
-    const float* st = state + ((size_t)slot_ids[s] * state_rows) * C;
+    const float* st = state + ((size_t)zai_checked_slot(slot_ids[s], num_slots, status) * state_rows) * C;
     float y[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) y[e] = bias ? bias[c + e] : 0.f;
@@ -107,7 +107,7 @@ template <int L>
 __global__ void __launch_bounds__(128) conv_rows_bf16x8_walk_kernel(
     bf16* __restrict__ z, const bf16* __restrict__ bcx, const float* __restrict__ w, const float* __restrict__ bias,
     const float* __restrict__ state, const int* __restrict__ seq_idx, const int* __restrict__ cu_q,
-    const int* __restrict__ slot_ids, int N, int C, int state_rows) {
+    const int* __restrict__ slot_ids, int N, int C, int state_rows, int num_slots, int* __restrict__ status) {
     pdl_trigger();
     pdl_wait();
     const int t0 = blockIdx.x * CONV_R;
@@ -149,7 +149,7 @@ __global__ void __launch_bounds__(128) conv_rows_bf16x8_walk_kernel(
         const int t = t0 + r, s = sq[r];
         const int i = t - cu_q[s];                                // the row's place in its span
         if (L > 1 && (s != prev_seq || i == 0)) {                // (re)build the history: earlier rows, or the state
-            const float* st = state + ((size_t)slot_ids[s] * state_rows) * C;
+            const float* st = state + ((size_t)zai_checked_slot(slot_ids[s], num_slots, status) * state_rows) * C;
 #pragma unroll
             for (int j = 0; j < L - 1; ++j) {
                 const int rr = i + j - (L - 1);
@@ -215,14 +215,14 @@ __global__ void __launch_bounds__(128) conv_rows_bf16x8_walk_kernel(
 template <typename T>
 __global__ void conv_state_kernel(const T* __restrict__ bcx, float* __restrict__ state,
                                   const int* __restrict__ cu_q, const int* __restrict__ slot_ids,
-                                  int C, int L, int state_rows) {
+                                  int C, int L, int state_rows, int num_slots, int* __restrict__ status) {
     pdl_trigger();
     pdl_wait();
     const int s = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= C) return;
     const int a = cu_q[s], n = cu_q[s + 1] - a;
-    float* st = state + ((size_t)slot_ids[s] * state_rows) * C;
+    float* st = state + ((size_t)zai_checked_slot(slot_ids[s], num_slots, status) * state_rows) * C;
     float keep[ZAI_MAX_TAPS];
 #pragma unroll
     for (int r = 0; r < ZAI_MAX_TAPS; ++r) {
@@ -245,13 +245,13 @@ __global__ void conv_state_kernel(const T* __restrict__ bcx, float* __restrict__
 template <typename T>
 __global__ void conv_decode_kernel(T* __restrict__ z, const T* __restrict__ bcx, const float* __restrict__ w,
                                    const float* __restrict__ bias, float* __restrict__ state,
-                                   const int* __restrict__ slot_ids, int C, int L, int state_rows, int write_state) {
+                                   const int* __restrict__ slot_ids, int C, int L, int state_rows, int write_state, int num_slots, int* __restrict__ status) {
     pdl_trigger();
     pdl_wait();
     const int s = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= C) return;
-    float* st = state + ((size_t)slot_ids[s] * state_rows) * C;
+    float* st = state + ((size_t)zai_checked_slot(slot_ids[s], num_slots, status) * state_rows) * C;
     const T* row = bcx + (size_t)s * 3 * C;
     const float u = to_float(row[c]) * to_float(row[2 * C + c]);
     float y = bias ? bias[c] : 0.f;
@@ -273,14 +273,14 @@ __global__ void conv_decode_kernel(T* __restrict__ z, const T* __restrict__ bcx,
 
 ZAI_API int zai_short_conv(void* z, const void* bcx, int dtype, const float* w, const float* bias, float* state,
                            const int* seq_idx, const int* cu_q, const int* slot_ids, int N, int S, int C, int L,
-                           int state_rows, int decode_only, int write_state, cudaStream_t stream) {
+                           int state_rows, int decode_only, int write_state, int num_slots, int* status, cudaStream_t stream) {
     if (N <= 0) return ZAI_OK;
     if (L < 1 || L > ZAI_MAX_TAPS || state_rows < L - 1) return ZAI_BAD_SIZE;
     const int threads = 128;
     const unsigned bx = (unsigned)((C + threads - 1) / threads);
     if (decode_only) {
         ZAI_DISPATCH(dtype, return launch_pdl(conv_decode_kernel<T>, dim3(S, bx), dim3(threads), 0, stream,
-            (T*)z, (const T*)bcx, w, bias, state, slot_ids, C, L, state_rows, write_state));
+            (T*)z, (const T*)bcx, w, bias, state, slot_ids, C, L, state_rows, write_state, num_slots, status));
     }
     int e = 0;
     const bool aligned = ((reinterpret_cast<uintptr_t>(z) | reinterpret_cast<uintptr_t>(bcx) | reinterpret_cast<uintptr_t>(w) |
@@ -289,16 +289,16 @@ ZAI_API int zai_short_conv(void* z, const void* bcx, int dtype, const float* w, 
         const int c8 = C / 8, th = c8 < 128 ? ((c8 + 31) / 32) * 32 : 128;
         const dim3 walk((N + CONV_R - 1) / CONV_R, (c8 + th - 1) / th);
 #define ZAI_CONV_WALK(l) if (L == l) e = launch_pdl(conv_rows_bf16x8_walk_kernel<l>, walk, dim3(th), 0, stream, (bf16*)z, \
-        (const bf16*)bcx, w, bias, (const float*)state, seq_idx, cu_q, slot_ids, N, C, state_rows);
+        (const bf16*)bcx, w, bias, (const float*)state, seq_idx, cu_q, slot_ids, N, C, state_rows, num_slots, status);
         ZAI_CONV_WALK(1) ZAI_CONV_WALK(2) ZAI_CONV_WALK(3) ZAI_CONV_WALK(4)
 #undef ZAI_CONV_WALK
         if (L > 4)
             e = launch_pdl(conv_rows_bf16x8_kernel, dim3(N, (c8 + th - 1) / th), dim3(th), 0, stream, (bf16*)z, (const bf16*)bcx, w,
-                           bias, (const float*)state, seq_idx, cu_q, slot_ids, C, L, state_rows);
+                           bias, (const float*)state, seq_idx, cu_q, slot_ids, C, L, state_rows, num_slots, status);
     } else
     ZAI_DISPATCH(dtype, e = launch_pdl(conv_rows_kernel<T>, dim3(N, bx), dim3(threads), 0, stream,
-        (T*)z, (const T*)bcx, w, bias, (const float*)state, seq_idx, cu_q, slot_ids, C, L, state_rows));
+        (T*)z, (const T*)bcx, w, bias, (const float*)state, seq_idx, cu_q, slot_ids, C, L, state_rows, num_slots, status));
     if (e || !write_state || L == 1) return e;
     ZAI_DISPATCH(dtype, return launch_pdl(conv_state_kernel<T>, dim3(S, bx), dim3(threads), 0, stream,
-        (const T*)bcx, state, cu_q, slot_ids, C, L, state_rows));
+        (const T*)bcx, state, cu_q, slot_ids, C, L, state_rows, num_slots, status));
 }

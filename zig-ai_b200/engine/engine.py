@@ -21,7 +21,7 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from ..sampling.sampler import Sampler, SamplingParams
-from .runner import ModelRunner, load_runner
+from .runner import ModelRunner, StepError, load_runner
 from .scheduler import RUNNING, PlanEntry, Request, Scheduler, StepPlan
 
 
@@ -80,34 +80,50 @@ class Engine:
     def _launch(self, plan: StepPlan, device_tokens: Optional[torch.Tensor] = None):
         """Run the plan's step and its sampling kernel; nothing is read back."""
         entries = [(e.request.request_id, e.tokens, [len(e.tokens) - 1] if e.sample else []) for e in plan.entries]
-        logits = self.runner.step(entries, trusted=True, device_tokens=device_tokens)
+        logits = self.runner.step(entries, trusted=True, device_tokens=device_tokens, check=False)
+        number = self.runner.steps - 1
         wanting = [e.request for e in plan.entries if e.sample]
         ahead = 1 if device_tokens is not None else 0         # one token of each output is still on the device
         ids = self.sampler.sample_device(logits, [r.params for r in wanting], [len(r.output) + ahead for r in wanting],
                                          [r.output for r in wanting])
         # the copy to the host is queued now, before any later step's kernels, so that reading it
         # waits for this step only
+        # the kernels' status word rides along, behind the ids in the same pinned buffer
+        status = getattr(self.runner.ops, "status_tensor", None)
+        status = status(self.runner.device) if status else None
         if ids.device.type != "cuda":
-            return plan, wanting, ids, ids, None
+            host = torch.cat([ids.to(torch.int32), status.to(torch.int32)]) if status is not None else ids
+            if status is not None:
+                status.zero_()
+            return plan, wanting, ids, host, None, number
         if not self._host_ids:
-            self._host_ids = [torch.empty((max(self.scheduler.max_num_seqs, 1),), dtype=torch.int32).pin_memory()
+            self._host_ids = [torch.empty((max(self.scheduler.max_num_seqs, 1) + 1,), dtype=torch.int32).pin_memory()
                               for _ in range(4)]
         host = self._host_ids[self._host_turn % len(self._host_ids)]
         self._host_turn += 1
         n = int(ids.shape[0])
-        if n > host.shape[0]:
-            host = torch.empty((n,), dtype=torch.int32).pin_memory()
+        if n + 1 > host.shape[0]:
+            host = torch.empty((n + 1,), dtype=torch.int32).pin_memory()
         host[:n].copy_(ids, non_blocking=True)
+        host[n:n + 1].copy_(status, non_blocking=True)
         done = torch.cuda.Event()
         done.record()
-        return plan, wanting, ids, host, done
+        return plan, wanting, ids, host, done, number
 
     def _collect(self, launched) -> List[Request]:
         """Read a launched step's token ids and hand them to the scheduler; returns the requests that ended."""
-        plan, wanting, _ids_dev, host, done = launched
+        plan, wanting, _ids_dev, host, done, number = launched
         if done is not None:
             done.synchronize()
         ids = host[:len(wanting)].tolist()
+        code = int(host[len(wanting)]) if host.shape[0] > len(wanting) else 0
+        if code:
+            # a kernel met an id outside its bound or gave up a wait: the step's tokens are void
+            ops = self.runner.ops
+            if done is not None:
+                ops.status_tensor(self.runner.device).zero_()
+            self._inflight = None
+            raise StepError(f"step {number}: {ops.describe_status(code)} (status {code}); its results are void")
         # rows of requests that ended while this step was already on its way count for nothing
         plan.entries = [e for e in plan.entries if e.request.status == RUNNING]
         sampled = {r.request_id: t for r, t in zip(wanting, ids) if r.status == RUNNING}

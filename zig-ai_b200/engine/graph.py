@@ -125,7 +125,10 @@ class ShapeGraphs:
     SEEN_BEFORE_CAPTURE = 2
 
     def __init__(self, model, cache, ops, dtype, device, widths: Dict[int, int]):
-        self.model, self.cache, self.ops, self.dtype, self.device, self.widths = model, cache, ops, dtype, device, widths
+        self.model, self.cache, self.ops, self.dtype, self.device = model, cache, ops, dtype, device
+        # the span of the null request that fills a bucket's spare rows lies at positions 0..63 at most:
+        # every table row is wide enough for them, however few positions the pool holds
+        self.widths = {g: max(w, -(-64 // cache.page_size)) for g, w in widths.items()}
         self.seen: Dict[tuple, int] = {}
         self.graphs: Dict[tuple, tuple] = {}          # key -> (graph, host, dev, logits, launches)
         self.replays = 0

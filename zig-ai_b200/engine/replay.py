@@ -22,6 +22,8 @@ def main(argv=None) -> int:
                     help="most tokens live requests hold at any time (each rounded up to 64)")
     ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--max-requests", type=int, default=8)
+    ap.add_argument("--stats", default=None, metavar="FILE",
+                    help="when the input ends, write the cache's and the runner's counters to FILE as JSON")
     args = ap.parse_args(argv)
 
     from .runner import load_runner
@@ -51,4 +53,9 @@ def main(argv=None) -> int:
             if runner.has_request(rid):
                 runner.end_request(rid)
         print(f"done {step}", flush=True)
+    if args.stats:
+        stats = dict(runner.cache.stats(), steps=runner.steps, tokens_run=runner.tokens_run,
+                     num_pages=runner.cache.num_pages, page_size=runner.cache.page_size)
+        with open(args.stats, "w") as f:
+            json.dump(stats, f)
     return 0

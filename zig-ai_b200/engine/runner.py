@@ -23,7 +23,8 @@ from .batch import StepBatch, pack_step
 
 
 class StepError(ValueError):
-    """A step that cannot run: an unknown token id, a request that is too long, a bad entry."""
+    """A step that cannot run (an unknown token id, a request that is too long, a bad entry), or a step
+    whose kernels raised the status word: its results are void."""
 
 
 class ModelRunner:
@@ -135,35 +136,36 @@ class ModelRunner:
         return self.graphs.run_prepared(prepared)
 
     def _pad_rows(self, spans, tables):
-        """Round a step's row count up (to a multiple of 32 up to 256 rows, of 64 beyond) with a span of
-        the null request (null slot, null page, nothing wanted), so that the library's matrix products
-        see few distinct row counts: it plans every new shape once, at a millisecond each, and a
-        serving run would otherwise meet thousands of them."""
+        """Round a step's row count up (see `pad_rows`) on the device path."""
         if self.device.type != "cuda" or os.environ.get("ZAI_PAD_ROWS", "1") == "0":
             return spans, tables
-        n = sum(len(s[2]) for s in spans)
-        if n <= 16:                                            # the few-rows kernels: no library product
-            return spans, tables
-        step = 32 if n <= 256 else 64
-        pad = -n % step
-        if pad == 0:
-            return spans, tables
-        spans = list(spans) + [(None, 0, [0] * pad, [], NULL_SLOT)]
-        tables = {g: np.vstack([np.asarray(t, dtype=np.int32).reshape(len(spans) - 1, -1),
-                                np.full((1, max(np.asarray(t).reshape(len(spans) - 1, -1).shape[1], 1)), NULL_PAGE, dtype=np.int32)])
-                  for g, t in tables.items()}
-        return spans, tables
+        return pad_rows(spans, tables, self.cache.page_size)
 
     def can_take_device_tokens(self, n_rows: int) -> bool:
         """Whether a step of `n_rows` single tokens may get its tokens from a device tensor."""
         return bool(self.use_graphs and self.graphs.bucket(n_rows) is not None)
 
-    def step(self, entries, trusted: bool = False, device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def check_status(self, step_number: Optional[int] = None) -> None:
+        """Read the kernels' status word (this waits for the device) and raise `StepError` if a kernel
+        met an id outside its bound or gave up a bounded wait: what the step returned is void.  The
+        reference lets every failure of a step come up as an error in the same way
+        (src/paged_attention/block_table.zig:37, src/main.zig:394-402)."""
+        read = getattr(self.ops, "read_status", None)
+        code = read(self.device) if read else 0
+        if code:
+            raise StepError(f"step {self.steps if step_number is None else step_number}: "
+                            f"{self.ops.describe_status(code)} (status {code}); its results are void")
+
+    def step(self, entries, trusted: bool = False, device_tokens: Optional[torch.Tensor] = None,
+             check: bool = True) -> torch.Tensor:
         """entries: (request, its next tokens, wanted places among them).  Returns 32-bit logits
         [wanted, vocab] in the order of the entries and of their wanted places.  (A step that ran
         as a CUDA graph returns a view of that graph's output buffer, valid until the next such step.)
         `device_tokens`: for a step of single tokens, the tokens as an int32 device tensor in the
-        order of the entries; the tokens in `entries` are then placeholders."""
+        order of the entries; the tokens in `entries` are then placeholders.
+        `check`: read the kernels' status word after the step and raise `StepError` if it is raised
+        (this waits for the step; a caller that reads the word with its own results, as `Engine`
+        does in the copy that brings the token ids back, passes False)."""
         spans, tables = self._reserve(entries, trusted)
         n_tokens = sum(len(e[1]) for e in entries)
         graphed = (self.use_graphs and n_tokens == len(entries) and self.graphs.bucket(len(entries)) is not None
@@ -187,7 +189,32 @@ class ModelRunner:
             self.processed[rid] += len(tokens)
         self.steps += 1
         self.tokens_run += n_tokens
+        if check:
+            self.check_status(self.steps - 1)
         return logits
+
+
+def pad_rows(spans, tables, page_size: int):
+    """Round a step's row count up (to a multiple of 32 up to 256 rows, of 64 beyond) with a span of
+    the null request (null slot, null pages, nothing wanted), so that the library's matrix products
+    see few distinct row counts: it plans every new shape once, at a millisecond each, and a
+    serving run would otherwise meet thousands of them.  The added span lies at positions 0..pad-1;
+    every table is widened so that its row covers them."""
+    n = sum(len(s[2]) for s in spans)
+    if n <= 16:                                                # the few-rows kernels: no library product
+        return spans, tables
+    step = 32 if n <= 256 else 64
+    pad = -n % step
+    if pad == 0:
+        return spans, tables
+    spans = list(spans) + [(None, 0, [0] * pad, [], NULL_SLOT)]
+    out = {}
+    for g, t in tables.items():
+        m = np.asarray(t, dtype=np.int32).reshape(len(spans) - 1, -1)
+        wide = np.full((len(spans), max(m.shape[1], -(-pad // page_size), 1)), NULL_PAGE, dtype=np.int32)
+        wide[:len(spans) - 1, :m.shape[1]] = m
+        out[g] = wide
+    return spans, out
 
 
 def load_runner(model_dir: str, dtype="bfloat16", max_tokens: int = 4096, max_requests: int = 64,

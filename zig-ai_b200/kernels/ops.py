@@ -25,34 +25,34 @@ _P, _I, _F = c_void_p, c_int, c_float
 
 _SIGNATURES = {
     "embed": {
-        "zai_embed": [_P, _P, _I, _P, _I, _I, _I, _P],
+        "zai_embed": [_P, _P, _I, _P, _I, _I, _I, _P, _P],
         "zai_gather_add": [_P, _P, _P, _I, _P, _I, _I, _P],
     },
     "norm": {"zai_add_rmsnorm": [_P, _P, _P, _P, _I, _F, _I, _I, _P]},
     "activation": {"zai_silu_mul": [_P, _P, _I, _I, _I, _P]},
-    "shortconv": {"zai_short_conv": [_P, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P]},
+    "shortconv": {"zai_short_conv": [_P, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P]},
     "rope_kv": {
         "zai_rope_table": [_P, _P, _P, _I, _I, _P],
         "zai_qk_norm_rope": [_P, _I, _I, _P, _P, _F, _P, _I, _P, _P, _P, _I, _P, _I, _P, _P,
-                             _I, _I, _I, _I, _I, _I, _P],
-        "zai_kv_write": [_P, _I, _P, _I, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P],
+                             _I, _I, _I, _I, _I, _I, _I, _P, _P],
+        "zai_kv_write": [_P, _I, _P, _I, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P],
     },
     "attention": {
-        "zai_paged_attention_general": [_P, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
+        "zai_paged_attention_general": [_P, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
     },
     "attention_mma": {
         "zai_attention_mma_supports": [_I, _I, _I],
-        "zai_prefill_attention_mma": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
-        "zai_decode_attention_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+        "zai_prefill_attention_mma": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
+        "zai_decode_attention_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
         "zai_decode_attention_fused": [_P, _P, _P, _P, _P, _I, _P, _P, _F, _P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I,
-                                       _F, _I, _I, _I, _P],
+                                       _F, _I, _I, _I, _I, _P, _P],
         "zai_decode_chunk_keys": [],
         "zai_prefill_block_rows": [],
     },
     "decode_gemm": {
         "zai_skinny_gemm_supports": [_I, _I, _I, _I, _I],
         "zai_skinny_gemm": [_P, _P, _P, _P, _P, _P, _P, _P, _F, _I, _I, _I, _I, _P],
-        "zai_skinny_conv": [_P, _P, _P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+        "zai_skinny_conv": [_P, _P, _P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     },
     "gemm_tc": {
         "zai_gemm_tc_supports": [_I, _I, _I, _I],
@@ -232,7 +232,8 @@ def embed(ids, table):
     _cuda(ids, table)
     N, (V, H) = ids.numel(), table.shape
     out = torch.empty((N, H), dtype=torch.float32, device=table.device)
-    _check(_fn("embed", "zai_embed")(_ptr(out), _ptr(table), _dt(table), _ptr(ids), N, H, V, _stream()), "embed")
+    _check(_fn("embed", "zai_embed")(_ptr(out), _ptr(table), _dt(table), _ptr(ids), N, H, V, _status_ptr(table.device),
+                                     _stream()), "embed")
     return out
 
 
@@ -285,36 +286,68 @@ def _skinny(x, w, epilogue, out_cols, out_dtype):
     return y
 
 
-_tc_status = None
 TC_MIN_ROWS = 128        # from this many rows on a product may go to the tcgen05 kernel
 # Measured on B200 (graph-timed, weights from HBM) the library's two-block 256x256 tiles are 1.15x to
 # 2x faster than this one-block 128x{128,256} kernel at the shapes of the LFM2 models, so products go
 # to the library unless ZAI_TC_GEMM=1 asks for the tcgen05 kernel (its tests call it directly).
 USE_TC_GEMM = os.environ.get("ZAI_TC_GEMM", "0") == "1"
 
+# ---- the status word: one int32 per device that kernels OR bits into (csrc/common.cuh: ZaiStatusBit).
+# A kernel that meets an id outside its bound uses id 0 instead, and a kernel whose bounded wait runs
+# out stops waiting; both raise a bit here, and whoever reads the step's results reads this word
+# with them and throws the step away if it is not zero.
+STATUS_BITS = {1: "a bounded wait inside a kernel ran out", 2: "a token id outside the vocabulary",
+               4: "a block-table entry outside the page pool", 8: "a state slot outside the slots",
+               16: "a position outside its request's block-table row"}
+_status = {}
+
+
+def status_tensor(device=None) -> torch.Tensor:
+    """The device's status word (int32 [1]), made at first use."""
+    dev = torch.device("cuda") if device is None else torch.device(device)
+    index = torch.cuda.current_device() if dev.index is None else dev.index
+    entry = _status.get(index)
+    if entry is None:
+        t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", index))
+        entry = _status[index] = (t, t.data_ptr())
+    return entry[0]
+
+
+def _status_ptr(device) -> int:
+    entry = _status.get(device.index)
+    if entry is None:
+        status_tensor(device)
+        entry = _status[torch.cuda.current_device() if device.index is None else device.index]
+    return entry[1]
+
+
+def describe_status(code: int) -> str:
+    return "; ".join(text for bit, text in STATUS_BITS.items() if code & bit) or f"status {code}"
+
+
+def read_status(device=None) -> int:
+    """The status word, cleared (reads the device: waits for the work queued so far)."""
+    t = status_tensor(device)
+    v = int(t.item())
+    if v:
+        t.zero_()
+    return v
+
 
 def tc_status() -> int:
-    """0, or 1 if a block of the tcgen05 kernel gave up a wait since the last call (reads the device)."""
-    if _tc_status is None:
-        return 0
-    v = int(_tc_status.item())
-    if v:
-        _tc_status.zero_()
-    return v
+    """1 if a bounded wait of a kernel ran out since the status word was last read, else 0 (reads the device)."""
+    return 1 if read_status() & 1 else 0
 
 
 def _tensor_core(x, w, epilogue, out_cols, out_dtype):
     """The tcgen05 product kernel, if it takes these operands and is the faster choice; else None."""
-    global _tc_status
     N, (O, K) = x.shape[0], w.shape
     if not USE_TC_GEMM or N < TC_MIN_ROWS or w.dtype != torch.bfloat16 or x.dtype != torch.bfloat16:
         return None
     if not x.is_contiguous() or not _fn("gemm_tc", "zai_gemm_tc_supports")(N, O, K, epilogue):
         return None
-    if _tc_status is None:
-        _tc_status = torch.zeros(1, dtype=torch.int32, device=w.device)
     y = torch.empty((N, out_cols), dtype=out_dtype, device=w.device)
-    _check(_fn("gemm_tc", "zai_gemm_tc")(_ptr(y), _ptr(w), _ptr(x), _ptr(_tc_status), N, O, K, epilogue, _stream()),
+    _check(_fn("gemm_tc", "zai_gemm_tc")(_ptr(y), _ptr(w), _ptr(x), _status_ptr(w.device), N, O, K, epilogue, _stream()),
            "gemm_tc")
     return y
 
@@ -356,17 +389,14 @@ USE_PAIR_GEMM = os.environ.get("ZAI_PAIR_GEMM", "0") == "1"
 def gemm_pair(x, w, epilogue, out_cols, out_dtype, wide=-1):
     """The two-block tcgen05 product kernel: x [N, K] times w [O, K] transposed with the epilogue
     (0 bfloat16, 1 32-bit, 2 SwiGLU over stacked gate|up rows); None if it does not take the operands."""
-    global _tc_status
     _cuda(x, w)
     N, (O, K) = x.shape[0], w.shape
     if w.dtype != torch.bfloat16 or x.dtype != torch.bfloat16 or not x.is_contiguous() or not w.is_contiguous():
         return None
     if not _fn("gemm_tc_pair", "zai_gemm_pair_supports")(N, O, K, epilogue):
         return None
-    if _tc_status is None:
-        _tc_status = torch.zeros(1, dtype=torch.int32, device=w.device)
     y = torch.empty((N, out_cols), dtype=out_dtype, device=w.device)
-    _check(_fn("gemm_tc_pair", "zai_gemm_pair")(_ptr(y), _ptr(w), _ptr(x), _ptr(_tc_status), N, O, K, epilogue, wide,
+    _check(_fn("gemm_tc_pair", "zai_gemm_pair")(_ptr(y), _ptr(w), _ptr(x), _status_ptr(w.device), N, O, K, epilogue, wide,
                                                 _stream()), "gemm_pair")
     return y
 
@@ -419,7 +449,7 @@ def linear_short_conv(x, w_in, conv_w, conv_b, state, step, taps, write_state=Tr
     z = torch.empty((M, C), dtype=torch.bfloat16, device=w_in.device)
     fn = _fn("decode_gemm", "zai_skinny_conv")
     tail = (_ptr(conv_w), _ptr(conv_b), _ptr(state), _ptr(step.slot_ids), M, C, K, int(taps), state.shape[1],
-            int(bool(write_state)), _stream())
+            int(bool(write_state)), state.shape[0], _status_ptr(state.device), _stream())
     if lazy:
         res = x.residual
         _cuda(res.data, x.delta, x.gamma)
@@ -443,7 +473,7 @@ def short_conv(bcx, conv_w, conv_b, state, step, taps, write_state=True):
     _check(_fn("shortconv", "zai_short_conv")(
         _ptr(z), _ptr(bcx), _dt(bcx), _ptr(conv_w), _ptr(conv_b), _ptr(state), _ptr(step.seq_idx), _ptr(step.cu_q),
         _ptr(step.slot_ids), N, step.n_seqs, C, int(taps), state.shape[1], int(step.decode_only),
-        int(write_state), _stream()), "short_conv", 1 if (step.decode_only or taps == 1 or not write_state) else 2)
+        int(write_state), state.shape[0], _status_ptr(state.device), _stream()), "short_conv", 1 if (step.decode_only or taps == 1 or not write_state) else 2)
     return z
 
 
@@ -490,7 +520,8 @@ def qk_norm_rope(qkv, q_w, k_w, eps, rotary_dim, theta, step, cache, heads, kv_h
         _ptr(qkv), cols, _dt(qkv), _ptr(q_w), _ptr(k_w), float(eps), _ptr(table), int(rotary_dim),
         _ptr(step.positions), _ptr(step.seq_idx), _ptr(bt) if do_write else None,
         bt.shape[1] if do_write else 0, _ptr(pages) if do_write else None, cache.page_size, _ptr(q), _ptr(k_out),
-        N, heads, kv_heads, head_dim, int(has_kv), int(do_write), _stream()), "qk_norm_rope")
+        N, heads, kv_heads, head_dim, int(has_kv), int(do_write), pages.shape[0] if do_write else 0,
+        _status_ptr(qkv.device), _stream()), "qk_norm_rope")
     return q, k_out
 
 
@@ -501,7 +532,7 @@ def kv_write(k, v, step, cache, kv_heads, head_dim):
     _check(_fn("rope_kv", "zai_kv_write")(
         _ptr(k), k.stride(0), _ptr(v), v.stride(0), _dt(k), _ptr(step.positions), _ptr(step.seq_idx),
         _ptr(cache.block_table), cache.block_table.shape[1], _ptr(cache.pages), cache.page_size, N, kv_heads,
-        head_dim, _stream()), "kv_write")
+        head_dim, cache.pages.shape[0], _status_ptr(k.device), _stream()), "kv_write")
 
 
 USE_TC_ATTENTION = os.environ.get("ZAI_TC_ATTENTION", "1") == "1"     # tcgen05 prefill attention where the sizes allow
@@ -531,7 +562,7 @@ def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=Non
             _check(_fn("attention_mma", "zai_decode_attention_mma")(
                 _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(q), _ptr(cache.pages), _ptr(bt), bt.shape[1],
                 _ptr(step.positions), n, n_chunks, cache.page_size, heads, kv_heads, head_dim, float(scale),
-                int(window or 0), _stream()), "decode attention", 2)
+                int(window or 0), cache.pages.shape[0], _status_ptr(q.device), _stream()), "decode attention", 2)
 
         if step.decode_only:
             single_tokens(N)
@@ -547,23 +578,20 @@ def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=Non
             n_tiles = (step.attn_tiles - ns) if getattr(step, "attn_tiles", None) else sum(-(-n // block_rows) for n in step.q_lens[ns:])
             if (impl != "mma" and (USE_TC_ATTENTION or impl == "tcgen05") and q.is_contiguous()
                     and _fn("attention_tc", "zai_prefill_attention_tc_supports")(head_dim, heads, kv_heads, cache.page_size)):
-                global _tc_status
-                if _tc_status is None:
-                    _tc_status = torch.zeros(1, dtype=torch.int32, device=q.device)
                 _check(_fn("attention_tc", "zai_prefill_attention_tc")(
-                    _ptr(out), _ptr(q), _ptr(cache.pages), cache.pages.shape[0], _ptr(_tc_status), _ptr(bt), bt.shape[1],
+                    _ptr(out), _ptr(q), _ptr(cache.pages), cache.pages.shape[0], _status_ptr(q.device), _ptr(bt), bt.shape[1],
                     _ptr(cu_q), _ptr(ctx_lens), N, S, n_tiles, cache.page_size, heads, kv_heads,
                     head_dim, float(scale), int(window or 0), _stream()), "prefill attention (tcgen05)")
                 return out
             _check(_fn("attention_mma", "zai_prefill_attention_mma")(
                 _ptr(out), _ptr(q), _ptr(cache.pages), _ptr(bt), bt.shape[1], _ptr(cu_q), _ptr(ctx_lens),
                 S, n_tiles, cache.page_size, heads, kv_heads, head_dim, float(scale), int(window or 0),
-                _stream()), "prefill attention")
+                cache.pages.shape[0], _status_ptr(q.device), _stream()), "prefill attention")
         return out
     _check(_fn("attention", "zai_paged_attention_general")(
         _ptr(out), _ptr(q), _ptr(cache.pages), _dt(q), _ptr(bt), bt.shape[1],
         _ptr(step.positions), _ptr(step.seq_idx), cache.page_size, N, heads, kv_heads, head_dim, float(scale),
-        int(window or 0), _stream()), "paged_attention")
+        int(window or 0), cache.pages.shape[0], _status_ptr(q.device), _stream()), "paged_attention")
     return out
 
 
@@ -606,11 +634,8 @@ def decode_attention_fused(qkv, q_w, k_w, eps, rotary_dim, theta, step, cache, h
     table = rope_table(step, rotary_dim, theta, dev) if rotary_dim else None
     bt = cache.block_table
     if USE_TMA_ATTENTION and _fn("attention_tma", "zai_decode_attention_tma_supports")(head_dim, heads, kv_heads, cache.page_size):
-        global _tc_status
-        if _tc_status is None:
-            _tc_status = torch.zeros(1, dtype=torch.int32, device=dev)
         _check(_fn("attention_tma", "zai_decode_attention_tma")(
-            _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(tickets), _ptr(_tc_status), _ptr(qkv), cols, _ptr(q_w), _ptr(k_w),
+            _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(tickets), _status_ptr(dev), _ptr(qkv), cols, _ptr(q_w), _ptr(k_w),
             float(eps), _ptr(table), int(rotary_dim), _ptr(cache.pages), cache.pages.shape[0], _ptr(bt), bt.shape[1],
             _ptr(step.positions), B, n_chunks, cache.page_size, heads, kv_heads, head_dim, float(scale), int(window or 0),
             int(bool(write)), chunk, _stream()), "decode_attention_tma")
@@ -618,8 +643,8 @@ def decode_attention_fused(qkv, q_w, k_w, eps, rotary_dim, theta, step, cache, h
     _check(_fn("attention_mma", "zai_decode_attention_fused")(
         _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(tickets), _ptr(qkv), cols, _ptr(q_w), _ptr(k_w), float(eps),
         _ptr(table), int(rotary_dim), _ptr(cache.pages), _ptr(bt), bt.shape[1], _ptr(step.positions), B, n_chunks,
-        cache.page_size, heads, kv_heads, head_dim, float(scale), int(window or 0), int(bool(write)), chunk, _stream()),
-        "decode_attention_fused")
+        cache.page_size, heads, kv_heads, head_dim, float(scale), int(window or 0), int(bool(write)), chunk,
+        cache.pages.shape[0], _status_ptr(dev), _stream()), "decode_attention_fused")
     return out
 
 
