@@ -38,9 +38,38 @@ def test_groups_planes_and_shared_caches():
     needs = [("own", STATE), ("own", FULL), ("own", STATE), ("own", FULL), ("shared", 1), ("own", WIN)]
     m = CacheManager(needs, 4, 8, 2, torch.float32, "cpu")
     assert len(m.groups) == 3
-    assert m.where == [(0, 0), (1, 0), (0, 1), (1, 1), (1, 0), (2, 0)]
+    assert m.where == [[(0, 0)], [(1, 0)], [(0, 1)], [(1, 1)], [(1, 0)], [(2, 0)]]
     assert m.groups[1].data.shape == (2, 9, 2, 2, 4, 16) and m.groups[0].data.shape == (2, 3, 2, 8)
     assert m.bytes_per_token() == (2 + 1) * 2 * 2 * 16 * 4
+
+
+def test_several_needs_per_layer_call_and_other_page_layouts():
+    """A layer call may need pages and a state, or two states (a state matrix beside a conv state); a
+    paged need may hold one vector per position instead of keys and values; a state may be kept in
+    another dtype than 32-bit.  Each need gets a view of its own; equal needs share a group."""
+    from zig_ai_b200.parts.base import PagedRowsNeed
+    matrix, conv = StateNeed((4, 4), "bfloat16"), StateNeed((2, 8))
+    latent = PagedRowsNeed(24)
+    needs = [("own", (FULL, conv)), ("own", (matrix, conv)), ("own", None), ("own", latent), ("shared", 1), ("own", (latent, FULL))]
+    m = CacheManager(needs, 4, 8, 2, torch.float32, "cpu")
+    assert [type(g.need).__name__ for g in m.groups] == ["PagedKVNeed", "StateNeed", "StateNeed", "PagedRowsNeed"]
+    assert m.where == [[(0, 0), (1, 0)], [(2, 0), (1, 1)], [], [(3, 0)], [(2, 0), (1, 1)], [(3, 1), (0, 1)]]
+    assert m.groups[2].data.dtype == torch.bfloat16 and m.groups[2].data.shape == (1, 3, 4, 4)
+    assert m.groups[3].data.shape == (2, 9, 4, 24)
+    assert m.bytes_per_token() == (2 * 2 * 2 * 16 + 2 * 24) * 4
+
+    class Step:
+        block_tables = {0: "kv tables", 3: "latent tables"}
+    v = m.views(5, Step)
+    assert len(v) == 2 and v[0].block_table == "latent tables" and v[0].pages.shape == (9, 4, 24)
+    assert v[1].block_table == "kv tables" and v[1].pages.shape == (9, 2, 2, 4, 16)
+    assert m.views(2, Step) == [] and m.view(2, Step).pages is None and m.view(1, Step).state.shape == (3, 4, 4)
+    # pages of both paged groups are taken and given back together
+    m.admit("a")
+    m.reserve("a", 9)
+    assert m.groups[0].pool.n_used == 3 and m.groups[3].pool.n_used == 3
+    m.release("a")
+    m.check()
 
 
 def test_pages_taken_returned_and_reused():

@@ -40,6 +40,7 @@ def test_tiny_configs_parse_and_differ():
     ({"num_key_value_heads": 3}, "multiple"),
     ({"head_dim": 15}, "even"),
     ({"conv_L_cache": 0}, "conv_L_cache"),
+    ({"conv_L_cache": 17}, "more than the 16 taps"),
     ({"norm_eps": "small"}, "norm_eps"),
     ({"architectures": ["NoSuchModel"]}, "unknown architecture"),
     ({"vocab_size": 0}, "vocab_size"),
@@ -131,6 +132,53 @@ def test_load_keeps_dtypes_and_reports_all_faults(tmp_path):
     assert [w[0] for w in err.wrong_dtype] == ["blk.0.attn_k.weight"]
     for word in ("missing", "unexpected", "wrong shape", "blk.9.extra.weight", "[96, 96]"):
         assert word in str(err)
+
+
+def test_other_naming_schemes_load_through_the_rename_table(tmp_path):
+    """A folder that spells its tensors in the other ways the reference accepts (layer.zig:244-253,
+    gguf_model.zig:66-70, `model.layers.{i}.self_attn.*`) gives the same tensors; a tensor stored under
+    two spellings is an error; tensors nobody asks for are an error or, if the caller says so, a list."""
+    from zig_ai_b200.weights.names import canonical_name
+    assert canonical_name("model.layers.3.self_attn.o_proj.weight") == "blk.3.attn_output.weight"
+    assert canonical_name("blk.12.feed_forward.w3.weight") == "blk.12.ffn_up.weight"
+    assert canonical_name("output_norm.weight") == "token_embd_norm.weight"
+    assert canonical_name("blk.1.shortconv.conv.weight") == "blk.1.shortconv.conv.weight"
+    cfg = config_from_dict(TINY_B)
+    decls = build_model(cfg).param_decls()
+    tensors = random_tensors(decls, 3)
+    other = {"self_attn.q_proj.weight": "attn_q.weight", "wk.weight": "attn_k.weight", "self_attn.v_proj.weight": "attn_v.weight",
+             "attn_o.weight": "attn_output.weight", "mlp.gate_proj.weight": "ffn_gate.weight",
+             "feed_forward.w3.weight": "ffn_up.weight", "mlp.down_proj.weight": "ffn_down.weight",
+             "input_layernorm.weight": "attn_norm.weight", "post_attention_layernorm.weight": "ffn_norm.weight"}
+    back = {v: k for k, v in other.items()}
+    renamed = {}
+    for name, t in tensors.items():
+        if name.startswith("blk."):
+            _, i, rest = name.split(".", 2)
+            name = f"model.layers.{i}." + back.get(rest, rest)
+        renamed["output_norm.weight" if name == "token_embd_norm.weight" else name] = t
+    assert set(renamed) != set(tensors)
+    d = str(tmp_path / "renamed")
+    os.makedirs(d)
+    write_safetensors(os.path.join(d, "model.safetensors"), renamed)
+    got = load_tensors(d, decls, torch.bfloat16, "cpu")
+    assert set(got) == set(decls) and all(torch.equal(got[k].float(), tensors[k].float().reshape(got[k].shape)) for k in decls)
+    assert got.renamed["blk.0.attn_q.weight"] == "model.layers.0.self_attn.q_proj.weight" and got.unused == []
+    # the same tensor under two spellings
+    renamed["blk.0.attn_q.weight"] = tensors["blk.0.attn_q.weight"]
+    renamed["rope_freqs.weight"] = torch.zeros(4)
+    renamed["model.layers.0.rotary.inv_freq"] = torch.zeros(4)
+    write_safetensors(os.path.join(d, "model.safetensors"), renamed)
+    with pytest.raises(WeightError) as e:
+        load_tensors(d, decls, torch.bfloat16, "cpu")
+    assert any("stored twice" in u and "attn_q" in u for u in e.value.unexpected)
+    assert any("rotary.inv_freq" in u for u in e.value.unexpected) and not any("rope_freqs" in u for u in e.value.unexpected)
+    del renamed["blk.0.attn_q.weight"]
+    write_safetensors(os.path.join(d, "model.safetensors"), renamed)
+    with pytest.raises(WeightError):
+        load_tensors(d, decls, torch.bfloat16, "cpu")
+    got = load_tensors(d, decls, torch.bfloat16, "cpu", unexpected="warn")
+    assert len(got.unused) == 2 and set(got) == set(decls)
 
 
 def test_random_weights_are_reproducible(tmp_path):

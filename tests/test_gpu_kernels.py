@@ -674,3 +674,88 @@ def test_tma_decode_attention_long_contexts_repeat(ps):
             assert torch.allclose(got.float(), want.float(), atol=2e-3, rtol=2e-2)
         assert torch.equal(got, first), rep
     assert o.tc_status() == 0
+
+
+# ----------------------------------------------------------------------------- ids outside their bounds
+def test_ids_outside_their_bounds_raise_the_status_word_and_touch_nothing():
+    """Every kernel that indexes by page, slot, position or token id is told a pool four pages (a state
+    two slots) smaller than the tensor that was really allocated, and is given an id in the part it was
+    not told of: it must use id 0 instead, leave the part beyond its bound as it was, and raise the
+    matching bit of the status word.  (Not even a missed check would touch foreign memory here.)"""
+    o = ops()
+    dtype, Hq, Hkv, D, ps = torch.bfloat16, 4, 2, 64, 16
+    g = torch.Generator().manual_seed(90)
+    num_pages, told = 40, 36
+    assert o.read_status() == 0
+
+    def fresh(q_lens, ctx):
+        step = make_step(o, dtype, ctx, q_lens, ps, told, 91)            # tables from pages 1..35
+        pages = fill_pages(step, ctx, q_lens, ps, Hkv, D, dtype, num_pages, g, junk=0.0)
+        return step, pages
+
+    # --- pages: spans (page write, the three span attention kernels), then single tokens
+    for q_lens, ctx in (([20, 3], [5, 40]), ([1, 1, 1], [30, 70, 5])):
+        step, pages = fresh(q_lens, ctx)
+        N = sum(q_lens)
+        bad = step.block_tables[0].clone()
+        bad[1, 0] = told + 2                                             # allocated, but beyond what the kernels are told
+        beyond = pages[told:].clone()
+        view = CacheView(0, pages[:told], bad, ps)
+        qkv = torch.randn(N, (Hq + 2 * Hkv) * D, generator=g).to(dtype).cuda()
+        q = qkv[:, :Hq * D].contiguous()
+        w = torch.ones(D, device="cuda")
+        calls = [lambda: o.paged_attention(q, step, view, Hq, Hkv, D, D ** -0.5, None, impl="general")]
+        if step.decode_only:
+            calls += [lambda: o.paged_attention(q, step, view, Hq, Hkv, D, D ** -0.5, None)]
+            for tma in (True, False):
+                def fused(tma=tma):
+                    old, o.USE_TMA_ATTENTION = o.USE_TMA_ATTENTION, tma
+                    try:
+                        o.decode_attention_fused(qkv, w, w, 1e-5, D, 1e4, step, view, Hq, Hkv, D, D ** -0.5, None, True)
+                    finally:
+                        o.USE_TMA_ATTENTION = old
+                calls.append(fused)
+        else:
+            calls += [lambda: o.paged_attention(q, step, view, Hq, Hkv, D, D ** -0.5, None, impl="mma"),
+                      lambda: o.paged_attention(q, step, view, Hq, Hkv, D, D ** -0.5, None, impl="tcgen05")]
+        def run(which):
+            for i, call in enumerate(which):
+                call()
+                assert o.read_status() == 4, (q_lens, i)
+                assert torch.equal(pages[told:], beyond), (q_lens, i)
+
+        run(calls)                                                       # kernels that read the request's first page
+        bad[1, 0] = int(step.block_tables[0][1, 0])
+        bad[1, ctx[1] // ps] = told + 1                                  # the page the request's new rows are written to
+        run([lambda: o.qk_norm_rope(qkv, w, w, 1e-5, D, 1e4, step, view, Hq, Hkv, D, True, True, False),
+             lambda: o.kv_write(qkv[:, Hq * D:(Hq + Hkv) * D], qkv[:, (Hq + Hkv) * D:], step, view, Hkv, D)])
+        # --- positions: a table row narrower than the request's positions
+        narrow = CacheView(0, pages[:told], step.block_tables[0][:, :1].contiguous(), ps)
+        o.qk_norm_rope(qkv, w, w, 1e-5, D, 1e4, step, narrow, Hq, Hkv, D, True, True, False)
+        assert o.read_status() & 16
+        o.paged_attention(q, step, narrow, Hq, Hkv, D, D ** -0.5, None, impl="general")
+        assert o.read_status() & 16
+    # --- slots
+    C, L = 64, 3
+    conv_w = torch.randn(C, L, generator=g).cuda()
+    state = torch.randn(8, L - 1, C, generator=g).cuda()
+    for q_lens in ([1, 1, 1], [4, 1, 6]):
+        step = make_step(o, dtype, [3] * 3, q_lens, ps, told, 92, slots=[1, 7, 2])        # slot 7 is beyond the six it is told
+        bcx = torch.randn(sum(q_lens), 3 * C, generator=g).to(dtype).cuda()
+        keep = state[6:].clone()
+        o.short_conv(bcx, conv_w, None, state[:6], step, L, True)
+        assert o.read_status() == 8 and torch.equal(state[6:], keep)
+    step = make_step(o, dtype, [3] * 3, [1, 1, 1], ps, told, 92, slots=[1, 7, 2])
+    K = 128
+    x = torch.randn(3, K, generator=g).to(dtype).cuda()
+    w_in = (torch.randn(3 * C, K, generator=g) * K ** -0.5).to(dtype).cuda()
+    before = o.launches
+    o.linear_short_conv(x, w_in, conv_w, None, state[:6], step, L, True)                # the product's convolution epilogue
+    assert o.read_status() == 8 and torch.equal(state[6:], keep)
+    # --- token ids
+    table = torch.randn(50, 32, generator=g).to(dtype).cuda()
+    out = o.embed(torch.tensor([3, 50, -1, 49], dtype=torch.int32).cuda(), table)
+    assert o.read_status() == 2 and torch.equal(out[1], table[0].float()) and torch.equal(out[3], table[49].float())
+    # --- and the word is what the step function reads: a raised bit voids the step
+    o.status_tensor().fill_(1)
+    assert o.tc_status() == 1 and o.read_status() == 0

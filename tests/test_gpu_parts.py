@@ -231,7 +231,7 @@ def test_toy_architecture_is_registered_built_and_stepped(toy_registered, tmp_pa
     d = write_random_model(cfg, 31, str(tmp_path / "toy"), matrix_std="fan_in")
     runner = load_runner(d, dtype, max_tokens=256, max_requests=3, page_size=4)
     assert len(runner.cache.groups) == 2                       # the states, and one paged group with a window
-    assert runner.cache.where == [(0, 0), (1, 0), (0, 1), (1, 0)]
+    assert runner.cache.where == [[(0, 0)], [(1, 0)], [(0, 1)], [(1, 0)]]
     W = P.read_weights(d)
     g = random.Random(5)
     reqs = {k: [g.randrange(cfg.vocab_size) for _ in range(n)] for k, n in (("x", 41), ("y", 18))}

@@ -24,7 +24,7 @@ from typing import Dict, List, Optional
 import numpy as np
 import torch
 
-from ..parts.base import PagedKVNeed, StateNeed
+from ..parts.base import StateNeed
 from .pages import IdPool, OutOfPages
 
 NULL_PAGE = 0
@@ -41,7 +41,7 @@ class CacheGroup:
 
     @property
     def paged(self) -> bool:
-        return isinstance(self.need, PagedKVNeed)
+        return hasattr(self.need, "page_shape")
 
 
 @dataclass
@@ -56,47 +56,50 @@ class RequestCache:
 class CacheView:
     """What one layer call sees of the cache during one step."""
     group: int = -1
-    pages: Optional[torch.Tensor] = None        # [num_pages, 2, kv_heads, page_size, head_dim]
+    pages: Optional[torch.Tensor] = None        # [num_pages, *need.page_shape(page_size)]; keys and values:
+    #                                             [num_pages, 2, kv_heads, page_size, head_dim]
     block_table: Optional[torch.Tensor] = None  # [requests of the step, max pages] int32
     page_size: int = 0
-    state: Optional[torch.Tensor] = None        # [slots, *shape] 32-bit
+    state: Optional[torch.Tensor] = None        # [slots, *shape] in the need's dtype (32-bit by default)
 
 
 class CacheManager:
     def __init__(self, needs, page_size: int, num_pages: int, max_requests: int,
                  dtype: torch.dtype, device, allocate: bool = True):
-        """`needs` is `Model.cache_needs()`.  `num_pages` pages (beside the null page) are given to
+        """`needs` is `Model.cache_needs()`: per entry of the running order ("own", its needs) or
+        ("shared", the entry whose cache it reads); the needs of an entry are a tuple (a single need or
+        None is taken as a tuple of one or none).  `num_pages` pages (beside the null page) are given to
         every paged group; `max_requests` slots (beside the null slot) exist."""
         if page_size < 1 or num_pages < 1 or max_requests < 1:
             raise ValueError("page_size, num_pages and max_requests should be positive")
         self.page_size, self.num_pages, self.max_requests = int(page_size), int(num_pages), int(max_requests)
         self.dtype, self.device = dtype, device
         self.groups: List[CacheGroup] = []
-        self.where: List[Optional[tuple]] = []      # running-order entry -> (group, plane) or None
+        self.where: List[List[tuple]] = []          # running-order entry -> [(group, plane) per need]
         by_need = {}
         for k, (how, need) in enumerate(needs):
             if how == "shared":
                 self.where.append(self.where[need])
                 continue
-            if need is None:
-                self.where.append(None)
-                continue
-            if need not in by_need:
-                by_need[need] = len(self.groups)
-                self.groups.append(CacheGroup(need))
-            g = by_need[need]
-            self.where.append((g, len(self.groups[g].members)))
-            self.groups[g].members.append(k)
+            entry = []
+            for one in (() if need is None else (tuple(need) if isinstance(need, (tuple, list)) else (need,))):
+                if one not in by_need:
+                    by_need[one] = len(self.groups)
+                    self.groups.append(CacheGroup(one))
+                g = by_need[one]
+                entry.append((g, len(self.groups[g].members)))
+                self.groups[g].members.append(k)
+            self.where.append(entry)
         for grp in self.groups:
             if grp.paged:
                 grp.pool = IdPool(self.num_pages, first=1, what="page")
                 if allocate:
-                    grp.data = torch.zeros((len(grp.members), self.num_pages + 1, 2, grp.need.kv_heads,
-                                            self.page_size, grp.need.head_dim), dtype=dtype, device=device)
+                    grp.data = torch.zeros((len(grp.members), self.num_pages + 1) + tuple(grp.need.page_shape(self.page_size)),
+                                           dtype=dtype, device=device)
             elif isinstance(grp.need, StateNeed):
                 if allocate:
                     grp.data = torch.zeros((len(grp.members), self.max_requests + 1) + tuple(grp.need.shape),
-                                           dtype=torch.float32, device=device)
+                                           dtype=self._state_dtype(grp.need), device=device)
             else:
                 raise TypeError(f"unknown cache need {grp.need!r}")
         self.slots = IdPool(self.max_requests, first=1, what="slot")
@@ -108,9 +111,17 @@ class CacheManager:
         self._ever_used = [set() for _ in self.groups]
 
     # ------------------------------------------------------------------ sizes
+    def _state_dtype(self, need: StateNeed) -> torch.dtype:
+        if isinstance(need.dtype, torch.dtype):
+            return need.dtype
+        if need.dtype == "model":
+            return self.dtype
+        return {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16,
+                "int32": torch.int32}[need.dtype]
+
     def bytes_per_token(self) -> int:
         esize = torch.empty((), dtype=self.dtype).element_size()
-        return sum(len(g.members) * 2 * g.need.kv_heads * g.need.head_dim * esize for g in self.groups if g.paged)
+        return sum(len(g.members) * g.need.elements_per_token() * esize for g in self.groups if g.paged)
 
     def paged_groups(self):
         return [i for i, g in enumerate(self.groups) if g.paged]
@@ -254,13 +265,20 @@ class CacheManager:
             rows = self._rows[group]
         return rows[slots, :width]
 
+    def views(self, call_index: int, step) -> List[CacheView]:
+        """What the layer call at `call_index` of the running order sees during `step`: one view per
+        need of its block, in the block's order."""
+        out = []
+        for g, plane in self.where[call_index]:
+            grp = self.groups[g]
+            if grp.paged:
+                out.append(CacheView(group=g, pages=grp.data[plane], block_table=step.block_tables[g],
+                                     page_size=self.page_size))
+            else:
+                out.append(CacheView(group=g, state=grp.data[plane]))
+        return out
+
     def view(self, call_index: int, step) -> CacheView:
-        w = self.where[call_index]
-        if w is None:
-            return CacheView()
-        g, plane = w
-        grp = self.groups[g]
-        if grp.paged:
-            return CacheView(group=g, pages=grp.data[plane], block_table=step.block_tables[g],
-                             page_size=self.page_size)
-        return CacheView(group=g, state=grp.data[plane])
+        """The first (for most layers: the only) view of `views`, or an empty one."""
+        v = self.views(call_index, step)
+        return v[0] if v else CacheView()

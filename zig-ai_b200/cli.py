@@ -13,6 +13,12 @@ names and meanings for the options it shares with this engine.
     -np N                      parallel sequences of the same prompt, seeds seed..seed+N-1 (default 1)
     -b, --batch-size N         tokens per step (default 2048)
     -ub, --ubatch-size N       largest prompt portion per step (default 512)
+    --page-size N              positions per cache page (default 64; the reference's BLOCK_SIZE = 16, src/main.zig:604)
+    --num-pages N              pages of the pool (default: room for every sequence at --max-model-len;
+                               the reference's MAX_BLOCKS_GPU, src/main.zig:605-611)
+    --max-num-seqs N           sequences that run at once (default: as many as there are prompts)
+    --profile                  time every step's kernels by class and print the table (PERF_STAGE, src/main.zig:817-931)
+    --allow-unused-tensors     stored tensors that the model does not ask for are passed over with a note
 
 Options of the reference that belong to features outside this engine (-ctk/-ctv, --spec-*, --quant,
 --layer-stream*, -ngl, -jinja) are accepted and ignored with a note.
@@ -51,6 +57,11 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--max-model-len", type=int, default=None)
     ap.add_argument("--eos-id", type=int, default=None)
+    ap.add_argument("--page-size", type=int, default=64)
+    ap.add_argument("--num-pages", type=int, default=None)
+    ap.add_argument("--max-num-seqs", type=int, default=None)
+    ap.add_argument("--profile", action="store_true")
+    ap.add_argument("--allow-unused-tensors", action="store_true")
     ap.add_argument("--random-weights", metavar="CONFIG_JSON", default=None,
                     help="write a model folder with random weights for this config.json into --model and use it")
     for flag in ("-ctk", "--cache-type-k", "-ctv", "--cache-type-v", "--spec-draft-type-k", "--spec-draft-type-v",
@@ -92,9 +103,16 @@ def main(argv=None) -> int:
     from .sampling.sampler import SamplingParams
     import torch
     longest = max(len(p) for p in prompts) + args.max_tokens
-    eng = Engine(args.model, args.dtype, max_num_seqs=max(len(prompts), 1),
-                 max_batched_tokens=min(args.batch_size, max(args.ubatch_size, 1) + len(prompts)),
-                 max_model_len=args.max_model_len or longest)
+    if args.page_size < 1 or (args.num_pages is not None and args.num_pages < 1) or \
+            (args.max_num_seqs is not None and args.max_num_seqs < 1):
+        print("[!] --page-size, --num-pages and --max-num-seqs take positive numbers")
+        return 2
+    n_seqs = args.max_num_seqs or max(len(prompts), 1)
+    eng = Engine(args.model, args.dtype, max_num_seqs=n_seqs,
+                 max_batched_tokens=min(args.batch_size, max(args.ubatch_size, 1) + n_seqs),
+                 max_model_len=args.max_model_len or longest, page_size=args.page_size,
+                 max_tokens=args.num_pages * args.page_size if args.num_pages else None, profile=args.profile,
+                 unexpected_tensors="warn" if args.allow_unused_tensors else "error")
     print(f"[+] model {args.model}: {eng.config.architecture}, dtype {args.dtype}, {len(prompts)} sequence(s)")
     ids = [eng.add_request(p, SamplingParams(
         temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
@@ -119,7 +137,23 @@ def main(argv=None) -> int:
     print(f"[+] prefill: {n_prompt} tokens in {prefill_ms:.1f} ms ({n_prompt / max(prefill_ms, 1e-6) * 1e3:.1f} tok/s)")
     print(f"[+] decode: {max(n_gen - len(ids), 0)} tokens in {decode_s * 1e3:.1f} ms "
           f"({max(n_gen - len(ids), 0) / decode_s:.1f} tok/s)")
+    st = eng.stats()
+    print(f"[+] cache: {eng.runner.cache.num_pages} pages of {args.page_size} positions, high water "
+          + ", ".join(f"{v}" for k, v in st.items() if k.endswith("_pages_high_water")) + f"; {st['preemptions']} preemption(s)")
+    if args.profile:
+        print_profile(eng.profile_report())
     return 0
+
+
+def print_profile(report) -> None:
+    """Per kind of step: milliseconds a step by kernel class (steps launched kernel by kernel)."""
+    for kind, acc in report.items():
+        steps = max(int(acc.get("steps", 0)), 1)
+        rows = sorted(((k, v) for k, v in acc.items() if k not in ("steps", "tokens")), key=lambda kv: -kv[1])
+        total = sum(v for _, v in rows)
+        print(f"[profile] {kind}: {steps} step(s), {int(acc.get('tokens', 0))} tokens, {total / steps:.3f} ms of kernels a step")
+        for k, v in rows:
+            print(f"[profile]   {k:<48s} {v / steps:9.3f} ms  {100 * v / max(total, 1e-12):5.1f} %")
 
 
 if __name__ == "__main__":

@@ -33,6 +33,9 @@ def adjusted_ff_dim(block_ff_dim: int, auto_adjust: bool, multiplier: Optional[f
     return multiple_of * ((f + multiple_of - 1) // multiple_of)
 
 
+MAX_CONV_TAPS = 16      # ZAI_MAX_TAPS of csrc/shortconv.cu
+
+
 @dataclass
 class Lfm2Config(ModelConfig):
     hidden_size: int = 0
@@ -115,6 +118,8 @@ class Lfm2Config(ModelConfig):
         taps = read_key(d, "conv_L_cache", int, 3)
         if taps < 1:
             raise ConfigError(f"conv_L_cache {taps} should be at least 1")
+        if taps > MAX_CONV_TAPS:
+            raise ConfigError(f"conv_L_cache {taps} is more than the {MAX_CONV_TAPS} taps the convolution kernels take")
         vocab = read_key(d, "vocab_size", int)
         if vocab < 1:
             raise ConfigError("vocab_size should be positive")

@@ -750,11 +750,10 @@ template <int D> static size_t decode_fused_smem() {
 template <int D>
 static int launch_decode_fused(const FusedDecodeArgs& a, int B, int n_chunks, cudaStream_t stream) {
     const size_t smem = decode_fused_smem<D>();
-    static bool configured = false;
-    if (!configured) {
+    static unsigned long long configured = 0;
+    if (zai_first_on_device(&configured)) {
         cudaError_t e = cudaFuncSetAttribute(decode_fused_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
     }
     return launch_pdl(decode_fused_kernel<D>, dim3(n_chunks, a.Hkv, B), dim3(NTHREADS), smem, stream, a);
 }
@@ -771,11 +770,10 @@ static int launch_prefill(bf16* out, const bf16* q, const bf16* pages, const int
                           const int* cu_q, const int* ctx_lens, int S, int n_tiles, int page_size, int Hq, int Hkv,
                           float scale, int window, int num_pages, int* status, cudaStream_t stream) {
     const size_t smem = prefill_smem<D>();
-    static bool configured = false;
-    if (!configured) {
+    static unsigned long long configured = 0;
+    if (zai_first_on_device(&configured)) {
         cudaError_t e = cudaFuncSetAttribute(prefill_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
     }
     return launch_pdl(prefill_mma_kernel<D>, dim3(n_tiles, Hq), dim3(PREFILL_WARPS * 32), smem, stream,
                       out, q, pages, block_table, table_width, cu_q, ctx_lens, S, page_size, Hq, Hkv,
@@ -788,11 +786,10 @@ static int launch_decode(bf16* out, float* part_o, float* part_ml, const bf16* q
                          int page_size, int Hq, int Hkv, float scale, int window, int num_pages, int* status,
                          cudaStream_t stream) {
     const size_t smem = decode_smem<D>();
-    static bool configured = false;
-    if (!configured) {
+    static unsigned long long configured = 0;
+    if (zai_first_on_device(&configured)) {
         cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
     }
     int e = launch_pdl(decode_mma_kernel<D>, dim3(n_chunks, Hkv, B), dim3(NTHREADS), smem, stream,
                        part_o, part_ml, q, pages, block_table, table_width, positions, page_size, Hq, Hkv,

@@ -472,14 +472,13 @@ ZAI_API int zai_prefill_attention_tc(void* out, const void* q, const void* pages
     a.page_shift = 0;
     while ((1 << a.page_shift) < page_size) ++a.page_shift;
     const size_t smem = AT_Q_BYTES + (size_t)AT_STAGES * AT_KV_BYTES + AT_P_BYTES + 128;
-    static bool configured = false;
-    if (!configured) {
+    static unsigned long long configured = 0;
+    if (zai_first_on_device(&configured)) {
         cudaError_t err = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return (int)err;
         // two blocks per SM: ask for the largest shared-memory carve-out
         err = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         if (err != cudaSuccess) return (int)err;
-        configured = true;
     }
     return launch_pdl(prefill_tc_kernel, dim3(n_tiles, Hq), dim3(AT_THREADS), smem, stream, mq, mkv, a);
 }

@@ -475,11 +475,11 @@ ZAI_API int zai_decode_attention_tma(void* out, float* part_o, float* part_ml, i
     a.stages = tiles < TT_STAGES ? (tiles < 2 ? 2 : tiles) : TT_STAGES;
     const size_t tail = (size_t)16 * (TT_D + 8) * 2 + (size_t)4 * TT_D * 4 + (size_t)2 * TT_D * 2 + 16 * 4;
     const size_t smem = 1024 + (size_t)a.stages * TT_STAGE_BYTES + tail;
-    static size_t configured = 0;
-    if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static unsigned long long configured = 0;
+    if (zai_first_on_device(&configured)) {                // once per device, for the longest ring
+        const size_t most = 1024 + (size_t)TT_STAGES * TT_STAGE_BYTES + tail;
+        cudaError_t e = cudaFuncSetAttribute(decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most);
         if (e != cudaSuccess) return (int)e;
-        configured = smem;
     }
     a.chunk_fastest = (long long)B * Hkv * n_chunks > 6 * (long long)tt_sm_count();    // more than two rounds of three blocks per SM
     const dim3 grid = a.chunk_fastest ? dim3(n_chunks, Hkv, B) : dim3(Hkv, B, n_chunks);

@@ -194,6 +194,16 @@ static inline bool pdl_enabled() {
     return on == 1;
 }
 
+// True the first time it is called with `*done` on each device: a kernel's attributes (its dynamic
+// shared-memory limit) are set per device, so a launcher sets them on its first launch on every device.
+static inline bool zai_first_on_device(unsigned long long* done) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
+    if ((*done >> dev) & 1ull) return false;
+    *done |= 1ull << dev;
+    return true;
+}
+
 template <typename... KArgs, typename... Args>
 static inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                              Args... args) {

@@ -608,11 +608,10 @@ __global__ void __launch_bounds__(SG_WARPS * 32) skinny_splitk_kernel(const Spli
 template <int MT, int CS>
 static int splitk_launch(const SplitKArgs& a, cudaStream_t stream) {
     const size_t smem = (size_t)SG_WARPS * SK_MAX_BLOCKS * (2 + MT) * 512 + (size_t)(SG_WARPS + CS) * MT * 4 * 32 * sizeof(float);
-    static bool configured = false;
-    if (!configured) {
+    static unsigned long long configured = 0;
+    if (zai_first_on_device(&configured)) {
         cudaError_t e = cudaFuncSetAttribute(skinny_splitk_kernel<MT, CS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(a.n_tiles * CS));

@@ -301,11 +301,10 @@ static int tc_launch(const CUtensorMap& mw, const CUtensorMap& mx, TcArgs a, int
     if (stages < 2) return ZAI_BAD_SIZE;
     a.stages = stages;
     const size_t smem = stage * stages + 1024;
-    static bool configured = false;
-    if (!configured) {
+    static unsigned long long configured = 0;
+    if (zai_first_on_device(&configured)) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, ACC_BUFS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
     }
     a.tiles_o = o_tiles;
     a.tiles = o_tiles * ((a.N + BN - 1) / BN);

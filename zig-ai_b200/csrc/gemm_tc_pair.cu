@@ -377,11 +377,10 @@ static int tp_launch(const CUtensorMap& mx, const CUtensorMap& mw, TpArgs a, int
     a.stages = stages;
     a.prefetch = prefetch;
     const size_t smem = stage * stages + 1024;
-    static bool configured = false;
-    if (!configured) {
+    static unsigned long long configured = 0;
+    if (zai_first_on_device(&configured)) {
         cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<WR, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
     }
     a.tiles_m = (a.N + 2 * TP_BM - 1) / (2 * TP_BM);
     a.tiles = a.tiles_m * w_tiles;

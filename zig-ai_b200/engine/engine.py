@@ -28,10 +28,14 @@ from .scheduler import RUNNING, PlanEntry, Request, Scheduler, StepPlan
 class Engine:
     def __init__(self, model_dir: str, dtype="bfloat16", max_num_seqs: int = 64, max_batched_tokens: int = 2048,
                  max_model_len: Optional[int] = None, max_tokens: Optional[int] = None, page_size: int = 64,
-                 device=None, ops=None, pipeline: bool = True):
+                 device=None, ops=None, pipeline: bool = True, profile: bool = False,
+                 unexpected_tensors: str = "error"):
         """`max_tokens`: positions the cache pool holds in all (default: room for `max_num_seqs`
         requests of `max_model_len`, capped at 1 Mi positions).  `pipeline`: keep one decode step
-        ahead of the host (a step's tokens are then handed out by the `step()` call after it)."""
+        ahead of the host (a step's tokens are then handed out by the `step()` call after it).
+        `profile`: time every step's kernels by class with CUDA events (`profile_report()`); steps are
+        then launched kernel by kernel, not replayed as graphs, and none runs ahead of the host.
+        `unexpected_tensors`: see `load_runner`."""
         from ..config import load_config
         cfg = load_config(model_dir)
         model_max = getattr(cfg, "max_position_embeddings", 1 << 30)
@@ -40,13 +44,16 @@ class Engine:
             max_tokens = min(self.max_model_len * max_num_seqs, 1 << 20)
         self.runner: ModelRunner = load_runner(model_dir, dtype, max_tokens=max_tokens, max_requests=max_num_seqs,
                                                page_size=page_size, device=device, ops=ops,
-                                               max_positions=self.max_model_len)
+                                               max_positions=self.max_model_len, graphs=not profile,
+                                               unexpected_tensors=unexpected_tensors)
+        self.profile = bool(profile) and hasattr(self.runner.ops, "profile_begin")
+        self._profile: Dict[str, Dict[str, float]] = {}
         self.config = self.runner.config
         self.scheduler = Scheduler(self.runner.cache, max_num_seqs, max_batched_tokens, self.max_model_len,
                                    owner=self.runner)
         self.sampler = Sampler(self.runner.ops, self.runner.device)
         self._next_id = 0
-        self.pipeline = bool(pipeline)
+        self.pipeline = bool(pipeline) and not profile
         self._inflight = None             # a launched step not read back yet: (plan, requests in row order, ids on the
         #                                   device, their pinned host copy, the event after that copy)
         self._host_ids: List[torch.Tensor] = []
@@ -80,6 +87,8 @@ class Engine:
     def _launch(self, plan: StepPlan, device_tokens: Optional[torch.Tensor] = None):
         """Run the plan's step and its sampling kernel; nothing is read back."""
         entries = [(e.request.request_id, e.tokens, [len(e.tokens) - 1] if e.sample else []) for e in plan.entries]
+        if self.profile:
+            self.runner.ops.profile_begin()
         logits = self.runner.step(entries, trusted=True, device_tokens=device_tokens, check=False)
         number = self.runner.steps - 1
         wanting = [e.request for e in plan.entries if e.sample]
@@ -88,6 +97,13 @@ class Engine:
                                          [r.output for r in wanting])
         # the copy to the host is queued now, before any later step's kernels, so that reading it
         # waits for this step only
+        if self.profile:
+            kind = "decode steps" if all(len(e.tokens) == 1 for e in plan.entries) else "steps with prompt portions"
+            acc = self._profile.setdefault(kind, {"steps": 0, "tokens": 0})
+            acc["steps"] += 1
+            acc["tokens"] += plan.n_tokens
+            for name, ms in self.runner.ops.profile_end().items():
+                acc[name] = acc.get(name, 0.0) + ms
         # the kernels' status word rides along, behind the ids in the same pinned buffer
         status = getattr(self.runner.ops, "status_tensor", None)
         status = status(self.runner.device) if status else None
@@ -215,6 +231,11 @@ class Engine:
         if failed:
             raise RuntimeError(f"{len(failed)} request(s) could not be served: out of pages")
         return [done[i].output for i in ids]
+
+    def profile_report(self) -> Dict[str, Dict[str, float]]:
+        """With `profile=True`: per kind of step, the number of steps and tokens and the milliseconds
+        its kernels took by class (the reference's PERF_STAGE table, src/main.zig:1369-1412)."""
+        return {k: dict(v) for k, v in self._profile.items()}
 
     def stats(self) -> dict:
         out = dict(self.runner.cache.stats())

@@ -18,6 +18,7 @@ from ..cache.manager import NULL_PAGE, NULL_SLOT
 from .batch import StepBatch
 
 BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+HOST_BUFFERS = 3        # pinned staging buffers per graph, used in turn
 
 
 class StaticDecodeStep:
@@ -26,7 +27,11 @@ class StaticDecodeStep:
     def __init__(self, ops, dtype, device, B: int, widths: Dict[int, int], page_size: int = 1):
         self.B, self.widths = B, dict(widths)
         n = 3 * B + (B + 1) + 3 * B + sum(B * w for w in widths.values())
-        self.host = torch.zeros(n, dtype=torch.int32).pin_memory()
+        # Pinned staging, taken in turn: the copy to the device is asynchronous, and a caller that keeps a
+        # step ahead of the host packs the next description while the last one's copy may still be queued.
+        self.hosts = [torch.zeros(n, dtype=torch.int32).pin_memory() for _ in range(HOST_BUFFERS)]
+        self.turn = 0
+        self.host = self.hosts[0]
         self.dev = torch.zeros(n, dtype=torch.int32, device=device)
         off = 0
 
@@ -62,7 +67,9 @@ class StaticDecodeStep:
     def pack(self, spans, tables, host: torch.Tensor = None) -> torch.Tensor:
         """Write the description of the live rows (request, ctx_len, [token], wanted, slot) and padding
         into a pinned host buffer (this step's own if none is given).  `tables[g]` is [n, >= width]."""
-        host = self.host if host is None else host
+        if host is None:
+            self.turn = (self.turn + 1) % len(self.hosts)
+            host = self.host = self.hosts[self.turn]
         hv = host.numpy()
         n, B = len(spans), self.B
         hv[:] = self._template
@@ -130,7 +137,7 @@ class ShapeGraphs:
         # every table row is wide enough for them, however few positions the pool holds
         self.widths = {g: max(w, -(-64 // cache.page_size)) for g, w in widths.items()}
         self.seen: Dict[tuple, int] = {}
-        self.graphs: Dict[tuple, tuple] = {}          # key -> (graph, host, dev, logits, launches)
+        self.graphs: Dict[tuple, tuple] = {}          # key -> (graph, pinned staging buffers, dev, logits, launches)
         self.replays = 0
 
     @staticmethod
@@ -183,9 +190,11 @@ class ShapeGraphs:
             # place (conv state, pages) must see it once.  So this step runs eagerly now, and the
             # graph is captured from a dry run on the null request's slot and page afterwards.
             return self._capture_later(k, spans_p, tables_p, lay, host, dev, batch)[:n_wanted]
-        graph, host, dev, logits, launches = entry
+        graph, hosts, dev, logits, launches = entry
         spans_p, tables_p = self._fill(k, spans, tables)
         flat, _ = pack_host(spans_p, tables_p, self.widths, pad_wanted=k[2])
+        hosts.append(hosts.pop(0))                    # staging buffers in turn (the copy below is asynchronous)
+        host = hosts[0]
         host.numpy()[:] = flat
         dev.copy_(host, non_blocking=True)
         graph.replay()
@@ -216,7 +225,8 @@ class ShapeGraphs:
             self.ops.launches = before
         while len(self.graphs) >= self.KEEP:
             self.graphs.pop(next(iter(self.graphs)))
-        self.graphs[k] = (graph, host, dev, logits, launches)
+        hosts = [host] + [torch.empty_like(host).pin_memory() for _ in range(HOST_BUFFERS - 1)]
+        self.graphs[k] = (graph, hosts, dev, logits, launches)
         return logits_now
 
 

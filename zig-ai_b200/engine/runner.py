@@ -42,8 +42,7 @@ class ModelRunner:
     def enable_graphs(self, max_positions: int) -> bool:
         """Run decode-only steps as CUDA graphs, if the device is CUDA and every part says its
         forward can be captured (no host reads of device data)."""
-        parts = [p for b in self.model.blocks for p in (b, b.mixer, b.feed_forward, b.mixer_norm, b.ff_norm)]
-        if self.device.type != "cuda" or not all(getattr(p, "graph_safe", False) for p in parts + [self.model.final_norm]):
+        if self.device.type != "cuda" or not all(getattr(p, "graph_safe", False) for p in self.model.all_parts()):
             return False
         from .graph import DecodeGraphs, ShapeGraphs
         self.graphs = DecodeGraphs(self.model, self.cache, self.ops, self.dtype, self.device,
@@ -219,9 +218,10 @@ def pad_rows(spans, tables, page_size: int):
 
 def load_runner(model_dir: str, dtype="bfloat16", max_tokens: int = 4096, max_requests: int = 64,
                 page_size: int = 64, device=None, ops=None, graphs: bool = True,
-                max_positions: Optional[int] = None) -> ModelRunner:
+                max_positions: Optional[int] = None, unexpected_tensors: str = "error") -> ModelRunner:
     """Read config.json, build the model its architecture names, load the tensors and make a cache
-    for `max_tokens` positions."""
+    for `max_tokens` positions.  `unexpected_tensors`: "error" (stored tensors that the model does not ask
+    for are listed in the loader's error) or "warn" (they are passed over with a note)."""
     from ..config import load_config
     from ..weights import load_tensors
     tdtype = parse_dtype(dtype)
@@ -234,7 +234,7 @@ def load_runner(model_dir: str, dtype="bfloat16", max_tokens: int = 4096, max_re
     device = torch.device(device)
     cfg = load_config(model_dir)
     model = build_model(cfg)
-    tensors = load_tensors(model_dir, model.param_decls(), tdtype, device)
+    tensors = load_tensors(model_dir, model.param_decls(), tdtype, device, unexpected=unexpected_tensors)
     model.bind(tensors, tdtype)
     num_pages = max(-(-int(max_tokens) // page_size), 1)
     cache = CacheManager(model.cache_needs(), page_size, num_pages, max_requests, tdtype, device)

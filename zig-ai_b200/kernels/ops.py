@@ -222,12 +222,71 @@ def _cuda(*tensors):
             raise KernelError("kernels take contiguous CUDA tensors")
 
 
+# ----------------------------------------------------------------------------- timing by kernel class
+# The reference prints, per stage of a step, the time its kernels took (PERF_STAGE, src/main.zig:817-931,
+# 1369-1412).  Here `profile_begin()` makes every kernel function below record a CUDA event before and
+# after its launches under the name of its class; `profile_end()` waits and returns milliseconds per
+# class.  No special build is needed; steps must be launched kernel by kernel for it (a replayed graph
+# has no place for events), so their sum is larger than a graphed step's time: it is the shares that count.
+_profile = None
+_profile_depth = 0
+
+
+def profile_begin() -> None:
+    global _profile
+    _profile = []
+
+
+def profile_end() -> dict:
+    """Milliseconds per kernel class since `profile_begin()` (waits for the device)."""
+    global _profile
+    records, _profile = _profile or [], None
+    torch.cuda.synchronize()
+    out = {}
+    for name, a, b in records:
+        out[name] = out.get(name, 0.0) + a.elapsed_time(b)
+    return out
+
+
+def _timed(name):
+    """Record the decorated kernel function under class `name` while a profile is open (`name` may be a
+    function of the call's arguments and result).  A call that launched nothing (returned None) is not
+    recorded."""
+    def wrap(f):
+        import functools
+
+        @functools.wraps(f)
+        def g(*args, **kwargs):
+            global _profile_depth
+            if _profile is None or _profile_depth:             # (a kernel function called by another counts with it)
+                return f(*args, **kwargs)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            _profile_depth += 1
+            try:
+                r = f(*args, **kwargs)
+            finally:
+                _profile_depth -= 1
+            if r is None and f.__name__.startswith("_"):
+                return r
+            b.record()
+            _profile.append((name(*args, **kwargs) if callable(name) else name, a, b))
+            return r
+        return g
+    return wrap
+
+
+def _product_class(x, w, epilogue, *rest, **kw):
+    return {_EPI_F32: "head", _EPI_SWIGLU: "products (gate/up + SwiGLU)", 3: "products (in_proj + conv)"}.get(epilogue, "products")
+
+
 # ----------------------------------------------------------------------------- kernels
 fuses_norm = True       # `linear` and `linear_swiglu` take a LazyNorm and apply it inside the product kernel
 
 _EPI_BF16, _EPI_F32, _EPI_SWIGLU = 0, 1, 2
 
 
+@_timed("embedding")
 def embed(ids, table):
     _cuda(ids, table)
     N, (V, H) = ids.numel(), table.shape
@@ -237,6 +296,7 @@ def embed(ids, table):
     return out
 
 
+@_timed("norm")
 def gather_add(h, pending, rows):
     _cuda(h, pending, rows)
     R, H = rows.numel(), h.shape[1]
@@ -247,6 +307,7 @@ def gather_add(h, pending, rows):
     return out
 
 
+@_timed("norm")
 def add_rmsnorm(h, delta, w, eps, out_dtype):
     _cuda(h, delta, w)
     if h.dtype != torch.float32 or w.dtype != torch.float32:
@@ -260,6 +321,7 @@ def add_rmsnorm(h, delta, w, eps, out_dtype):
     return out
 
 
+@_timed(_product_class)
 def _skinny(x, w, epilogue, out_cols, out_dtype):
     """The few-rows product kernel, if it takes these operands; else None."""
     lazy = isinstance(x, LazyNorm)
@@ -339,6 +401,7 @@ def tc_status() -> int:
     return 1 if read_status() & 1 else 0
 
 
+@_timed(_product_class)
 def _tensor_core(x, w, epilogue, out_cols, out_dtype):
     """The tcgen05 product kernel, if it takes these operands and is the faster choice; else None."""
     N, (O, K) = x.shape[0], w.shape
@@ -368,6 +431,12 @@ def linear(x, w, out_dtype=None):
         y = _tensor_core(x, w, _EPI_F32 if out_dtype == torch.float32 else _EPI_BF16, w.shape[0], out_dtype)
         if y is not None:
             return y
+    return _library_product(x, w, out_dtype)
+
+
+@_timed(lambda x, w, out_dtype: "head" if out_dtype == torch.float32 and x.dtype != torch.float32 else "products")
+def _library_product(x, w, out_dtype):
+    """The library's matrix product: true 32-bit where an operand or the result is 32-bit."""
     if x.dtype == torch.float32 or w.dtype == torch.float32 or out_dtype == torch.float32:
         if torch.backends.cuda.matmul.allow_tf32:
             torch.backends.cuda.matmul.allow_tf32 = False
@@ -386,6 +455,7 @@ PAIR_SWIGLU_MIN_ROWS = int(os.environ.get("ZAI_PAIR_SWIGLU_MIN_ROWS", "1024"))
 USE_PAIR_GEMM = os.environ.get("ZAI_PAIR_GEMM", "0") == "1"
 
 
+@_timed(_product_class)
 def gemm_pair(x, w, epilogue, out_cols, out_dtype, wide=-1):
     """The two-block tcgen05 product kernel: x [N, K] times w [O, K] transposed with the epilogue
     (0 bfloat16, 1 32-bit, 2 SwiGLU over stacked gate|up rows); None if it does not take the operands."""
@@ -419,6 +489,7 @@ def linear_swiglu(x, w_gate_up, ff_dim):
     return silu_mul(linear(x, w_gate_up), ff_dim)
 
 
+@_timed("activation")
 def silu_mul(gu, ff_dim):
     _cuda(gu)
     N = gu.shape[0]
@@ -445,6 +516,11 @@ def linear_short_conv(x, w_in, conv_w, conv_b, state, step, taps, write_state=Tr
              and M == step.n_seqs and _fn("decode_gemm", "zai_skinny_gemm_supports")(M, O, K, _EPI_CONV, int(lazy)))
     if not fused:
         return short_conv(linear(x, w_in), conv_w, conv_b, state, step, taps, write_state)
+    return _skinny_conv(x, w_in, conv_w, conv_b, state, step, taps, write_state, lazy, M, C, K)
+
+
+@_timed("products (in_proj + conv)")
+def _skinny_conv(x, w_in, conv_w, conv_b, state, step, taps, write_state, lazy, M, C, K):
     _cuda(w_in, conv_w, conv_b, state)
     z = torch.empty((M, C), dtype=torch.bfloat16, device=w_in.device)
     fn = _fn("decode_gemm", "zai_skinny_conv")
@@ -464,6 +540,7 @@ def linear_short_conv(x, w_in, conv_w, conv_b, state, step, taps, write_state=Tr
     return z
 
 
+@_timed("conv")
 def short_conv(bcx, conv_w, conv_b, state, step, taps, write_state=True):
     _cuda(bcx, conv_w, conv_b, state)
     N, C = bcx.shape[0], bcx.shape[1] // 3
@@ -491,6 +568,7 @@ def inverse_frequencies(rotary_dim: int, theta: float, device) -> torch.Tensor:
     return t
 
 
+@_timed("q/k norm, rotation, page write")
 def rope_table(step, rotary_dim: int, theta: float, device) -> torch.Tensor:
     """(cos, sin) of position * frequency for every row of the step, [N, rotary_dim/2, 2] 32-bit,
     computed once per step and rotation and kept with the step."""
@@ -505,6 +583,7 @@ def rope_table(step, rotary_dim: int, theta: float, device) -> torch.Tensor:
     return t
 
 
+@_timed("q/k norm, rotation, page write")
 def qk_norm_rope(qkv, q_w, k_w, eps, rotary_dim, theta, step, cache, heads, kv_heads, head_dim,
                  has_kv=True, write=True, return_k=False):
     _cuda(qkv, q_w, k_w)
@@ -525,6 +604,7 @@ def qk_norm_rope(qkv, q_w, k_w, eps, rotary_dim, theta, step, cache, heads, kv_h
     return q, k_out
 
 
+@_timed("q/k norm, rotation, page write")
 def kv_write(k, v, step, cache, kv_heads, head_dim):
     if k.stride(-1) != 1 or v.stride(-1) != 1:
         raise KernelError("k and v rows should be contiguous")
@@ -538,6 +618,7 @@ def kv_write(k, v, step, cache, kv_heads, head_dim):
 USE_TC_ATTENTION = os.environ.get("ZAI_TC_ATTENTION", "1") == "1"     # tcgen05 prefill attention where the sizes allow
 
 
+@_timed("attention")
 def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=None, impl=None):
     """Causal attention of the step's rows over their requests' pages.  bfloat16 runs on the
     tensor cores (a split-key kernel when every span is one token, else the flash-style kernel)
@@ -605,6 +686,7 @@ def fused_decode_attention_available(dtype, heads, kv_heads, head_dim) -> bool:
     return dtype == torch.bfloat16 and bool(_fn("attention_mma", "zai_attention_mma_supports")(head_dim, heads, kv_heads))
 
 
+@_timed("attention (with q/k norm, rotation, page write)")
 def decode_attention_fused(qkv, q_w, k_w, eps, rotary_dim, theta, step, cache, heads, kv_heads, head_dim, scale,
                            window=None, write=True):
     """A decode step's attention in one kernel, from the qkv projection's rows [B, (Hq + 2 Hkv) D]:
@@ -648,6 +730,7 @@ def decode_attention_fused(qkv, q_w, k_w, eps, rotary_dim, theta, step, cache, h
     return out
 
 
+@_timed("sampling")
 def argmax(logits):
     _cuda(logits)
     R, V = logits.shape
@@ -656,6 +739,7 @@ def argmax(logits):
     return out
 
 
+@_timed("sampling")
 def repetition_penalty(logits, tokens, counts, offsets, penalty):
     """In place: logits[r, tokens[i]] is penalised counts[i] times for offsets[r] <= i < offsets[r+1]."""
     _cuda(logits, tokens, counts, offsets, penalty)
@@ -665,6 +749,7 @@ def repetition_penalty(logits, tokens, counts, offsets, penalty):
     return logits
 
 
+@_timed("sampling")
 def sample(logits, temperature, top_k, top_p, u):
     _cuda(logits, temperature, top_k, top_p, u)
     R, V = logits.shape

@@ -26,14 +26,11 @@ def build_spec(cfg: Lfm2Config) -> ModelSpec:
         else:
             mixer = PartSpec("short_conv", dict(
                 hidden=cfg.hidden_size, conv_dim=cfg.hidden_size, taps=cfg.conv_L_cache, bias=cfg.conv_bias))
-        layers.append(LayerSpec(
-            prefix=f"blk.{i}.",
-            block=PartSpec("prenorm_residual"),
+        layers.append(LayerSpec(prefix=f"blk.{i}.", block=PartSpec("prenorm_residual", dict(
             mixer=mixer,
             feed_forward=PartSpec("swiglu", dict(hidden=cfg.hidden_size, ff_dim=cfg.ff_dim)),
             mixer_norm=PartSpec("rmsnorm", dict(size=cfg.hidden_size, eps=cfg.norm_eps, weight="attn_norm.weight")),
-            ff_norm=PartSpec("rmsnorm", dict(size=cfg.hidden_size, eps=cfg.norm_eps, weight="ffn_norm.weight")),
-        ))
+            ff_norm=PartSpec("rmsnorm", dict(size=cfg.hidden_size, eps=cfg.norm_eps, weight="ffn_norm.weight"))))))
     return ModelSpec(
         architecture=ARCHITECTURE,
         hidden_size=cfg.hidden_size,

@@ -15,12 +15,19 @@ from .base import Block, register_part
 class PreNormResidual(Block):
     graph_safe = True      # forward launches kernels only; nothing is read back to the host
 
+    def __init__(self, mixer, feed_forward, mixer_norm, ff_norm):
+        super().__init__()
+        self.mixer_norm = self.sub("mixer_norm", "norm", mixer_norm)
+        self.mixer = self.sub("mixer", "mixer", mixer)
+        self.ff_norm = self.sub("ff_norm", "norm", ff_norm)
+        self.feed_forward = self.sub("feed_forward", "feed_forward", feed_forward)
+
     def params(self):
         return {}
 
     def forward(self, h, pending, step, cache, write_cache=True):
         r = self.mixer_norm.forward(h, pending, step, lazy=self.mixer.accepts_lazy_input)
-        m = self.mixer.forward(r, step, cache, write_cache)
+        m = self.mixer.forward(r, step, self.cache_for(self.mixer, cache), write_cache)
         r2 = self.ff_norm.forward(h, m, step, lazy=self.feed_forward.accepts_lazy_input)
         f = self.feed_forward.forward(r2, step)
         return h, f

@@ -18,6 +18,9 @@ from __future__ import annotations
 from .base import Mixer, ParamDecl, StateNeed, register_part
 
 
+MAX_TAPS = 16      # ZAI_MAX_TAPS of csrc/shortconv.cu
+
+
 class ShortConv(Mixer):
     accepts_lazy_input = True     # x goes straight into a product
     graph_safe = True      # forward launches kernels only; nothing is read back to the host
@@ -26,6 +29,8 @@ class ShortConv(Mixer):
         self.hidden, self.conv_dim, self.taps, self.bias = int(hidden), int(conv_dim), int(taps), bool(bias)
         if self.taps < 1:
             raise ValueError("a convolution needs at least one tap")
+        if self.taps > MAX_TAPS:
+            raise ValueError(f"{self.taps} taps are more than the {MAX_TAPS} the convolution kernels take")
 
     def params(self):
         p = {
