@@ -95,6 +95,29 @@ def test_command_line(tiny_models):
     assert "decode:" in out.stdout and "prefill:" in out.stdout
 
 
+def test_command_line_sizes_the_pool_and_profiles(tiny_models):
+    """--page-size, --num-pages and --max-num-seqs size the engine (four sequences through two seats and a
+    pool of 12 pages of 8 positions: the same tokens as alone); --profile prints the time by kernel class
+    for both kinds of step and changes no token."""
+    base = [sys.executable, os.path.join(ROOT, "bin", "zig-ai-engine"), "-m", tiny_models["C"], "--prompt", "5,17,3,900,41",
+            "-n", "7", "--temperature", "0"]
+    want = plain_greedy(tiny_models["C"], [5, 17, 3, 900, 41], 7)
+    out = subprocess.run(base + ["--dtype", "float32", "-np", "4", "--max-num-seqs", "2", "--page-size", "8", "--num-pages", "12"],
+                         capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr
+    lines = [l for l in out.stdout.splitlines() if l.startswith("[") and ") " in l and not l.startswith("[+]")]
+    assert len(lines) == 4 and all([int(x) for x in l.split(")")[1].split()] == want for l in lines)
+    assert "12 pages of 8 positions" in out.stdout
+    out = subprocess.run(base + ["--dtype", "bfloat16", "--profile"], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr
+    prof = [l for l in out.stdout.splitlines() if l.startswith("[profile]")]
+    assert any("decode steps" in l for l in prof) and any("steps with prompt portions" in l for l in prof)
+    for word in ("attention", "products", "head", "sampling", "embedding"):
+        assert any(word in l for l in prof), word
+    bad = subprocess.run(base + ["--page-size", "0"], capture_output=True, text=True, timeout=600)
+    assert bad.returncode == 2
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_repeated_step_shapes_run_as_graphs_and_agree(tiny_models, dtype):
     """The same span lengths again and again (here: five requests of 40 tokens, each cut 24 + 16):
