@@ -243,6 +243,10 @@ def run_ours(args):
     nums = model_numbers(cfg)
     if args.workload == "mixed":
         return run_mixed(args, cfg)
+    if args.only == "table":
+        return run_table(args)
+    if args.only == "stream":
+        return run_stream_table(cfg)
     with tempfile.TemporaryDirectory(prefix="lfm2_350m_") as d:
         z.write_random_model(cfg, 0, d)
         eng = z.Engine(d, "bfloat16", max_num_seqs=64, max_batched_tokens=2048 + 64, max_model_len=CONTEXT,
@@ -264,7 +268,7 @@ def run_ours(args):
         dev_ms, e2e_ms, ctx_tokens, launches, h2d, d2h, clock_info = time_decode(eng, 8, args.steps, args.warmup, clocks)
         points = {}
         for B in (1, 64):
-            ms, _, _, _, _, _, _ = time_decode(eng, B, max(args.steps // 2, 5), args.warmup)
+            ms, _, _, _, _, _, _ = time_decode(eng, B, max(args.steps // 2, 20), args.warmup)
             points[f"decode_b{B}"] = round(B / ms * 1e3, 1)
     weight_bytes = 2 * (nums["layer_params"] + nums["head_params"])
     step_bytes = weight_bytes + ctx_tokens * nums["kv_bytes_per_token"] + 8 * nums["state_bytes"]
@@ -295,6 +299,58 @@ def run_ours(args):
         "clocks": clock_info,
     }
     print(json.dumps(out))
+    return 0
+
+
+def measure_shape(model, steps, warmup, page_size=64):
+    """Every figure of one model shape: decode at batch 1, 8 and 64 (device-timed and through Engine.step),
+    the prefill of 2048 tokens, each with the bytes or flops it has to move and the fraction of the peak."""
+    import zig_ai_b200 as z
+    from zig_ai_b200.config import config_from_dict
+    hbm_peak, flops_peak, peak_src = peaks()
+    cfg = config_from_dict(shape_config(model))
+    nums = model_numbers(cfg)
+    rows = []
+    with tempfile.TemporaryDirectory(prefix=f"lfm2_{model.replace('.', '_')}_") as d:
+        z.write_random_model(cfg, 0, d)
+        eng = z.Engine(d, "bfloat16", max_num_seqs=64, max_batched_tokens=2048 + 64, max_model_len=CONTEXT,
+                       max_tokens=64 * CONTEXT, page_size=page_size)
+        prefill_ms = time_prefill(eng, reps=max(min(steps, 20), 5))
+        Hq, D = nums["attn_dims"]
+        T = PREFILL_TOKENS
+        flops = 2 * T * nums["layer_params"] + 2 * nums["head_params"] + nums["n_attn"] * 2 * T * T * Hq * D
+        rows.append({"model": model, "point": "prefill 2048", "ms": round(prefill_ms, 3), "tokens_per_s": round(T / prefill_ms * 1e3),
+                     "work": f"{flops / 1e12:.3f} TFLOP", "achieved": f"{flops / prefill_ms / 1e9:.0f} TFLOP/s",
+                     "frac_of_peak": round(flops / (prefill_ms * 1e-3) / (flops_peak * 1e12), 3)})
+        weight_bytes = 2 * (nums["layer_params"] + nums["head_params"])
+        for B in (1, 8, 64):
+            dev_ms, e2e_ms, ctx_tokens, launches, _, _, _ = time_decode(eng, B, max(steps, 20), warmup)
+            step_bytes = weight_bytes + ctx_tokens * nums["kv_bytes_per_token"] + B * nums["state_bytes"]
+            rows.append({"model": model, "point": f"decode batch {B}", "ms": round(dev_ms, 4), "e2e_ms": round(e2e_ms, 4),
+                         "tokens_per_s": round(B / dev_ms * 1e3), "e2e_tokens_per_s": round(B / e2e_ms * 1e3),
+                         "mean_context": round(ctx_tokens / B), "work": f"{step_bytes / 1e9:.3f} GB",
+                         "achieved": f"{step_bytes / dev_ms / 1e6:.0f} GB/s",
+                         "frac_of_peak": round(step_bytes / (dev_ms * 1e-3) / 1e9 / hbm_peak, 3),
+                         "launches_per_step": round(launches)})
+    return rows, peak_src
+
+
+def run_table(args):
+    """The tracked table: every shape BASELINE.json lists, decode at batch 1/8/64 device-timed and end to end,
+    the prefill of 2048 tokens, and the mixed workload of the 700M shape, as JSON lines and as markdown."""
+    hbm_peak, flops_peak, peak_src = peaks()
+    all_rows = []
+    for model in ("350m", "700m", "1.2b"):
+        rows, _ = measure_shape(model, args.steps, args.warmup, args.page_size)
+        for r in rows:
+            print(json.dumps(r), flush=True)
+        all_rows += rows
+    print(f"\npeaks ({peak_src}): {hbm_peak:.0f} GB/s copy bandwidth, {flops_peak:.0f} TFLOP/s bf16 product (burst)\n")
+    print("| shape | point | ms a step (device) | tokens/s (device) | ms a step (end to end) | tokens/s (end to end) | bytes or flops a step | achieved | of the measured peak |")
+    print("|---|---|---|---|---|---|---|---|---|")
+    for r in all_rows:
+        print(f"| LFM2-{r['model'].upper()} | {r['point']} | {r['ms']} | {r['tokens_per_s']} | {r.get('e2e_ms', '')} | "
+              f"{r.get('e2e_tokens_per_s', '')} | {r['work']} | {r['achieved']} | {r['frac_of_peak']} |")
     return 0
 
 
@@ -410,6 +466,71 @@ def run_gemm_table(cfg):
     return 0
 
 
+def run_stream_table(cfg):
+    """The products of a layer at 24, 64 and 128 rows: the weight-streaming tcgen05 kernel of this package
+    (csrc/stream_gemm.cu, with SwiGLU fused where the layer has it) against the library's product (plus the
+    activation kernel), each timed as a CUDA graph of 20 calls that rotate over copies of the weights."""
+    import torch
+    from zig_ai_b200.kernels import ops
+    ops.require()
+    ops.USE_STREAM_GEMM = True
+    H, F = cfg.hidden_size, cfg.ff_dim
+    qkv = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim
+    shapes = [("out_proj", H, H, 0), ("qkv", qkv, H, 0), ("in_proj", 3 * H, H, 0), ("gate_up+swiglu", 2 * F, H, 2), ("down", H, F, 0),
+              ("head", cfg.vocab_size, H, 1)]
+
+    def graph_time(f, reps=20):
+        for _ in range(2):
+            f()
+        torch.cuda.synchronize()
+        g, s = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+        with torch.cuda.stream(s):
+            with torch.cuda.graph(g):
+                ops.begin_forward()
+                for _ in range(reps):
+                    f()
+                ops.end_forward()
+        torch.cuda.synchronize()
+        g.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(5):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / (5 * reps) * 1e3
+
+    for N in (24, 64, 128):
+        for name, O, K, epi in shapes:
+            ws = [torch.randn(O, K).to(torch.bfloat16).cuda() for _ in range(max(2, min(8, int(300e6 // (O * K * 2)))))]
+            x = torch.randn(N, K).to(torch.bfloat16).cuda()
+            it = [0]
+
+            def mine():
+                w = ws[it[0] % len(ws)]
+                it[0] += 1
+                if epi == 2:
+                    ops.linear_swiglu(x, w, O // 2)
+                else:
+                    ops.linear(x, w, torch.float32 if epi == 1 else None)
+
+            def lib():
+                w = ws[it[0] % len(ws)]
+                it[0] += 1
+                if epi == 2:
+                    ops.silu_mul(torch.matmul(x, w.t()), O // 2)
+                elif epi == 1:
+                    torch.mm(x, w.t(), out_dtype=torch.float32)
+                else:
+                    torch.matmul(x, w.t())
+            t1, t2 = graph_time(mine), graph_time(lib)
+            print(json.dumps({"rows": N, "product": name, "O": O, "K": K, "stream_us": round(t1, 2), "library_us": round(t2, 2),
+                              "stream_GBs": round(O * K * 2 / t1 / 1e3)}), flush=True)
+    print(json.dumps({"only": "stream", "status": ops.read_status()}))
+    return 0
+
+
 def run_mixed(args, cfg):
     """64 requests with prompts of 256..2048 random tokens and 256 new tokens each, chunked prefill
     interleaved with decoding, through Engine.step(): tokens per second end to end."""
@@ -450,8 +571,9 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "gemm", "timeline"],
-                    help="profiling aid: run only the batch-8 decode steps or only the prefill (prints a short line)")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "gemm", "timeline", "table", "stream"],
+                    help="profiling aid: run only the batch-8 decode steps or only the prefill (prints a short line); "
+                         "table: every figure of the 350M, 700M and 1.2B shapes (profiles/measurements.md)")
     ap.add_argument("--batch", type=int, default=8, help="with --only decode: the batch size")
     ap.add_argument("--profile-range", action="store_true",
                     help="mark the device-timed decode steps for a profiler (ncu --profile-from-start off)")

@@ -759,3 +759,98 @@ def test_ids_outside_their_bounds_raise_the_status_word_and_touch_nothing():
     # --- and the word is what the step function reads: a raised bit voids the step
     o.status_tensor().fill_(1)
     assert o.tc_status() == 1 and o.read_status() == 0
+
+
+# ----------------------------------------------------------------------------- 17 to 128 rows: the weight-streaming products
+@pytest.fixture
+def stream_gemm_on():
+    """The ops send products of 17 to 128 rows to the weight-streaming kernel (an option, off by default)."""
+    from zig_ai_b200.kernels import ops as o
+    old, o.USE_STREAM_GEMM = o.USE_STREAM_GEMM, True
+    yield
+    o.USE_STREAM_GEMM = old
+
+
+def _stream_call(o, y, w, x, epilogue):
+    fn = o._fn("stream_gemm", "zai_stream_gemm")
+    code = fn(y.data_ptr(), w.data_ptr(), x.data_ptr(), o.status_tensor().data_ptr(), x.shape[0], w.shape[0], w.shape[1], epilogue,
+              torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert code == 0 and o.read_status() == 0, code
+
+
+@pytest.mark.parametrize("rows,ksplit", [(0, 0), (128, 1), (64, 2), (8, 8), (16, 4), (32, 1)])
+@pytest.mark.parametrize("N,O,K", [(17, 128, 64), (64, 1024, 1024), (33, 517, 1000), (128, 1024, 4608), (100, 3072, 1024),
+                                   (24, 96, 96), (65, 256, 136), (32, 65536, 1024), (1, 300, 72), (64, 2048, 1536)])
+def test_stream_gemm_bf16_and_f32(N, O, K, rows, ksplit, stream_gemm_on):
+    """Tiles that end inside the matrix in every direction, K that is no multiple of 64, one 64-k slice
+    only, tiles of 8 to 128 weight rows, K cut across clusters of every size (`rows`, `ksplit`: asked
+    for; 0 leaves the choice to the launcher) and more blocks in a cluster than slices."""
+    o = ops()
+    o._fn("stream_gemm", "zai_stream_force_cluster")(ksplit)
+    o._fn("stream_gemm", "zai_stream_force_rows")(rows)
+    g = torch.Generator().manual_seed(70)
+    x = torch.randn(N, K, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(O, K, generator=g) * K ** -0.5).to(torch.bfloat16).cuda()
+    want = x.float() @ w.float().t()
+    y = torch.full((N, O), float("nan"), dtype=torch.bfloat16, device="cuda")
+    _stream_call(o, y, w, x, 0)
+    assert torch.allclose(y.float(), want, atol=2e-2, rtol=2e-2)
+    y32 = torch.full((N, O), float("nan"), dtype=torch.float32, device="cuda")
+    _stream_call(o, y32, w, x, 1)
+    assert torch.allclose(y32, want, atol=2e-3, rtol=2e-3)
+    o._fn("stream_gemm", "zai_stream_force_cluster")(0)
+    o._fn("stream_gemm", "zai_stream_force_rows")(0)
+    if 17 <= N:
+        before = o.launches
+        assert torch.allclose(o.linear(x, w).float(), want, atol=2e-2, rtol=2e-2) and o.launches == before + 1
+
+
+@pytest.mark.parametrize("rows", [0, 64, 8])
+@pytest.mark.parametrize("N,F,K", [(17, 64, 64), (64, 4608, 1024), (40, 100, 96), (128, 1000, 520), (96, 8192, 2048)])
+def test_stream_gemm_swiglu(N, F, K, rows, stream_gemm_on):
+    o = ops()
+    o._fn("stream_gemm", "zai_stream_force_rows")(rows)
+    g = torch.Generator().manual_seed(71)
+    x = torch.randn(N, K, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(2 * F, K, generator=g) * K ** -0.5).to(torch.bfloat16).cuda()
+    gu = x.float() @ w.float().t()
+    want = torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]
+    y = torch.full((N, F), float("nan"), dtype=torch.bfloat16, device="cuda")
+    _stream_call(o, y, w, x, 2)
+    o._fn("stream_gemm", "zai_stream_force_rows")(0)
+    assert torch.allclose(y.float(), want, atol=3e-2, rtol=3e-2)
+    before = o.launches
+    assert torch.allclose(o.linear_swiglu(x, w, F).float(), want, atol=3e-2, rtol=3e-2) and o.launches == before + 1
+
+
+@pytest.mark.parametrize("rows", [0, 32, 8])
+@pytest.mark.parametrize("M,C,K,L,bias", [(17, 64, 128, 3, False), (64, 1024, 1024, 3, False), (40, 200, 96, 4, True),
+                                          (128, 96, 520, 2, True), (33, 48, 64, 1, False), (100, 2048, 2048, 3, False)])
+def test_stream_gemm_short_conv_epilogue(M, C, K, L, bias, rows, stream_gemm_on):
+    """The short convolution as the input projection's epilogue for 17 to 128 single tokens: against the
+    plain product followed by the plain convolution, twice in a row (the state moves on), with slots in
+    another order than the rows, and once without writing the state."""
+    o = ops()
+    g = torch.Generator().manual_seed(72)
+    w_in = (torch.randn(3 * C, K, generator=g) * K ** -0.5).to(torch.bfloat16).cuda()
+    conv_w = (torch.randn(C, L, generator=g) * 0.3).cuda()
+    conv_b = (torch.randn(C, generator=g) * 0.3).cuda() if bias else None
+    rows = max(L - 1, 1)
+    slots = list(range(1, M + 1))
+    random.Random(73).shuffle(slots)
+    state_a = torch.randn(M + 3, rows, C, generator=g).cuda()
+    state_b = state_a.clone()
+    step = make_step(o, torch.bfloat16, [3] * M, [1] * M, 16, 2 * M + 2, 74, slots=slots)
+    o._fn("stream_gemm", "zai_stream_force_rows")(rows)
+    for rep, write in enumerate((True, True, False)):
+        x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+        before = o.launches
+        za = o.linear_short_conv(x, w_in, conv_w, conv_b, state_a, step, L, write)
+        assert o.launches == before + 1
+        bcx = (x.float() @ w_in.float().t()).to(torch.bfloat16)
+        zb = ref_ops.short_conv(bcx, conv_w, conv_b, state_b, step, L, write)
+        assert torch.allclose(za.float(), zb.float(), atol=3e-2, rtol=3e-2), rep
+        assert torch.allclose(state_a, state_b, atol=2e-2, rtol=2e-2), rep
+    o._fn("stream_gemm", "zai_stream_force_rows")(0)
+    assert torch.equal(state_a[0], state_b[0]) and o.read_status() == 0

@@ -54,6 +54,14 @@ _SIGNATURES = {
         "zai_skinny_gemm": [_P, _P, _P, _P, _P, _P, _P, _P, _F, _I, _I, _I, _I, _P],
         "zai_skinny_conv": [_P, _P, _P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     },
+    "stream_gemm": {
+        "zai_stream_gemm_supports": [_I, _I, _I, _I],
+        "zai_stream_force_cluster": [_I],
+        "zai_stream_force_rows": [_I],
+        "zai_stream_debug": [_P],
+        "zai_stream_gemm": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
+        "zai_stream_conv": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    },
     "gemm_tc": {
         "zai_gemm_tc_supports": [_I, _I, _I, _I],
         "zai_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
@@ -128,6 +136,8 @@ def require(dtype=None) -> None:
             libs.append("gemm_tc")
         if dtype is None or USE_PAIR_GEMM:
             libs.append("gemm_tc_pair")
+        if dtype is None or USE_STREAM_GEMM:
+            libs.append("stream_gemm")
     build.build_some(libs, verbose=True)
     for lib in libs:
         build.load(lib)
@@ -214,6 +224,7 @@ def end_forward() -> None:
 
 def _stream():
     return _stream_handle if _stream_handle is not None else torch.cuda.current_stream().cuda_stream
+
 
 
 def _cuda(*tensors):
@@ -415,6 +426,30 @@ def _tensor_core(x, w, epilogue, out_cols, out_dtype):
     return y
 
 
+# Steps of 17 to 128 rows: the weight-streaming tcgen05 kernel (csrc/stream_gemm.cu), with SwiGLU or the
+# short convolution as its epilogue.  Measured on B200 it is behind the library's product plus the
+# separate activation / convolution kernel at every shape of the LFM2 models but the head (a block's
+# K loop is bound by issuing its tcgen05.mma and waiting on its mbarriers, about 0.4 us per 64-k slice:
+# see profiles/stream_gemm_tcgen05_17_128_rows.md), so it is an option: ZAI_STREAM_GEMM=1 turns it on.
+USE_STREAM_GEMM = os.environ.get("ZAI_STREAM_GEMM", "0") == "1"
+STREAM_MIN_ROWS, STREAM_MAX_ROWS = 17, 128
+
+
+@_timed(_product_class)
+def _stream_product(x, w, epilogue, out_cols, out_dtype):
+    """The weight-streaming product kernel, if it takes these operands; else None."""
+    N, (O, K) = x.shape[0], w.shape
+    if (not USE_STREAM_GEMM or not STREAM_MIN_ROWS <= N <= STREAM_MAX_ROWS or w.dtype != torch.bfloat16
+            or x.dtype != torch.bfloat16 or not x.is_contiguous() or not w.is_contiguous()):
+        return None
+    if not _fn("stream_gemm", "zai_stream_gemm_supports")(N, O, K, epilogue):
+        return None
+    y = torch.empty((N, out_cols), dtype=out_dtype, device=w.device)
+    _check(_fn("stream_gemm", "zai_stream_gemm")(_ptr(y), _ptr(w), _ptr(x), _status_ptr(w.device), N, O, K, epilogue,
+                                                 _stream()), "stream_gemm")
+    return y
+
+
 def linear(x, w, out_dtype=None):
     """x [N, K] times w [O, K] transposed.  x may be a LazyNorm.  Few rows in bfloat16 go to the
     fused few-rows kernel, many rows to the tcgen05 kernel where it is the faster one; a matrix kept
@@ -428,7 +463,10 @@ def linear(x, w, out_dtype=None):
     if isinstance(x, LazyNorm):
         x = x.materialize(sys.modules[__name__])
     if x.dtype == torch.bfloat16 and out_dtype in (torch.bfloat16, torch.float32):
-        y = _tensor_core(x, w, _EPI_F32 if out_dtype == torch.float32 else _EPI_BF16, w.shape[0], out_dtype)
+        epi = _EPI_F32 if out_dtype == torch.float32 else _EPI_BF16
+        y = _stream_product(x, w, epi, w.shape[0], out_dtype)
+        if y is None:
+            y = _tensor_core(x, w, epi, w.shape[0], out_dtype)
         if y is not None:
             return y
     return _library_product(x, w, out_dtype)
@@ -479,7 +517,9 @@ def linear_swiglu(x, w_gate_up, ff_dim):
             return y
         if isinstance(x, LazyNorm):
             x = x.materialize(sys.modules[__name__])
-        y = _tensor_core(x, w_gate_up, _EPI_SWIGLU, ff_dim, torch.bfloat16)
+        y = _stream_product(x, w_gate_up, _EPI_SWIGLU, ff_dim, torch.bfloat16)
+        if y is None:
+            y = _tensor_core(x, w_gate_up, _EPI_SWIGLU, ff_dim, torch.bfloat16)
         if y is not None:
             return y
         if USE_PAIR_GEMM and x.shape[0] >= PAIR_SWIGLU_MIN_ROWS:
@@ -515,8 +555,25 @@ def linear_short_conv(x, w_in, conv_w, conv_b, state, step, taps, write_state=Tr
              and (not lazy or x.rows is None) and state.dtype == torch.float32 and state.shape[-1] == C
              and M == step.n_seqs and _fn("decode_gemm", "zai_skinny_gemm_supports")(M, O, K, _EPI_CONV, int(lazy)))
     if not fused:
+        if (USE_STREAM_GEMM and step.decode_only and STREAM_MIN_ROWS <= M <= STREAM_MAX_ROWS and M == step.n_seqs
+                and taps <= FUSED_CONV_MAX_TAPS and w_in.dtype == torch.bfloat16 and x.dtype == torch.bfloat16
+                and (not lazy or x.rows is None) and state.dtype == torch.float32 and state.shape[-1] == C and w_in.is_contiguous()
+                and _fn("stream_gemm", "zai_stream_gemm_supports")(M, O, K, _EPI_CONV)):
+            if lazy:
+                x = x.materialize(sys.modules[__name__])
+            return _stream_conv(x, w_in, conv_w, conv_b, state, step, taps, write_state, M, C, K)
         return short_conv(linear(x, w_in), conv_w, conv_b, state, step, taps, write_state)
     return _skinny_conv(x, w_in, conv_w, conv_b, state, step, taps, write_state, lazy, M, C, K)
+
+
+@_timed("products (in_proj + conv)")
+def _stream_conv(x, w_in, conv_w, conv_b, state, step, taps, write_state, M, C, K):
+    _cuda(x, w_in, conv_w, conv_b, state)
+    z = torch.empty((M, C), dtype=torch.bfloat16, device=w_in.device)
+    _check(_fn("stream_gemm", "zai_stream_conv")(
+        _ptr(z), _ptr(w_in), _ptr(x), _status_ptr(w_in.device), _ptr(conv_w), _ptr(conv_b), _ptr(state), _ptr(step.slot_ids),
+        M, C, K, int(taps), state.shape[1], int(bool(write_state)), state.shape[0], _stream()), "stream_conv")
+    return z
 
 
 @_timed("products (in_proj + conv)")
