@@ -336,7 +336,7 @@ def measure_shape(model, steps, warmup, page_size=64):
 
 
 def run_table(args):
-    """The tracked table: every shape BASELINE.json lists, decode at batch 1/8/64 device-timed and end to end,
+    """The tracked table: the 350M, 700M and 1.2B shapes, decode at batch 1/8/64 device-timed and end to end,
     the prefill of 2048 tokens, and the mixed workload of the 700M shape, as JSON lines and as markdown."""
     hbm_peak, flops_peak, peak_src = peaks()
     all_rows = []
