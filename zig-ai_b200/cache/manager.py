@@ -50,6 +50,7 @@ class RequestCache:
     slot: int
     tables: Dict[int, List[int]]          # group index -> physical page per logical page (RELEASED if given back)
     num_tokens: int = 0                   # positions whose pages are reserved
+    capacity: int = 0                     # positions that the pages held in every group cover
 
 
 @dataclass
@@ -164,6 +165,18 @@ class CacheManager:
             self._rows[gi] = rows = grown
         rows[slot, j] = page
 
+    def try_reserve(self, request_id, total_tokens: int) -> bool:
+        """`reserve` if it is possible, in one call; False (and nothing taken) if pages are short.  The
+        common case, a decoded token inside the request's last page, is a comparison."""
+        rc = self.requests[request_id]
+        if not self._has_window and rc.num_tokens <= total_tokens <= rc.capacity:
+            rc.num_tokens = total_tokens
+            return True
+        if not self.can_reserve(request_id, total_tokens):
+            return False
+        self.reserve(request_id, total_tokens)
+        return True
+
     def can_reserve(self, request_id, total_tokens: int) -> bool:
         if self._fits_already(self.requests[request_id], total_tokens):
             return True
@@ -183,6 +196,7 @@ class CacheManager:
             if not grp.paged and grp.data is not None:
                 grp.data[:, slot].zero_()
         rc = RequestCache(request_id, slot, {gi: [] for gi in self.paged_groups()})
+        rc.capacity = 0 if rc.tables else 1 << 40
         self.requests[request_id] = rc
         return rc
 
@@ -218,6 +232,7 @@ class CacheManager:
                 self._set_row(gi, rc.slot, len(table), p)
                 table.append(p)
         rc.num_tokens = total_tokens
+        rc.capacity = min((len(t) for t in rc.tables.values()), default=1 << 40) * self.page_size
 
     def release(self, request_id) -> None:
         """Give back everything the request holds."""

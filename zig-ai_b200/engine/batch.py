@@ -61,14 +61,16 @@ def pack_host(spans, tables: Dict[int, "np.ndarray"], widths: Dict[int, int] = N
     `spans` is a list of (request_id, ctx_len, tokens, wanted offsets, slot); `widths` fixes the
     table widths (a captured graph needs them constant), default: as wide as the tables given."""
     S = len(spans)
-    tok, pos, sidx, cu, ctx, slots, rows, q_lens, rids = [], [], [], [0], [], [], [], [], []
+    ctx, slots, rows, q_lens, rids = [], [], [], [], []
+    single_at, single_tok, longer = [], [], []     # one-token spans are gathered and written in one go
     at = 0
-    for s, (rid, c, tokens, want, slot) in enumerate(spans):
+    for rid, c, tokens, want, slot in spans:
         n = len(tokens)
-        tok.append(np.asarray(tokens, dtype=np.int32))
-        pos.append(np.arange(c, c + n, dtype=np.int32))
-        sidx.append(np.full(n, s, dtype=np.int32))
-        cu.append(at + n)
+        if n == 1:
+            single_at.append(at)
+            single_tok.append(tokens[0])
+        elif n:
+            longer.append((at, tokens))
         ctx.append(c)
         slots.append(slot)
         q_lens.append(n)
@@ -78,6 +80,20 @@ def pack_host(spans, tables: Dict[int, "np.ndarray"], widths: Dict[int, int] = N
                 raise ValueError(f"wanted place {w} is outside the {n} tokens of request {rid!r}")
             rows.append(at + w)
         at += n
+    tok_all = np.empty(at, dtype=np.int32)
+    if single_at:
+        tok_all[single_at] = single_tok
+    for a0, tokens in longer:
+        tok_all[a0:a0 + len(tokens)] = tokens
+    # positions and the rows' requests for all spans at once: row i of span s lies at ctx[s] + i
+    lens = np.asarray(q_lens, dtype=np.int64)
+    starts = np.zeros(S + 1, dtype=np.int64)
+    np.cumsum(lens, out=starts[1:])
+    sidx_all = np.repeat(np.arange(S, dtype=np.int32), lens)
+    pos_all = (np.arange(at, dtype=np.int64) - np.repeat(starts[:-1], lens) + np.repeat(np.asarray(ctx, dtype=np.int64), lens)).astype(np.int32)
+    tok = [tok_all] if at else []
+    pos, sidx = ([pos_all], [sidx_all]) if at else ([], [])
+    cu = starts.tolist()
     rows += [0] * max(pad_wanted - len(rows), 0)              # (`pad_wanted`: the wanted rows are filled up with row 0)
     parts = tok + pos + sidx + [np.array(cu + ctx + slots + rows, dtype=np.int32)]
     N, R = at, len(rows)

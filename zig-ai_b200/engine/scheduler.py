@@ -131,10 +131,7 @@ class Scheduler:
 
     # ------------------------------------------------------------------ planning
     def _try_reserve(self, req: Request, n: int) -> bool:
-        if not self.cache.can_reserve(req.request_id, req.computed + n):
-            return False
-        self.cache.reserve(req.request_id, req.computed + n)
-        return True
+        return self.cache.try_reserve(req.request_id, req.computed + n)
 
     def _preempt(self, victim: Request, plan: StepPlan) -> None:
         self.owner.release(victim.request_id)
