@@ -246,7 +246,7 @@ def run_ours(args):
     if args.only == "table":
         return run_table(args)
     if args.only == "stream":
-        return run_stream_table(cfg)
+        return run_stream_table(cfg, args.batch)
     with tempfile.TemporaryDirectory(prefix="lfm2_350m_") as d:
         z.write_random_model(cfg, 0, d)
         eng = z.Engine(d, "bfloat16", max_num_seqs=64, max_batched_tokens=2048 + 64, max_model_len=CONTEXT,
@@ -466,7 +466,7 @@ def run_gemm_table(cfg):
     return 0
 
 
-def run_stream_table(cfg):
+def run_stream_table(cfg, only_rows=0):
     """The products of a layer at 24, 64 and 128 rows: the weight-streaming tcgen05 kernel of this package
     (csrc/stream_gemm.cu, with SwiGLU fused where the layer has it) against the library's product (plus the
     activation kernel), each timed as a CUDA graph of 20 calls that rotate over copies of the weights."""
@@ -501,7 +501,7 @@ def run_stream_table(cfg):
         torch.cuda.synchronize()
         return a.elapsed_time(b) / (5 * reps) * 1e3
 
-    for N in (24, 64, 128):
+    for N in ((only_rows,) if only_rows in (24, 64, 128) else (24, 64, 128)):
         for name, O, K, epi in shapes:
             ws = [torch.randn(O, K).to(torch.bfloat16).cuda() for _ in range(max(2, min(8, int(300e6 // (O * K * 2)))))]
             x = torch.randn(N, K).to(torch.bfloat16).cuda()
@@ -574,7 +574,8 @@ def main():
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "gemm", "timeline", "table", "stream"],
                     help="profiling aid: run only the batch-8 decode steps or only the prefill (prints a short line); "
                          "table: every figure of the 350M, 700M and 1.2B shapes (profiles/measurements.md)")
-    ap.add_argument("--batch", type=int, default=8, help="with --only decode: the batch size")
+    ap.add_argument("--batch", type=int, default=8, help="with --only decode: the batch size; with --only stream: 24, 64 or "
+                                                         "128 runs that row count only")
     ap.add_argument("--profile-range", action="store_true",
                     help="mark the device-timed decode steps for a profiler (ncu --profile-from-start off)")
     ap.add_argument("--page-size", type=int, default=64, help="positions per cache page")

@@ -314,3 +314,29 @@ def test_a_step_ahead_with_preemptions(tiny_models):
     got, st1 = run(True)
     assert got == base and all(len(o) == 24 for o in got)
     assert st0["preemptions"] > 0 and st1["preemptions"] > 0 and st1["steps_ahead"] > 0
+
+
+@pytest.mark.parametrize("name", ["B", "C"])
+def test_preemption_and_recomputation_in_bfloat16_pick_plain_maxima(tiny_models, name):
+    """In bfloat16, with so few pages that running requests are preempted and recomputed from their prompt
+    and the tokens they had produced: every request still gets all its tokens, and every greedy token is
+    within the bfloat16 tolerance of the plain implementation's best logit at its place (a recomputed
+    request runs its old tokens as a prompt portion, through other kernels than when it decoded them)."""
+    import zig_ai_b200 as z
+    g = random.Random(14)
+    V = TINY[name][0]["vocab_size"]
+    ps = PAGE_SIZE[name]
+    prompts = [[g.randrange(V) for _ in range(n)] for n in (2 * ps + 3, ps + 1, 2 * ps - 1, ps // 2 + 1)]
+    new = ps + 5
+    eng = z.Engine(tiny_models[name], "bfloat16", max_num_seqs=4, max_batched_tokens=3 * ps, max_model_len=4 * ps + 16,
+                   max_tokens=9 * ps, page_size=ps)
+    got = eng.generate(prompts, max_new_tokens=new, temperature=0.0)
+    st = eng.stats()
+    assert st["preemptions"] > 0 and all(len(o) == new for o in got)
+    assert all(v == 0 for k, v in st.items() if k.endswith("_pages_used")) and st["slots_used"] == 0
+    c, W = plain_lfm2.read_config(tiny_models[name]), plain_lfm2.read_weights(tiny_models[name])
+    for p, out in zip(prompts, got):
+        logits = plain_lfm2.forward(c, W, p + out)
+        for i, tok in enumerate(out):
+            row = logits[len(p) + i - 1]
+            assert float(row.max() - row[tok]) <= 8e-2 * float(row.abs().max()), (i, tok)
