@@ -84,10 +84,13 @@ __device__ __forceinline__ MaxIdx scan_row(const float* __restrict__ row, int V)
     return x;
 }
 
-__global__ void argmax_kernel(int* __restrict__ out, const float* __restrict__ logits, int V) {
+// `status`, if given, is the step's status word: block 0 copies it behind the R token ids (out[R]), so that one
+// copy to the host brings both.
+__global__ void argmax_kernel(int* __restrict__ out, const float* __restrict__ logits, int V, const int* __restrict__ status) {
     __shared__ MaxIdx red[33];
     pdl_trigger();
     pdl_wait();
+    if (status && blockIdx.x == 0 && threadIdx.x == 0) out[gridDim.x] = *status;
     const float* row = logits + (size_t)blockIdx.x * V;
     MaxIdx x = scan_row(row, V);
     x = block_argmax(x, red);
@@ -113,13 +116,15 @@ __global__ void repetition_penalty_kernel(float* __restrict__ logits, const int*
 
 __global__ void sample_kernel(int* __restrict__ out, const float* __restrict__ logits,
                               const float* __restrict__ temperature, const int* __restrict__ top_k,
-                              const float* __restrict__ top_p, const float* __restrict__ uniform, int V) {
+                              const float* __restrict__ top_p, const float* __restrict__ uniform, int V,
+                              const int* __restrict__ status) {
     __shared__ MaxIdx redm[33];
     __shared__ float red[33];
     __shared__ float scan[SAMPLE_THREADS];
     __shared__ int chosen;
     pdl_trigger();
     pdl_wait();
+    if (status && blockIdx.x == 0 && threadIdx.x == 0) out[gridDim.x] = *status;
     const int r = blockIdx.x, tid = threadIdx.x;
     const float* row = logits + (size_t)r * V;
     const float T = temperature[r];
@@ -229,9 +234,10 @@ __global__ void sample_kernel(int* __restrict__ out, const float* __restrict__ l
     }
 }
 
-ZAI_API int zai_argmax(int* out, const float* logits, int R, int V, cudaStream_t stream) {
+// out holds R ids, and the status word behind them if `status` is given (R + 1 ints then).
+ZAI_API int zai_argmax(int* out, const float* logits, int R, int V, const int* status, cudaStream_t stream) {
     if (R <= 0) return ZAI_OK;
-    return launch_pdl(argmax_kernel, dim3(R), dim3(1024), 0, stream, out, logits, V);
+    return launch_pdl(argmax_kernel, dim3(R), dim3(1024), 0, stream, out, logits, V, status);
 }
 
 ZAI_API int zai_repetition_penalty(float* logits, const int* tokens, const int* counts, const int* offsets,
@@ -242,7 +248,8 @@ ZAI_API int zai_repetition_penalty(float* logits, const int* tokens, const int* 
 }
 
 ZAI_API int zai_sample(int* out, const float* logits, const float* temperature, const int* top_k, const float* top_p,
-                       const float* uniform, int R, int V, cudaStream_t stream) {
+                       const float* uniform, int R, int V, const int* status, cudaStream_t stream) {
     if (R <= 0) return ZAI_OK;
-    return launch_pdl(sample_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, stream, out, logits, temperature, top_k, top_p, uniform, V);
+    return launch_pdl(sample_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, stream, out, logits, temperature, top_k, top_p, uniform, V,
+                      status);
 }

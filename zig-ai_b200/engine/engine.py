@@ -93,10 +93,10 @@ class Engine:
         number = self.runner.steps - 1
         wanting = [e.request for e in plan.entries if e.sample]
         ahead = 1 if device_tokens is not None else 0         # one token of each output is still on the device
+        on_device = logits.device.type == "cuda"
+        n = len(wanting)
         ids = self.sampler.sample_device(logits, [r.params for r in wanting], [len(r.output) + ahead for r in wanting],
-                                         [r.output for r in wanting])
-        # the copy to the host is queued now, before any later step's kernels, so that reading it
-        # waits for this step only
+                                         [r.output for r in wanting], with_status=on_device and n > 0)
         if self.profile:
             kind = "decode steps" if all(len(e.tokens) == 1 for e in plan.entries) else "steps with prompt portions"
             acc = self._profile.setdefault(kind, {"steps": 0, "tokens": 0})
@@ -104,10 +104,12 @@ class Engine:
             acc["tokens"] += plan.n_tokens
             for name, ms in self.runner.ops.profile_end().items():
                 acc[name] = acc.get(name, 0.0) + ms
-        # the kernels' status word rides along, behind the ids in the same pinned buffer
+        # The kernels' status word comes with the ids: the sampling kernel put it behind them (n + 1 ints, one
+        # copy); the copy to the host is queued now, before any later step's kernels, so that reading it
+        # waits for this step only
         status = getattr(self.runner.ops, "status_tensor", None)
         status = status(self.runner.device) if status else None
-        if ids.device.type != "cuda":
+        if not on_device:
             host = torch.cat([ids.to(torch.int32), status.to(torch.int32)]) if status is not None else ids
             if status is not None:
                 status.zero_()
@@ -117,11 +119,13 @@ class Engine:
                               for _ in range(4)]
         host = self._host_ids[self._host_turn % len(self._host_ids)]
         self._host_turn += 1
-        n = int(ids.shape[0])
         if n + 1 > host.shape[0]:
             host = torch.empty((n + 1,), dtype=torch.int32).pin_memory()
-        host[:n].copy_(ids, non_blocking=True)
-        host[n:n + 1].copy_(status, non_blocking=True)
+        if n > 0:
+            host[:n + 1].copy_(ids, non_blocking=True)
+            ids = ids[:n]
+        else:
+            host[:1].copy_(status, non_blocking=True)
         done = torch.cuda.Event()
         done.record()
         return plan, wanting, ids, host, done, number

@@ -80,9 +80,9 @@ _SIGNATURES = {
         "zai_prefill_attention_tc": [_P, _P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     },
     "sampling": {
-        "zai_argmax": [_P, _P, _I, _I, _P],
+        "zai_argmax": [_P, _P, _I, _I, _P, _P],
         "zai_repetition_penalty": [_P, _P, _P, _P, _P, _I, _I, _P],
-        "zai_sample": [_P, _P, _P, _P, _P, _P, _I, _I, _P],
+        "zai_sample": [_P, _P, _P, _P, _P, _P, _I, _I, _P, _P],
     },
 }
 
@@ -788,11 +788,14 @@ def decode_attention_fused(qkv, q_w, k_w, eps, rotary_dim, theta, step, cache, h
 
 
 @_timed("sampling")
-def argmax(logits):
+def argmax(logits, with_status=False):
+    """First index of each row's maximum, int32 [R]; `with_status`: [R + 1], the device's status word behind
+    the ids (one copy to the host then brings both)."""
     _cuda(logits)
     R, V = logits.shape
-    out = torch.empty((R,), dtype=torch.int32, device=logits.device)
-    _check(_fn("sampling", "zai_argmax")(_ptr(out), _ptr(logits), R, V, _stream()), "argmax")
+    out = torch.empty((R + (1 if with_status else 0),), dtype=torch.int32, device=logits.device)
+    _check(_fn("sampling", "zai_argmax")(_ptr(out), _ptr(logits), R, V,
+                                         _status_ptr(logits.device) if with_status else None, _stream()), "argmax")
     return out
 
 
@@ -807,10 +810,10 @@ def repetition_penalty(logits, tokens, counts, offsets, penalty):
 
 
 @_timed("sampling")
-def sample(logits, temperature, top_k, top_p, u):
+def sample(logits, temperature, top_k, top_p, u, with_status=False):
     _cuda(logits, temperature, top_k, top_p, u)
     R, V = logits.shape
-    out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    out = torch.empty((R + (1 if with_status else 0),), dtype=torch.int32, device=logits.device)
     _check(_fn("sampling", "zai_sample")(_ptr(out), _ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p),
-                                         _ptr(u), R, V, _stream()), "sample")
+                                         _ptr(u), R, V, _status_ptr(logits.device) if with_status else None, _stream()), "sample")
     return out

@@ -72,8 +72,9 @@ class Sampler:
         return self.sample_device(logits, params, indices, histories).tolist()
 
     def sample_device(self, logits: torch.Tensor, params: Sequence[SamplingParams], indices: Sequence[int],
-                      histories: Sequence[Sequence[int]]) -> torch.Tensor:
-        """As `sample`, but the token ids stay on the device (int32 [rows]); nothing waits for them."""
+                      histories: Sequence[Sequence[int]], with_status: bool = False) -> torch.Tensor:
+        """As `sample`, but the token ids stay on the device (int32 [rows]); nothing waits for them.
+        `with_status` (kernels that keep a status word only): [rows + 1], the status word behind the ids."""
         R = logits.shape[0]
         if R == 0:
             return torch.empty((0,), dtype=torch.int32, device=self.device)
@@ -93,13 +94,14 @@ class Sampler:
                     torch.tensor(counts, dtype=torch.int32, device=dev),
                     torch.tensor(offsets, dtype=torch.int32, device=dev),
                     torch.tensor(pens, dtype=torch.float32, device=dev))
+        extra = {"with_status": True} if with_status else {}
         if all(p.greedy for p in params):
-            ids = self.ops.argmax(logits)
+            ids = self.ops.argmax(logits, **extra)
         else:
             dev = self.device
             temperature = torch.tensor([p.temperature for p in params], dtype=torch.float32, device=dev)
             top_k = torch.tensor([p.top_k for p in params], dtype=torch.int32, device=dev)
             top_p = torch.tensor([p.top_p for p in params], dtype=torch.float32, device=dev)
             u = torch.tensor([uniform(p.seed, i) for p, i in zip(params, indices)], dtype=torch.float32, device=dev)
-            ids = self.ops.sample(logits, temperature, top_k, top_p, u)
+            ids = self.ops.sample(logits, temperature, top_k, top_p, u, **extra)
         return ids
