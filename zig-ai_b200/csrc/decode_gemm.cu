@@ -220,17 +220,22 @@ __global__ void __launch_bounds__(SG_WARPS * 32, 2) skinny_gemm_kernel(const Ski
         cv_b = (vc && a.conv_b) ? a.conv_b[ch] : 0.f;
 #pragma unroll
         for (int j = 0; j < SG_CONV_TAPS; ++j) cv_w[j] = (vc && j < a.taps) ? a.conv_w[(size_t)ch * a.taps + j] : 0.f;
+        bool bad_slot = false;                                // (raised once, below: no atomic in the unrolled loops)
 #pragma unroll
         for (int nt = 0; nt < (EPI == EPI_CONV ? MT : 1); ++nt)
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int tok = nt * 8 + 2 * t + e;
-                cv_slot[nt][e] = tok < a.M ? zai_checked_slot(a.slot_ids[tok], a.num_slots, a.status) : 0;
+                const int slot = tok < a.M ? a.slot_ids[tok] : 0;
+                const bool bad = (unsigned)slot >= (unsigned)a.num_slots;     // outside the slots: slot 0, and the step is void
+                bad_slot |= bad;
+                cv_slot[nt][e] = bad ? 0 : slot;
 #pragma unroll
                 for (int j = 0; j < SG_CONV_TAPS - 1; ++j)
                     cv_prev[nt][e][j] = (vc && tok < a.M && j < a.taps - 1)
                         ? a.conv_state[((size_t)cv_slot[nt][e] * a.state_rows + j) * a.F + ch] : 0.f;
             }
+        if (bad_slot) zai_raise(a.status, ZAI_ST_SLOT);
     };
     // the norm's weight and the rows' source indices are written by no kernel of the step: they are
     // fetched before the wait, the weight into shared memory
