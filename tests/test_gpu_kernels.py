@@ -58,7 +58,8 @@ def test_embed_and_gather(dtype, N, H, V):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("N,H,eps", [(5, 96, 1e-6), (3, 1000, 1e-5), (17, 4104, 1e-3), (1, 64, 1e-5),
-                                     (70, 1024, 1e-5), (100, 1000, 1e-6), (65, 2048, 1e-5), (64, 1540, 1e-3), (300, 96, 1e-5)])
+                                     (70, 1024, 1e-5), (100, 1000, 1e-6), (65, 2048, 1e-5), (64, 1540, 1e-3), (300, 96, 1e-5),
+                                     (600, 1024, 1e-5), (513, 1000, 1e-6), (2048, 2048, 1e-5), (519, 1536, 1e-3), (512, 4, 1e-5)])
 def test_add_rmsnorm(dtype, N, H, eps):
     o = ops()
     g = torch.Generator().manual_seed(2)
