@@ -205,7 +205,7 @@ def time_decode(eng, B, steps, warmup, clocks=None):
     width = next(iter(runner.graphs.widths.values())) if runner.graphs else 0
     bucket = runner.graphs.bucket(B) if runner.graphs else B
     h2d = 4 * (3 * bucket + (bucket + 1) + 3 * bucket + bucket * width)
-    d2h = 4 * B
+    d2h = 4 * (B + 1)                        # the token ids and the kernels' status word behind them
     return dev_ms, e2e_ms, ctx_tokens, launches, h2d, d2h, clock_info
 
 
