@@ -855,3 +855,29 @@ def test_stream_gemm_short_conv_epilogue(M, C, K, L, bias, rows, stream_gemm_on)
         assert torch.allclose(state_a, state_b, atol=2e-2, rtol=2e-2), rep
     o._fn("stream_gemm", "zai_stream_force_rows")(0)
     assert torch.equal(state_a[0], state_b[0]) and o.read_status() == 0
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,ps,qk_norm", [(16, 8, 64, 64, True), (4, 2, 16, 16, True), (3, 1, 32, 8, False), (2, 1, 128, 16, True),
+                                                  (3, 3, 256, 8, True)])
+def test_qk_norm_rope_many_rows(Hq, Hkv, D, ps, qk_norm):
+    """From 256 rows on the bfloat16 kernel works with 16-byte accesses: spans of hundreds of rows that
+    start inside pages, against the plain version, pages included."""
+    o = ops()
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(16)
+    ctx, q_lens = [0, ps - 1, 3 * ps, 100], [300, 2, 1, 45]
+    num_pages = sum(-(-(c + n) // ps) for c, n in zip(ctx, q_lens)) + 4
+    step = make_step(o, dtype, ctx, q_lens, ps, num_pages, 17)
+    N = sum(q_lens)
+    qkv = torch.randn(N, (Hq + 2 * Hkv) * D, generator=g).to(dtype).cuda()
+    qw = (1 + 0.1 * torch.randn(D, generator=g)).cuda() if qk_norm else None
+    kw = (1 + 0.1 * torch.randn(D, generator=g)).cuda() if qk_norm else None
+    pages_a = torch.zeros(num_pages, 2, Hkv, ps, D, dtype=dtype, device="cuda")
+    pages_b = pages_a.clone()
+    va, vb = CacheView(0, pages_a, step.block_tables[0], ps), CacheView(0, pages_b, step.block_tables[0], ps)
+    qa, ka = o.qk_norm_rope(qkv, qw, kw, 1e-5, D, 10000.0, step, va, Hq, Hkv, D, True, True, True)
+    qb, kb = ref_ops.qk_norm_rope(qkv, qw, kw, 1e-5, D, 10000.0, step, vb, Hq, Hkv, D, True, True, True)
+    assert torch.allclose(qa.float(), qb.float(), **tol(dtype))
+    assert torch.allclose(ka.float(), kb.float(), **tol(dtype))
+    assert torch.allclose(pages_a.float(), pages_b.float(), **tol(dtype))
+    assert pages_a[0].abs().sum() == 0 and o.read_status() == 0

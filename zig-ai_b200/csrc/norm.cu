@@ -92,62 +92,11 @@ __global__ void __launch_bounds__(256) add_rmsnorm_vec_kernel(float* __restrict_
     }
 }
 
-// Many rows: a warp takes a row of up to 128 * NV values and asks for all of it (NV 16-byte loads of h and
-// of delta per lane) before it uses the first; the sum of squares needs shuffles only, no block barrier.
-// The order of the additions depends on the row width alone, as above.
-template <typename T, int NV>
-__global__ void __launch_bounds__(256) add_rmsnorm_warp_kernel(float* __restrict__ h, const T* __restrict__ delta,
-                                                               const float* __restrict__ gamma, T* __restrict__ out,
-                                                               float eps, int N, int H) {
-    pdl_trigger();
-    pdl_wait();
-    const int lane = threadIdx.x & 31;
-    const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (row >= N) return;
-    const size_t base = (size_t)row * H;
-    float4 v[NV];
-    float d[NV][4];
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-        const int c = (i * 32 + lane) * 4;
-        v[i] = c < H ? *reinterpret_cast<const float4*>(h + base + c) : make_float4(0.f, 0.f, 0.f, 0.f);
-        if (delta && c < H) load4(delta + base + c, d[i]);
-    }
-    float ss = 0.f;
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-        const int c = (i * 32 + lane) * 4;
-        if (delta && c < H) {
-            v[i].x += d[i][0];
-            v[i].y += d[i][1];
-            v[i].z += d[i][2];
-            v[i].w += d[i][3];
-            *reinterpret_cast<float4*>(h + base + c) = v[i];
-        }
-        ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
-    }
-    ss = warp_sum(ss);
-    const float inv = rsqrtf(ss / (float)H + eps);
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-        const int c = (i * 32 + lane) * 4;
-        if (c < H) {
-            const float4 g = *reinterpret_cast<const float4*>(gamma + c);
-            store4(out + base + c, v[i].x * inv * g.x, v[i].y * inv * g.y, v[i].z * inv * g.z, v[i].w * inv * g.w);
-        }
-    }
-}
-
 ZAI_API int zai_add_rmsnorm(float* h, const void* delta, const float* gamma, void* out, int dtype, float eps,
                             int N, int H, cudaStream_t stream) {
     if (N <= 0) return ZAI_OK;
     const bool aligned = ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(delta) | reinterpret_cast<uintptr_t>(gamma) |
                            reinterpret_cast<uintptr_t>(out)) & 15) == 0;
-    if ((H & 3) == 0 && H <= 2048 && aligned && N >= 512) {      // enough rows to fill the SMs with a warp each
-        const dim3 grid((N + 7) / 8);
-        if (H <= 1024) { ZAI_DISPATCH(dtype, return launch_pdl(add_rmsnorm_warp_kernel<T, 8>, grid, dim3(256), 0, stream, h, (const T*)delta, gamma, (T*)out, eps, N, H)); }
-        ZAI_DISPATCH(dtype, return launch_pdl(add_rmsnorm_warp_kernel<T, 16>, grid, dim3(256), 0, stream, h, (const T*)delta, gamma, (T*)out, eps, N, H));
-    }
     if ((H & 3) == 0 && H <= 8192 && aligned) {
         if (H <= 1024) { ZAI_DISPATCH(dtype, return launch_pdl(add_rmsnorm_vec_kernel<T, 1>, dim3(N), dim3(256), 0, stream, h, (const T*)delta, gamma, (T*)out, eps, H)); }
         if (H <= 2048) { ZAI_DISPATCH(dtype, return launch_pdl(add_rmsnorm_vec_kernel<T, 2>, dim3(N), dim3(256), 0, stream, h, (const T*)delta, gamma, (T*)out, eps, H)); }

@@ -205,6 +205,123 @@ __global__ void __launch_bounds__(256) qk_norm_rope_vec_kernel(
     }
 }
 
+// The same with 16-byte accesses: D = 16 * TPH, TPH threads share a head, each with eight values of the lower
+// half and their eight partners of the upper half.
+template <int TPH>
+__global__ void __launch_bounds__(256) qk_norm_rope_vec8_kernel(
+    const bf16* __restrict__ qkv, int qkv_cols, const float* __restrict__ q_gamma, const float* __restrict__ k_gamma,
+    float eps, const float2* __restrict__ cs_table, const int* __restrict__ positions, const int* __restrict__ seq_idx,
+    const int* __restrict__ block_table, int table_width, bf16* __restrict__ pages, int page_size,
+    bf16* __restrict__ q_out, bf16* __restrict__ k_out, int N, int Hq, int Hkv, int has_kv, int write, int num_pages,
+    int* __restrict__ status) {
+    constexpr int D = 16 * TPH, half = 8 * TPH;
+    pdl_trigger();
+    pdl_wait();
+    const int n_heads = Hq + (has_kv ? 2 * Hkv : 0);
+    const long long item = (long long)blockIdx.x * (256 / TPH) + threadIdx.x / TPH;
+    if (item >= (long long)N * n_heads) return;                    // (a whole group of TPH lanes leaves together)
+    const int t = (int)(item / n_heads), h = (int)(item % n_heads), d0 = (threadIdx.x % TPH) * 8;
+    const bf16* x = qkv + (size_t)t * qkv_cols + (size_t)h * D;
+    const uint4 lo4 = *reinterpret_cast<const uint4*>(x + d0), hi4 = *reinterpret_cast<const uint4*>(x + half + d0);
+    const bool is_q = h < Hq, is_v = h >= Hq + Hkv;
+    size_t page_base = 0;
+    int off = 0;
+    if (!is_q && write) {
+        const int pos = positions[t];
+        const int page = zai_checked_page(block_table + (size_t)seq_idx[t] * table_width, table_width,
+                                          pos < 0 ? -1 : pos / page_size, num_pages, status);
+        off = pos < 0 ? 0 : pos % page_size;
+        page_base = (size_t)page * 2 * Hkv * page_size * D;
+    }
+    if (is_v) {
+        if (write) {
+            bf16* dst = pages + page_base + (((size_t)Hkv + (h - Hq - Hkv)) * page_size + off) * D;
+            *reinterpret_cast<uint4*>(dst + d0) = lo4;
+            *reinterpret_cast<uint4*>(dst + half + d0) = hi4;
+        }
+        return;
+    }
+    const float* gamma = is_q ? q_gamma : k_gamma;
+    float lo[8], hi[8];
+    {
+        const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&lo4);
+        const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&hi4);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 u = __bfloat1622float2(a[e]), v = __bfloat1622float2(b[e]);
+            lo[2 * e] = u.x; lo[2 * e + 1] = u.y;
+            hi[2 * e] = v.x; hi[2 * e + 1] = v.y;
+        }
+    }
+    // (cos, sin) of d0 .. d0 + 7: four 16-byte loads
+    float cs[8], sn[8];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float4 v = *reinterpret_cast<const float4*>(cs_table + (size_t)t * half + d0 + 2 * e);
+        cs[2 * e] = v.x; sn[2 * e] = v.y; cs[2 * e + 1] = v.z; sn[2 * e + 1] = v.w;
+    }
+    if (gamma) {
+        float gl[8], gh[8];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const float4 u = *reinterpret_cast<const float4*>(gamma + d0 + 4 * e), v = *reinterpret_cast<const float4*>(gamma + half + d0 + 4 * e);
+            gl[4 * e] = u.x; gl[4 * e + 1] = u.y; gl[4 * e + 2] = u.z; gl[4 * e + 3] = u.w;
+            gh[4 * e] = v.x; gh[4 * e + 1] = v.y; gh[4 * e + 2] = v.z; gh[4 * e + 3] = v.w;
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += lo[e] * lo[e] + hi[e] * hi[e];
+#pragma unroll
+        for (int o = TPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float inv = rsqrtf(ss / (float)D + eps);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            lo[e] = lo[e] * inv * gl[e];
+            hi[e] = hi[e] * inv * gh[e];
+        }
+    }
+    uint4 ol, oh;
+    {
+        __nv_bfloat162* a = reinterpret_cast<__nv_bfloat162*>(&ol);
+        __nv_bfloat162* b = reinterpret_cast<__nv_bfloat162*>(&oh);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int i = 2 * e, j = 2 * e + 1;
+            a[e] = __floats2bfloat162_rn(lo[i] * cs[i] - hi[i] * sn[i], lo[j] * cs[j] - hi[j] * sn[j]);
+            b[e] = __floats2bfloat162_rn(lo[i] * sn[i] + hi[i] * cs[i], lo[j] * sn[j] + hi[j] * cs[j]);
+        }
+    }
+    if (is_q) {
+        bf16* dst = q_out + ((size_t)t * Hq + h) * D;
+        *reinterpret_cast<uint4*>(dst + d0) = ol;
+        *reinterpret_cast<uint4*>(dst + half + d0) = oh;
+    } else {
+        if (write) {
+            bf16* dst = pages + page_base + ((size_t)(h - Hq) * page_size + off) * D;
+            *reinterpret_cast<uint4*>(dst + d0) = ol;
+            *reinterpret_cast<uint4*>(dst + half + d0) = oh;
+        }
+        if (k_out) {
+            bf16* dst = k_out + ((size_t)t * Hkv + (h - Hq)) * D;
+            *reinterpret_cast<uint4*>(dst + d0) = ol;
+            *reinterpret_cast<uint4*>(dst + half + d0) = oh;
+        }
+    }
+}
+
+template <int TPH>
+static int launch_qk_vec8(const void* qkv, int qkv_cols, const float* q_gamma, const float* k_gamma, float eps,
+                          const float2* cs_table, const int* positions, const int* seq_idx, const int* block_table,
+                          int table_width, void* pages, int page_size, void* q_out, void* k_out, int N, int Hq, int Hkv,
+                          int has_kv, int write, int num_pages, int* status, cudaStream_t stream) {
+    const long long items = (long long)N * (Hq + (has_kv ? 2 * Hkv : 0));
+    const long long blocks = (items + 256 / TPH - 1) / (256 / TPH);
+    if (blocks > 0x7fffffffLL) return ZAI_BAD_SIZE;
+    return launch_pdl(qk_norm_rope_vec8_kernel<TPH>, dim3((unsigned)blocks), dim3(256), 0, stream, (const bf16*)qkv, qkv_cols,
+                      q_gamma, k_gamma, eps, cs_table, positions, seq_idx, block_table, table_width, (bf16*)pages, page_size,
+                      (bf16*)q_out, (bf16*)k_out, N, Hq, Hkv, has_kv, write, num_pages, status);
+}
+
 template <int TPH>
 static int launch_qk_vec(const void* qkv, int qkv_cols, const float* q_gamma, const float* k_gamma, float eps,
                          const float2* cs_table, const int* positions, const int* seq_idx, const int* block_table,
@@ -258,6 +375,11 @@ ZAI_API int zai_qk_norm_rope(const void* qkv, int qkv_cols, int dtype, const flo
                           reinterpret_cast<uintptr_t>(cs_table) | reinterpret_cast<uintptr_t>(pages) |
                           reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_out);
     if (dtype == ZAI_BF16 && rot == D && (D & 7) == 0 && (qkv_cols & 7) == 0 && (all & 15) == 0) {
+        // many rows: 16 bytes a load (head sizes that are 16 times a power of two)
+#define ZAI_QK_VEC8(tph) if (N >= 256 && D == 16 * tph) return launch_qk_vec8<tph>(qkv, qkv_cols, q_gamma, k_gamma, eps, cs_table, positions, \
+        seq_idx, block_table, table_width, pages, page_size, q_out, k_out, N, Hq, Hkv, has_kv, write, num_pages, status, stream);
+        ZAI_QK_VEC8(1) ZAI_QK_VEC8(2) ZAI_QK_VEC8(4) ZAI_QK_VEC8(8) ZAI_QK_VEC8(16)
+#undef ZAI_QK_VEC8
 #define ZAI_QK_VEC(tph) if (D == 8 * tph) return launch_qk_vec<tph>(qkv, qkv_cols, q_gamma, k_gamma, eps, cs_table, positions, \
         seq_idx, block_table, table_width, pages, page_size, q_out, k_out, N, Hq, Hkv, has_kv, write, num_pages, status, stream);
         ZAI_QK_VEC(2) ZAI_QK_VEC(4) ZAI_QK_VEC(8) ZAI_QK_VEC(16) ZAI_QK_VEC(32)
