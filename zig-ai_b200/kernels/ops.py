@@ -428,9 +428,9 @@ def _tensor_core(x, w, epilogue, out_cols, out_dtype):
 
 # Steps of 17 to 128 rows: the weight-streaming tcgen05 kernel (csrc/stream_gemm.cu), with SwiGLU or the
 # short convolution as its epilogue.  Measured on B200 it is behind the library's product plus the
-# separate activation / convolution kernel at the shapes of the LFM2 models (a block's K loop is bound
-# by the turnover of its ring, through which every block also streams all of x, about 0.4 us per 64-k
-# slice: see profiles/stream_gemm_tcgen05_17_128_rows.md), so it is an option: ZAI_STREAM_GEMM=1 turns it on.
+# separate activation / convolution kernel at the shapes of the LFM2 models (a block's K loop costs about
+# 0.4 us per 64-k slice whatever the slice holds: see profiles/stream_gemm_tcgen05_17_128_rows.md), so it
+# is an option: ZAI_STREAM_GEMM=1 turns it on.
 USE_STREAM_GEMM = os.environ.get("ZAI_STREAM_GEMM", "0") == "1"
 STREAM_MIN_ROWS, STREAM_MAX_ROWS = 17, 128
 
