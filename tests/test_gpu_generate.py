@@ -340,3 +340,37 @@ def test_preemption_and_recomputation_in_bfloat16_pick_plain_maxima(tiny_models,
         for i, tok in enumerate(out):
             row = logits[len(p) + i - 1]
             assert float(row.max() - row[tok]) <= 8e-2 * float(row.abs().max()), (i, tok)
+
+
+def test_a_long_random_serving_run_gives_the_plain_greedy_tokens(tiny_models):
+    """Forty requests of random lengths through six seats and a pool so small that requests are preempted
+    and recomputed, arriving while others decode (so that steps of every kind follow one another: prompt
+    portions alone, beside decoding requests, decode steps replayed from graphs and launched a step
+    ahead): in 32-bit every request's tokens are the plain implementation's greedy tokens, and at the end
+    every page and slot is free."""
+    import zig_ai_b200 as z
+    name = "B"
+    g = random.Random(21)
+    V = TINY[name][0]["vocab_size"]
+    ps = PAGE_SIZE[name]
+    eng = z.Engine(tiny_models[name], "float32", max_num_seqs=6, max_batched_tokens=40, max_model_len=128,
+                   max_tokens=26 * ps, page_size=ps)
+    todo = [([g.randrange(V) for _ in range(g.randint(1, 60))], g.randint(3, 24)) for _ in range(40)]
+    ids, done, at = {}, {}, 0
+    while len(done) < len(todo):
+        # a few arrivals every few steps
+        if at < len(todo) and (eng.n_steps % 3 == 0 or not eng.has_work()):
+            for _ in range(g.randint(1, 3)):
+                if at < len(todo):
+                    p, n = todo[at]
+                    ids[eng.add_request(p, z.SamplingParams(temperature=0.0, max_new_tokens=n))] = at
+                    at += 1
+        for r in eng.step():
+            done[ids[r.request_id]] = r
+    eng.flush()
+    st = eng.stats()
+    assert st["preemptions"] > 0 and st["steps_ahead"] > 0
+    assert st["slots_used"] == 0 and all(v == 0 for k, v in st.items() if k.endswith("_pages_used"))
+    eng.runner.cache.check()
+    for i, (p, n) in enumerate(todo):
+        assert done[i].finish_reason == "length" and done[i].output == plain_greedy(tiny_models[name], p, n), i
