@@ -552,13 +552,13 @@ def test_two_block_tensor_core_gemm_swiglu(N, F, K, wide):
     assert torch.allclose(y.float(), want, atol=3e-2, rtol=3e-2)
     if wide and N >= o.PAIR_SWIGLU_MIN_ROWS:
         # and through the op the parts call, with the switch that sends gate/up products to this kernel
-        old, o.USE_PAIR_GEMM = o.USE_PAIR_GEMM, True
+        old, o.USE_PAIR_GEMM, o.PAIR_GEMM_ALWAYS = (o.USE_PAIR_GEMM, o.PAIR_GEMM_ALWAYS), True, True
         try:
             before = o.launches
             got = o.linear_swiglu(x, w, F)
             assert o.launches == before + 1 and torch.allclose(got.float(), want, atol=3e-2, rtol=3e-2)
         finally:
-            o.USE_PAIR_GEMM = old
+            o.USE_PAIR_GEMM, o.PAIR_GEMM_ALWAYS = old
         assert o.tc_status() == 0
 
 

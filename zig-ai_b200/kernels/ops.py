@@ -486,11 +486,16 @@ def _library_product(x, w, out_dtype):
 
 
 # The two-block tcgen05 kernel (csrc/gemm_tc_pair.cu) runs the gate/up product with SwiGLU in its
-# epilogue in the time the library's product and the activation kernel take together at the 350M
-# shape (38 us against 36-41 us at 2048 rows) and is 3 % behind them at the 1.2B shape, so it is an
-# option, not the default: ZAI_PAIR_GEMM=1 sends gate/up products of this many rows or more to it.
+# epilogue in the time the library's product and the activation kernel take together where the model is
+# 1024 wide (a prefill of 2048 tokens at the 350M shape: 1.98-2.01 ms either way, measured in one run)
+# and is 1 % and 2 % behind them at the widths of the 700M and 1.2B shapes.  So gate/up products of
+# PAIR_SWIGLU_MIN_ROWS rows or more go to it where K is at most PAIR_SWIGLU_MAX_K; ZAI_PAIR_GEMM=1 sends
+# them there at every width, ZAI_PAIR_GEMM=0 never.
 PAIR_SWIGLU_MIN_ROWS = int(os.environ.get("ZAI_PAIR_SWIGLU_MIN_ROWS", "1024"))
-USE_PAIR_GEMM = os.environ.get("ZAI_PAIR_GEMM", "0") == "1"
+PAIR_SWIGLU_MAX_K = 1024
+_pair_env = os.environ.get("ZAI_PAIR_GEMM", "auto")
+USE_PAIR_GEMM = _pair_env != "0"             # False: never; True: by the rule above (or always, with PAIR_GEMM_ALWAYS)
+PAIR_GEMM_ALWAYS = _pair_env == "1"
 
 
 @_timed(_product_class)
@@ -522,7 +527,7 @@ def linear_swiglu(x, w_gate_up, ff_dim):
             y = _tensor_core(x, w_gate_up, _EPI_SWIGLU, ff_dim, torch.bfloat16)
         if y is not None:
             return y
-        if USE_PAIR_GEMM and x.shape[0] >= PAIR_SWIGLU_MIN_ROWS:
+        if USE_PAIR_GEMM and x.shape[0] >= PAIR_SWIGLU_MIN_ROWS and (PAIR_GEMM_ALWAYS or x.shape[1] <= PAIR_SWIGLU_MAX_K):
             y = gemm_pair(x, w_gate_up, _EPI_SWIGLU, ff_dim, torch.bfloat16)
             if y is not None:
                 return y
