@@ -8,16 +8,25 @@
 //
 //     S = Q K^T      tcgen05.mma, M = 128 (query rows = TMEM lanes), N = 128 keys, K = 64, into TMEM
 //     P = exp2(..)   four warps, one query row per thread: the row's 128 scores come from TMEM with
-//                    tcgen05.ld (no shuffles: a thread owns its row), P goes to shared memory as the
-//                    next product's A operand (bfloat16, 128-byte swizzle)
-//     O_t = P V      tcgen05.mma, N = 64, K = 128 keys, V read straight from its page layout
-//                    [key][64] as an MN-major operand, accumulated into O in TMEM; the threads
+//                    tcgen05.ld (no shuffles: a thread owns its row), the load of the next 32 columns
+//                    in flight while these are worked on; P goes back into TMEM (tcgen05.st, two
+//                    bfloat16 a column) as the next product's A operand
+//     O_t = P V      tcgen05.mma with A in TMEM, N = 64, K = 128 keys, V read straight from its page
+//                    layout [key][64] as an MN-major operand, accumulated into O in TMEM; the threads
 //                    rescale O there only when a row's reference maximum has to move
 //
+// After a row's first tile the threads do not look for a tile's maximum first: they compute P against
+// the reference as it is and find the maximum on the way; only if it lies more than 2^8 above the
+// reference in some row of the warp does the reference move and the tile get walked again.
+//
 // Q, K and V reach shared memory by TMA (cp.async.bulk.tensor, no multicast), K and V page by page
-// through the block table into two stages.  Roles: warp 0 one lane issues the loads, warp 1 one lane
-// the products, warps 2-5 are the softmax.  The product of the next tile's scores is issued as soon
-// as P of this tile is consumed, so it overlaps the threads' work on O_t.
+// through the block table into three stages.  Roles: warp 0 one lane issues the loads, warp 1 one lane
+// the products, warps 2-5 are the softmax.  As soon as P of a tile is written, the scores of the next
+// tile are issued (the softmax threads wait for those), then O_t.
+//
+// Blocks are handed out heads first, tiles of query rows from the last rows backwards: under the causal
+// mask the last rows of a long span walk many more key tiles than the first, a block's tiles are a chain
+// (scores, softmax, P, product), and the longest blocks of every head should start first.
 // Every wait on an mbarrier is bounded; a block whose wait runs out raises the status word, its roles
 // leave their loops, TMEM is freed and the block returns.
 #include <cuda.h>
@@ -27,12 +36,13 @@
 #define AT_BM 128
 #define AT_BN 128
 #define AT_THREADS 192
-#define AT_STAGES 2
+#define AT_STAGES 3
 #define AT_SPIN_LIMIT 4000000
 #define AT_Q_BYTES (AT_BM * AT_D * 2)                 // 16 KB
 #define AT_KV_BYTES (2 * AT_BN * AT_D * 2)            // keys then values: 32 KB
-#define AT_P_BYTES (AT_BM * AT_BN * 2)                // 32 KB
-#define AT_TMEM_COLS 256                              // scores in columns 0..127, O in 128..191
+#define AT_TMEM_COLS 256                              // scores in columns 0..127, O in 128..191, P in 192..255
+#define AT_COL_O AT_BN
+#define AT_COL_P (AT_BN + AT_D)
 
 __device__ __forceinline__ uint32_t at_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void at_mbar_init(uint64_t* bar, int count) {
@@ -110,6 +120,29 @@ __device__ __forceinline__ void at_tmem_st32(uint32_t taddr, const uint32_t (&r)
                  : "memory");
 }
 
+__device__ __forceinline__ void at_tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+                 : "memory");
+}
+// A product whose A operand lies in TMEM (row = lane, two bfloat16 of k per 32-bit column)
+__device__ __forceinline__ void at_umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+// The wait for a thread's TMEM loads, tied to the registers of one of them: what is computed from those
+// registers cannot be scheduled ahead of the wait, while another load may stay in flight across it.
+__device__ __forceinline__ void at_tmem_wait_ld(uint32_t (&r)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                   "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                   "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                 :: "memory");
+}
+
 struct AtArgs {
     bf16* out;                  // [rows of the step, Hq, 64]
     const int* block_table;     // [S, table_width]
@@ -130,8 +163,7 @@ __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_con
     unsigned char* base = smem_raw;
     unsigned char* sQ = base;
     unsigned char* sKV = base + AT_Q_BYTES;
-    unsigned char* sP = sKV + AT_STAGES * AT_KV_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + AT_P_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + AT_STAGES * AT_KV_BYTES);
     uint64_t& q_full = bars[0];
     uint64_t* kv_full = bars + 1;                               // [AT_STAGES]
     uint64_t* kv_empty = bars + 1 + AT_STAGES;                  // [AT_STAGES]
@@ -170,9 +202,10 @@ __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_con
     pdl_trigger();
     pdl_wait();
     if (tid == 0) {
-        // blocks are numbered from the last rows of the last request backwards: under the causal
-        // mask later rows have more keys to walk, and the longest blocks should start first
-        int t = gridDim.x - 1 - blockIdx.x, s = 0;
+        // Blocks are handed out x fastest, so the heads are x and the tiles of query rows y, numbered from
+        // the last rows of the last request backwards: under the causal mask later rows have more keys
+        // to walk, and the longest blocks of every head should start first
+        int t = (int)gridDim.y - 1 - (int)blockIdx.y, s = 0;
         for (; s < a.S; ++s) {
             const int nt = (a.cu_q[s + 1] - a.cu_q[s] + AT_BM - 1) / AT_BM;
             if (t < nt) break;
@@ -184,7 +217,7 @@ __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_con
     __syncthreads();
     const int s = s_seq, i0 = s_i0;
     if (s < a.S && !failed_flag) {
-        const int h = blockIdx.y, hk = h / (a.Hq / a.Hkv);
+        const int h = blockIdx.x, hk = h / (a.Hq / a.Hkv);
         const int row0 = a.cu_q[s], q_len = a.cu_q[s + 1] - row0, ctx = a.ctx_lens[s];
         const int rows = min(AT_BM, q_len - i0);                    // valid query rows of this block
         const int kend = ctx + i0 + rows;                           // one past the last visible key of the block
@@ -192,7 +225,7 @@ __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_con
         const int tile0 = kbeg / AT_BN, tile1 = (kend + AT_BN - 1) / AT_BN, n_tiles = tile1 - tile0;
 
         if (warp == 0) {
-            if (lane == 0) {
+            if (lane == 0 && n_tiles > 0) {
                 // ---- loads: the block's queries, then a stage of keys and values per tile, page by page
                 const int* table = a.block_table + (size_t)s * a.table_width;
                 const int ps = a.page_size, box_rows = ps < AT_BN ? ps : AT_BN, per_tile = AT_BN / box_rows;
@@ -240,14 +273,15 @@ __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_con
                 }
             }
         } else if (warp == 1) {
-            if (lane == 0) {
+            if (lane == 0 && n_tiles > 0) {
                 // ---- products.  Instruction descriptors: D 32-bit, A and B bfloat16, M = 128; the scores
-                // have N = 128 and both operands K-major; O_t has N = 64 and B (the values) MN-major.
+                // have N = 128 and both operands K-major; O_t has N = 64, A (P) in TMEM and B (the values)
+                // MN-major.
                 constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(AT_BN >> 3) << 17) | ((uint32_t)(AT_BM >> 4) << 24);
                 constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(AT_D >> 3) << 17) |
                                              ((uint32_t)(AT_BM >> 4) << 24);
-                const uint32_t tS = tmem_base, tO = tmem_base + AT_BN;
-                const uint32_t aQ = at_smem(sQ), aP = at_smem(sP);
+                const uint32_t tS = tmem_base, tO = tmem_base + AT_COL_O, tP = tmem_base + AT_COL_P;
+                const uint32_t aQ = at_smem(sQ);
                 bool ok = at_mbar_wait(&q_full, 0, failed);
                 auto scores = [&](int i) {                      // S = Q K^T of tile i
                     const int st = i % AT_STAGES;
@@ -259,22 +293,24 @@ __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_con
                     at_commit(&s_ready);
                     return true;
                 };
-                if (ok && n_tiles > 0) ok = scores(0);
+                if (ok) ok = scores(0);
                 for (int i = 0; i < n_tiles && ok; ++i) {
                     const int st = i % AT_STAGES;
                     ok = at_mbar_wait(&p_ready, i & 1, failed);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    // P lies in TMEM beside the scores, which the softmax threads have read: the next
+                    // tile's scores go first (the threads wait for them), then this tile's O_t
+                    if (i + 1 < n_tiles) ok = scores(i + 1);
                     const uint32_t aV = at_smem(sKV + (size_t)st * AT_KV_BYTES + AT_BN * 128);
 #pragma unroll
-                    for (int kk = 0; kk < AT_BN / 16; ++kk)     // 16 keys a step: P 32 bytes along its rows, V two groups of 8 keys
-                        at_umma(tO, at_desc(aP + (kk >> 2) * (AT_BM * 128) + (kk & 3) * 32), at_desc(aV + kk * 2048), idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+                    for (int kk = 0; kk < AT_BN / 16; ++kk)     // 16 keys a step: eight columns of P, two groups of 8 keys of V
+                        at_umma_ts(tO, tP + kk * 8, at_desc(aV + kk * 2048), idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
                     at_commit(&o_ready);
                     at_commit(&kv_empty[st]);
-                    if (i + 1 < n_tiles) ok = scores(i + 1);
                 }
             }
-        } else {
+        } else if (n_tiles > 0) {
             // ---- softmax: thread = query row.  O stays in TMEM (the products add to it); the row's
             // reference maximum is only moved, and O and the sum rescaled, when a tile's maximum exceeds
             // it by more than 2^8 (P then stays below 256, exact enough in bfloat16 and 32-bit sums; the
@@ -284,10 +320,9 @@ __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_con
             const bool valid = row < rows;
             const int qpos = ctx + i0 + row;                    // the row's position: keys 0..qpos are visible
             const int klo = a.window > 0 ? max(qpos - a.window + 1, 0) : 0;
-            const uint32_t tS = tmem_base + ((uint32_t)(qd * 32) << 16), tO = tS + AT_BN;
+            const uint32_t tS = tmem_base + ((uint32_t)(qd * 32) << 16), tO = tS + AT_COL_O, tP = tS + AT_COL_P;
             const float c = a.scale_log2;
-            float m = -INFINITY, l = 0.f;                       // m: the reference, in units of the scores
-            unsigned char* prow = sP + (size_t)row * 128;
+            float m = -INFINITY, l = 0.f;                       // m: the row's reference, in units of the scores
             bool alive = true;
             for (int i = 0; i < n_tiles && alive; ++i) {
                 const int key0 = (tile0 + i) * AT_BN;
@@ -296,25 +331,68 @@ __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_con
                 // keys of this tile that the row sees: [lo, hi)
                 const int lo = valid ? max(klo - key0, 0) : AT_BN, hi = valid ? min(qpos + 1 - key0, AT_BN) : 0;
                 const bool full = lo <= 0 && hi >= AT_BN;       // the row sees the whole tile: no masking needed
-                float mx = -INFINITY;
-#pragma unroll 1
-                for (int c0 = 0; c0 < AT_BN; c0 += 64) {
+                // one walk over the row's 128 scores in chunks of 32 columns, the load of the next chunk in
+                // flight while this one is worked on: the maximum of the visible scores (`mx`), and with
+                // `emit` the probabilities against `ref` into P and their sum (`lt`)
+                auto walk = [&](bool emit, float ref, float& mx, float& lt) {
                     uint32_t r[2][32];
-                    at_tmem_ld32_nowait(tS + c0, r[0]);
-                    at_tmem_ld32_nowait(tS + c0 + 32, r[1]);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    at_tmem_ld32_nowait(tS, r[0]);
+                    if (emit && i > 0) {                        // P of the tile before must have been read by its product
+                        if (!__all_sync(0xffffffffu, at_mbar_wait(&o_ready, (i - 1) & 1, failed))) alive = false;
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    }
 #pragma unroll
-                    for (int hh = 0; hh < 2; ++hh) {
+                    for (int k = 0; k < AT_BN / 32; ++k) {
+                        at_tmem_wait_ld(r[k & 1]);
+                        if (k + 1 < AT_BN / 32) at_tmem_ld32_nowait(tS + 32 * (k + 1), r[(k + 1) & 1]);
+                        const uint32_t (&x)[32] = r[k & 1];
+                        const int c0 = 32 * k;
+                        if (!emit) {
+                            if (full) {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(x[j]));
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j)
+                                    if (c0 + j >= lo && c0 + j < hi) mx = fmaxf(mx, __uint_as_float(x[j]));
+                            }
+                            continue;
+                        }
+                        uint32_t pk[16];
                         if (full) {
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(r[hh][j]));
+                            for (int j = 0; j < 32; j += 2) {
+                                const float s0 = __uint_as_float(x[j]), s1 = __uint_as_float(x[j + 1]);
+                                mx = fmaxf(mx, fmaxf(s0, s1));
+                                const float p0 = at_exp2(s0 * c - ref), p1 = at_exp2(s1 * c - ref);
+                                lt += p0 + p1;
+                                __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
+                                pk[j >> 1] = *reinterpret_cast<uint32_t*>(&v);
+                            }
                         } else {
 #pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (c0 + hh * 32 + j >= lo && c0 + hh * 32 + j < hi) mx = fmaxf(mx, __uint_as_float(r[hh][j]));
+                            for (int j = 0; j < 32; j += 2) {
+                                // (a hidden score may be anything, also NaN: it is replaced before the exponential)
+                                const int k0 = c0 + j;
+                                const bool v0 = k0 >= lo && k0 < hi, v1 = k0 + 1 >= lo && k0 + 1 < hi;
+                                const float s0 = v0 ? __uint_as_float(x[j]) : -INFINITY, s1 = v1 ? __uint_as_float(x[j + 1]) : -INFINITY;
+                                mx = fmaxf(mx, fmaxf(s0, s1));
+                                const float p0 = at_exp2(s0 * c - ref), p1 = at_exp2(s1 * c - ref);
+                                lt += p0 + p1;
+                                __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
+                                pk[j >> 1] = *reinterpret_cast<uint32_t*>(&v);
+                            }
                         }
+                        at_tmem_st16(tP + 16 * k, pk);          // 32 keys = 16 columns of P
                     }
-                }
+                };
+                // With a reference in every row of the warp, the tile is walked once against it; else the
+                // maximum is found first, as a walk of its own.
+                const bool speculate = i > 0 && __all_sync(0xffffffffu, m != -INFINITY || !valid);
+                float mx = -INFINITY, lt = 0.f;
+                if (speculate) walk(true, m == -INFINITY ? 0.f : m * c, mx, lt);
+                else walk(false, 0.f, mx, lt);
+                if (!alive) break;
                 // move the reference?  (warp-wide decision: the TMEM accesses below are the whole warp's)
                 float alpha = 1.f;
                 if (m == -INFINITY) {
@@ -323,7 +401,8 @@ __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_con
                     alpha = at_exp2(m * c - mx * c);
                     m = mx;
                 }
-                if (i > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                const bool moved = __any_sync(0xffffffffu, alpha != 1.f);
+                if (i > 0 && moved) {
                     if (!__all_sync(0xffffffffu, at_mbar_wait(&o_ready, (i - 1) & 1, failed))) { alive = false; break; }   // the product before has added to O
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
@@ -334,57 +413,22 @@ __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_con
                         for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
                         at_tmem_st32(tO + c0, r);
                     }
-                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                     l *= alpha;
                 }
-                const float ref = m == -INFINITY ? 0.f : m * c;              // no key seen so far: every p is 0
-                float lt = 0.f;
-#pragma unroll 1
-                for (int c0 = 0; c0 < AT_BN; c0 += 64) {
-                    uint32_t r[2][32];
-                    at_tmem_ld32_nowait(tS + c0, r[0]);
-                    at_tmem_ld32_nowait(tS + c0 + 32, r[1]);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    unsigned char* half = prow + (c0 >> 6) * (AT_BM * 128);  // the half of P that holds these 64 keys
-#pragma unroll
-                    for (int hh = 0; hh < 2; ++hh) {
-                        uint32_t pk[16];
-                        if (full) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 2) {
-                                const float p0 = at_exp2(__uint_as_float(r[hh][j]) * c - ref), p1 = at_exp2(__uint_as_float(r[hh][j + 1]) * c - ref);
-                                lt += p0 + p1;
-                                __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
-                                pk[j >> 1] = *reinterpret_cast<uint32_t*>(&v);
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 2) {
-                                // (a hidden score may be anything, also NaN: it is replaced before the exponential)
-                                const int k0 = c0 + hh * 32 + j;
-                                const float s0 = (k0 >= lo && k0 < hi) ? __uint_as_float(r[hh][j]) * c - ref : -INFINITY;
-                                const float s1 = (k0 + 1 >= lo && k0 + 1 < hi) ? __uint_as_float(r[hh][j + 1]) * c - ref : -INFINITY;
-                                const float p0 = at_exp2(s0), p1 = at_exp2(s1);
-                                lt += p0 + p1;
-                                __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
-                                pk[j >> 1] = *reinterpret_cast<uint32_t*>(&v);
-                            }
-                        }
-                        // 32 keys = four 16-byte pieces of the row
-#pragma unroll
-                        for (int q4 = 0; q4 < 4; ++q4)
-                            *reinterpret_cast<uint4*>(half + (((hh * 4 + q4) ^ (row & 7)) << 4)) =
-                                make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
-                    }
+                if (!speculate || moved) {
+                    lt = 0.f;
+                    float again = -INFINITY;
+                    walk(true, m == -INFINITY ? 0.f : m * c, again, lt);   // no key seen so far: every p is 0
+                    if (!alive) break;
                 }
                 l += lt;
-                // P is written by these threads and read by the tensor core's (asynchronous) proxy
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                // P (and a rescaled O) are in TMEM before the product-issuing thread hears of it
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) at_mbar_arrive(&p_ready);
             }
-            if (alive && n_tiles > 0 && __all_sync(0xffffffffu, at_mbar_wait(&o_ready, (n_tiles - 1) & 1, failed))) {
+            if (alive && __all_sync(0xffffffffu, at_mbar_wait(&o_ready, (n_tiles - 1) & 1, failed))) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const float inv = l > 0.f ? 1.f / l : 0.f;
                 bf16* dst = a.out + ((size_t)(row0 + i0 + row) * a.Hq + h) * AT_D;
@@ -444,21 +488,21 @@ static int at_make_map(CUtensorMap* map, const void* ptr, cuuint64_t cols, cuuin
 
 // 1 if this kernel takes the sizes: head size 64, a page size that is a power of two from 8 to 128
 ZAI_API int zai_prefill_attention_tc_supports(int D, int Hq, int Hkv, int page_size) {
-    if (D != AT_D || Hkv < 1 || Hq % Hkv != 0 || Hq > 65535) return 0;
+    if (D != AT_D || Hkv < 1 || Hq % Hkv != 0 || Hq > 32767) return 0;
     if (page_size < 8 || page_size > AT_BN || (page_size & (page_size - 1))) return 0;
     return at_encode_tiled() != nullptr;
 }
 
 // out [N, Hq, 64] = attention of q [N, Hq, 64] (N rows in all, `n_tiles` blocks of 128 rows over the
 // requests' spans) over the pages [num_pages, 2, Hkv, page_size, 64]; arguments as
-// zai_prefill_attention_mma, plus the row and page counts and a status word that a block raises to 1
-// if one of its waits ran out.
+// zai_prefill_attention_mma, plus the row and page counts and the status word that a block raises
+// if one of its waits ran out or a page id lay outside the pool.
 ZAI_API int zai_prefill_attention_tc(void* out, const void* q, const void* pages, int num_pages, int* status,
                                      const int* block_table, int table_width, const int* cu_q, const int* ctx_lens, int N,
                                      int S, int n_tiles, int page_size, int Hq, int Hkv, int D, float scale, int window,
                                      cudaStream_t stream) {
     if (N <= 0 || S <= 0 || n_tiles <= 0) return ZAI_OK;
-    if (!zai_prefill_attention_tc_supports(D, Hq, Hkv, page_size)) return ZAI_BAD_SIZE;
+    if (!zai_prefill_attention_tc_supports(D, Hq, Hkv, page_size) || n_tiles > 65535) return ZAI_BAD_SIZE;
     if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(pages) | reinterpret_cast<uintptr_t>(out)) & 15) return ZAI_BAD_SIZE;
     CUtensorMap mq, mkv;
     int e = at_make_map(&mq, q, (cuuint64_t)Hq * AT_D, (cuuint64_t)N, AT_BM);
@@ -471,7 +515,7 @@ ZAI_API int zai_prefill_attention_tc(void* out, const void* q, const void* pages
     a.scale_log2 = scale * 1.4426950408889634f;
     a.page_shift = 0;
     while ((1 << a.page_shift) < page_size) ++a.page_shift;
-    const size_t smem = AT_Q_BYTES + (size_t)AT_STAGES * AT_KV_BYTES + AT_P_BYTES + 128;
+    const size_t smem = AT_Q_BYTES + (size_t)AT_STAGES * AT_KV_BYTES + 128;
     static unsigned long long configured = 0;
     if (zai_first_on_device(&configured)) {
         cudaError_t err = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -480,5 +524,5 @@ ZAI_API int zai_prefill_attention_tc(void* out, const void* q, const void* pages
         err = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         if (err != cudaSuccess) return (int)err;
     }
-    return launch_pdl(prefill_tc_kernel, dim3(n_tiles, Hq), dim3(AT_THREADS), smem, stream, mq, mkv, a);
+    return launch_pdl(prefill_tc_kernel, dim3(Hq, n_tiles), dim3(AT_THREADS), smem, stream, mq, mkv, a);
 }

@@ -11,6 +11,7 @@ from __future__ import annotations
 import ctypes
 import os
 import sys
+import weakref
 from ctypes import c_float, c_int, c_void_p
 
 import torch
@@ -53,6 +54,7 @@ _SIGNATURES = {
         "zai_skinny_gemm_supports": [_I, _I, _I, _I, _I],
         "zai_skinny_gemm": [_P, _P, _P, _P, _P, _P, _P, _P, _F, _I, _I, _I, _I, _P],
         "zai_skinny_conv": [_P, _P, _P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+        "zai_skinny_hint_next": [_P, ctypes.c_longlong],
     },
     "stream_gemm": {
         "zai_stream_gemm_supports": [_I, _I, _I, _I],
@@ -332,6 +334,29 @@ def add_rmsnorm(h, delta, w, eps, out_dtype):
     return out
 
 
+# ---- which weights follow which.  The few-rows product kernels ask the weights of the product after
+# them into L2 while they run.  Nobody has to tell them the order: a call notes that its weights came
+# after the last call's, and the next time the last call's weights are used, that is the hint.  (Weak
+# references: a hint never outlives the tensor it points to.  A wrong hint, after a change of model
+# or of step shape, costs a useless prefetch once and is then replaced.)
+_follower = {}          # data_ptr of a weight -> weak reference to the weight used after it last time
+_last_weight = [0]
+
+
+def _hint_next_weights(w) -> None:
+    p = w.data_ptr()
+    last = _last_weight[0]
+    if last and last != p:
+        known = _follower.get(last)
+        if known is None or known() is not w:
+            _follower[last] = weakref.ref(w)
+    _last_weight[0] = p
+    nxt = _follower.get(p)
+    nxt = nxt() if nxt is not None else None
+    if nxt is not None and nxt.is_cuda and nxt.device == w.device:
+        _fn("decode_gemm", "zai_skinny_hint_next")(nxt.data_ptr(), nxt.numel() * nxt.element_size())
+
+
 @_timed(_product_class)
 def _skinny(x, w, epilogue, out_cols, out_dtype):
     """The few-rows product kernel, if it takes these operands; else None."""
@@ -343,6 +368,7 @@ def _skinny(x, w, epilogue, out_cols, out_dtype):
     if not _fn("decode_gemm", "zai_skinny_gemm_supports")(M, O, K, epilogue, int(lazy)):
         return None
     y = torch.empty((M, out_cols), dtype=out_dtype, device=w.device)
+    _hint_next_weights(w)
     if lazy:
         res = x.residual
         _cuda(res.data, x.delta, x.gamma, x.rows)
@@ -586,6 +612,7 @@ def _skinny_conv(x, w_in, conv_w, conv_b, state, step, taps, write_state, lazy, 
     _cuda(w_in, conv_w, conv_b, state)
     z = torch.empty((M, C), dtype=torch.bfloat16, device=w_in.device)
     fn = _fn("decode_gemm", "zai_skinny_conv")
+    _hint_next_weights(w_in)
     tail = (_ptr(conv_w), _ptr(conv_b), _ptr(state), _ptr(step.slot_ids), M, C, K, int(taps), state.shape[1],
             int(bool(write_state)), state.shape[0], _status_ptr(state.device), _stream())
     if lazy:
