@@ -337,10 +337,6 @@ __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_con
                 auto walk = [&](bool emit, float ref, float& mx, float& lt) {
                     uint32_t r[2][32];
                     at_tmem_ld32_nowait(tS, r[0]);
-                    if (emit && i > 0) {                        // P of the tile before must have been read by its product
-                        if (!__all_sync(0xffffffffu, at_mbar_wait(&o_ready, (i - 1) & 1, failed))) alive = false;
-                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    }
 #pragma unroll
                     for (int k = 0; k < AT_BN / 32; ++k) {
                         at_tmem_wait_ld(r[k & 1]);
@@ -382,6 +378,12 @@ __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_con
                                 __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
                                 pk[j >> 1] = *reinterpret_cast<uint32_t*>(&v);
                             }
+                        }
+                        if (k == 0 && i > 0) {
+                            // P of the tile before must have been read by its product, which was issued behind
+                            // this tile's scores: the wait comes after the first chunk's arithmetic, not before
+                            if (!__all_sync(0xffffffffu, at_mbar_wait(&o_ready, (i - 1) & 1, failed))) alive = false;
+                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         }
                         at_tmem_st16(tP + 16 * k, pk);          // 32 keys = 16 columns of P
                     }
