@@ -118,11 +118,12 @@ PROFILE_RANGE = False      # --profile-range: the timed decode steps lie between
 
 
 def decode_requests(eng, B, steps_needed, seed):
-    """Add B requests with contexts spread over 2048..CONTEXT and run until all of them decode."""
+    """Add B requests with contexts spread over CONTEXT / 2..CONTEXT and run until all of them decode."""
     from zig_ai_b200.sampling import SamplingParams
     g = random.Random(seed)
+    lo = CONTEXT // 2
     hi = CONTEXT - steps_needed - 160          # room for the tokens decoded while later requests still prefill
-    lens = [2048 + (hi - 2048) * i // max(B - 1, 1) for i in range(B)] if B > 1 else [(2048 + hi) // 2]
+    lens = [lo + (hi - lo) * i // max(B - 1, 1) for i in range(B)] if B > 1 else [(lo + hi) // 2]
     V = eng.config.vocab_size
     ids = [eng.add_request([g.randrange(V) for _ in range(n)],
                            SamplingParams(temperature=0.0, max_new_tokens=CONTEXT - n)) for n in lens]
@@ -243,6 +244,8 @@ def run_ours(args):
     nums = model_numbers(cfg)
     if args.workload == "mixed":
         return run_mixed(args, cfg)
+    if args.only == "long":
+        return run_long(args)
     if args.only == "table":
         return run_table(args)
     if args.only == "stream":
@@ -351,6 +354,65 @@ def run_table(args):
     for r in all_rows:
         print(f"| LFM2-{r['model'].upper()} | {r['point']} | {r['ms']} | {r['tokens_per_s']} | {r.get('e2e_ms', '')} | "
               f"{r.get('e2e_tokens_per_s', '')} | {r['work']} | {r['achieved']} | {r['frac_of_peak']} |")
+    return 0
+
+
+def run_long(args):
+    """Further context lengths (one shape, --model): a prompt of --context tokens prefilled in portions of 2048
+    (each portion timed: its products are the same, its attention grows with the cached context), and decode
+    steps at batch 8 with contexts spread over the upper half of --context."""
+    global CONTEXT
+    import torch
+    import zig_ai_b200 as z
+    from zig_ai_b200.config import config_from_dict
+    hbm_peak, flops_peak, peak_src = peaks()
+    cfg = config_from_dict(shape_config(args.model))
+    nums = model_numbers(cfg)
+    CONTEXT = args.context
+    B = 8
+    with tempfile.TemporaryDirectory(prefix="lfm2_long_") as d:
+        z.write_random_model(cfg, 0, d)
+        eng = z.Engine(d, "bfloat16", max_num_seqs=B, max_batched_tokens=2048 + 64, max_model_len=CONTEXT,
+                       max_tokens=(B + 1) * CONTEXT, page_size=args.page_size)
+        runner = eng.runner
+        g = random.Random(5)
+        Hq, D = nums["attn_dims"]
+        T = PREFILL_TOKENS
+        for rep in range(2):                                   # the first pass warms up (graphs of the portions' shapes are captured)
+            rid = f"long{rep}"
+            runner.add_request(rid)
+            portions = []
+            for c in range(CONTEXT // T):
+                toks = [g.randrange(cfg.vocab_size) for _ in range(T)]
+                start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                start.record()
+                runner.step([(rid, toks, [T - 1])])
+                stop.record()
+                torch.cuda.synchronize()
+                portions.append(start.elapsed_time(stop))
+            runner.end_request(rid)
+        total_ms = sum(portions)
+        # flops: every portion's products, and attention of its 2048 rows over the cached context and itself
+        products = 2 * T * nums["layer_params"] + 2 * nums["head_params"]
+        attn = [nums["n_attn"] * 2 * 2 * Hq * D * (T * c * T + T * T // 2) for c in range(CONTEXT // T)]
+        flops = len(portions) * products + sum(attn)
+        print(json.dumps({"only": "long", "model": args.model, "point": f"prefill {CONTEXT} in portions of {T}",
+                          "ms": round(total_ms, 2), "tokens_per_s": round(CONTEXT / total_ms * 1e3),
+                          "first_portion_ms": round(portions[0], 3), "last_portion_ms": round(portions[-1], 3),
+                          "tflop": round(flops / 1e12, 2), "achieved_tflops": round(flops / total_ms / 1e9),
+                          "frac_of_peak": round(flops / (total_ms * 1e-3) / (flops_peak * 1e12), 3),
+                          "last_portion_attention_share_of_flops": round(attn[-1] / (products + attn[-1]), 3),
+                          "last_portion_frac_of_peak": round((products + attn[-1]) / (portions[-1] * 1e-3) / (flops_peak * 1e12), 3),
+                          "peaks": peak_src}), flush=True)
+        weight_bytes = 2 * (nums["layer_params"] + nums["head_params"])
+        dev_ms, e2e_ms, ctx_tokens, launches, _, _, _ = time_decode(eng, B, max(args.steps, 20), args.warmup)
+        step_bytes = weight_bytes + ctx_tokens * nums["kv_bytes_per_token"] + B * nums["state_bytes"]
+        print(json.dumps({"only": "long", "model": args.model, "point": f"decode batch {B}", "mean_context": round(ctx_tokens / B),
+                          "ms": round(dev_ms, 4), "e2e_ms": round(e2e_ms, 4), "tokens_per_s": round(B / dev_ms * 1e3),
+                          "e2e_tokens_per_s": round(B / e2e_ms * 1e3), "gb": round(step_bytes / 1e9, 3),
+                          "achieved_gbs": round(step_bytes / dev_ms / 1e6),
+                          "frac_of_peak": round(step_bytes / (dev_ms * 1e-3) / 1e9 / hbm_peak, 3), "peaks": peak_src}), flush=True)
     return 0
 
 
@@ -571,7 +633,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "gemm", "timeline", "table", "stream"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "gemm", "timeline", "table", "stream", "long"],
                     help="profiling aid: run only the batch-8 decode steps or only the prefill (prints a short line); "
                          "table: every figure of the 350M, 700M and 1.2B shapes (profiles/measurements.md)")
     ap.add_argument("--batch", type=int, default=8, help="with --only decode: the batch size; with --only stream: 24, 64 or "
@@ -579,6 +641,7 @@ def main():
     ap.add_argument("--profile-range", action="store_true",
                     help="mark the device-timed decode steps for a profiler (ncu --profile-from-start off)")
     ap.add_argument("--page-size", type=int, default=64, help="positions per cache page")
+    ap.add_argument("--context", type=int, default=32768, help="with --only long: the context length (a multiple of 2048)")
     ap.add_argument("--model", default="350m", choices=sorted(SHAPES), help="which LFM2 shape (default: the 350M shape)")
     ap.add_argument("--workload", default="steps", choices=["steps", "mixed"],
                     help="mixed: 64 requests, chunked prefill interleaved with decoding, end to end")
