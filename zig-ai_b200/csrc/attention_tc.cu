@@ -4,25 +4,28 @@
 // over their requests' pages (cached positions and the step's own), optionally with a window, by
 // the online-softmax recurrence over tiles of keys (the reference computes the same sums with one
 // thread block per query row and head, src/cuda/paged_attention.cu:230-337).  What differs is where the products
-// run: a block owns 128 query rows of one head; per tile of 128 keys
+// run: a block owns 128 query rows of one head; per tile of 64 keys
 //
-//     S = Q K^T      tcgen05.mma, M = 128 (query rows = TMEM lanes), N = 128 keys, K = 64, into TMEM
-//     P = exp2(..)   four warps, one query row per thread: the row's 128 scores come from TMEM with
+//     S = Q K^T      tcgen05.mma, M = 128 (query rows = TMEM lanes), N = 64 keys, K = 64, into TMEM
+//     P = exp2(..)   four warps, one query row per thread: the row's 64 scores come from TMEM with
 //                    tcgen05.ld (no shuffles: a thread owns its row), the load of the next 32 columns
 //                    in flight while these are worked on; P goes back into TMEM (tcgen05.st, two
 //                    bfloat16 a column) as the next product's A operand
-//     O_t = P V      tcgen05.mma with A in TMEM, N = 64, K = 128 keys, V read straight from its page
+//     O_t = P V      tcgen05.mma with A in TMEM, N = 64, K = 64 keys, V read straight from its page
 //                    layout [key][64] as an MN-major operand, accumulated into O in TMEM; the threads
 //                    rescale O there only when a row's reference maximum has to move
+//
+// TMEM holds two score buffers and two P buffers (tile i uses buffer i & 1), so the products run a
+// tile ahead of the softmax: the scores of tile i + 2 are issued when the softmax has read those of
+// tile i, and the softmax of tile i + 1 finds its scores ready when it has written P of tile i.
 //
 // After a row's first tile the threads do not look for a tile's maximum first: they compute P against
 // the reference as it is and find the maximum on the way; only if it lies more than 2^8 above the
 // reference in some row of the warp does the reference move and the tile get walked again.
 //
 // Q, K and V reach shared memory by TMA (cp.async.bulk.tensor, no multicast), K and V page by page
-// through the block table into three stages.  Roles: warp 0 one lane issues the loads, warp 1 one lane
-// the products, warps 2-5 are the softmax.  As soon as P of a tile is written, the scores of the next
-// tile are issued (the softmax threads wait for those), then O_t.
+// through the block table into six stages of 16 KB.  Roles: warp 0 one lane issues the loads, warp 1
+// one lane the products, warps 2-5 are the softmax.
 //
 // Blocks are handed out heads first, tiles of query rows from the last rows backwards: under the causal
 // mask the last rows of a long span walk many more key tiles than the first, a block's tiles are a chain
@@ -34,15 +37,15 @@
 
 #define AT_D 64
 #define AT_BM 128
-#define AT_BN 128
+#define AT_BN 64
 #define AT_THREADS 192
-#define AT_STAGES 3
+#define AT_STAGES 6
 #define AT_SPIN_LIMIT 4000000
 #define AT_Q_BYTES (AT_BM * AT_D * 2)                 // 16 KB
-#define AT_KV_BYTES (2 * AT_BN * AT_D * 2)            // keys then values: 32 KB
-#define AT_TMEM_COLS 256                              // scores in columns 0..127, O in 128..191, P in 192..255
-#define AT_COL_O AT_BN
-#define AT_COL_P (AT_BN + AT_D)
+#define AT_KV_BYTES (2 * AT_BN * AT_D * 2)            // keys then values: 16 KB
+#define AT_TMEM_COLS 256                              // two score buffers in columns 0..127, O in 128..191, two P buffers in 192..255
+#define AT_COL_O (2 * AT_BN)
+#define AT_COL_P (2 * AT_BN + AT_D)
 
 __device__ __forceinline__ uint32_t at_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void at_mbar_init(uint64_t* bar, int count) {
@@ -65,6 +68,12 @@ __device__ __forceinline__ bool at_mbar_wait(uint64_t* bar, uint32_t parity, vol
     }
     *failed = 1;
     return false;
+}
+// A warp's wait: lane 0 watches the barrier, the others hear the outcome.
+__device__ __forceinline__ bool at_mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* failed) {
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = at_mbar_wait(bar, parity, failed) ? 1 : 0;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 __device__ __forceinline__ void at_tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -156,8 +165,8 @@ struct AtArgs {
 
 __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                 const __grid_constant__ CUtensorMap map_kv, const AtArgs a) {
-    // All shared memory is dynamic and the tiles come first: 112 KB of tiles, 128 bytes of barriers and
-    // words, and the 1 KB the system reserves per block make 115,840 bytes, so that two blocks fit
+    // All shared memory is dynamic and the tiles come first: 112 KB of tiles, 256 bytes of barriers and
+    // words, and the 1 KB the system reserves per block make 115,968 bytes, so that two blocks fit
     // an SM's 233,472 (with a kilobyte of static variables or of alignment slack they would not).
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* base = smem_raw;
@@ -167,11 +176,11 @@ __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_con
     uint64_t& q_full = bars[0];
     uint64_t* kv_full = bars + 1;                               // [AT_STAGES]
     uint64_t* kv_empty = bars + 1 + AT_STAGES;                  // [AT_STAGES]
-    uint64_t& s_ready = bars[1 + 2 * AT_STAGES];
-    uint64_t& p_ready = bars[2 + 2 * AT_STAGES];
-    uint64_t& o_ready = bars[3 + 2 * AT_STAGES];
-    uint32_t& tmem_base_holder = *reinterpret_cast<uint32_t*>(bars + 4 + 2 * AT_STAGES);
-    int* words = reinterpret_cast<int*>(bars + 5 + 2 * AT_STAGES);
+    uint64_t* s_ready = bars + 1 + 2 * AT_STAGES;               // [2] scores of tile i in buffer i & 1
+    uint64_t* p_ready = bars + 3 + 2 * AT_STAGES;               // [2] P of tile i in buffer i & 1
+    uint64_t* o_ready = bars + 5 + 2 * AT_STAGES;               // [2] the product of tile i has read P buffer i & 1 and added to O
+    uint32_t& tmem_base_holder = *reinterpret_cast<uint32_t*>(bars + 7 + 2 * AT_STAGES);
+    int* words = reinterpret_cast<int*>(bars + 8 + 2 * AT_STAGES);
     int& failed_flag = words[0];
     int& s_seq = words[1];
     int& s_i0 = words[2];
@@ -185,9 +194,11 @@ __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_con
             at_mbar_init(&kv_full[s], 1);
             at_mbar_init(&kv_empty[s], 1);
         }
-        at_mbar_init(&s_ready, 1);
-        at_mbar_init(&p_ready, 4);                              // one arrival per softmax warp
-        at_mbar_init(&o_ready, 1);
+        for (int b = 0; b < 2; ++b) {
+            at_mbar_init(&s_ready[b], 1);
+            at_mbar_init(&p_ready[b], 4);                       // one arrival per softmax warp
+            at_mbar_init(&o_ready[b], 1);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -274,40 +285,42 @@ __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_con
             }
         } else if (warp == 1) {
             if (lane == 0 && n_tiles > 0) {
-                // ---- products.  Instruction descriptors: D 32-bit, A and B bfloat16, M = 128; the scores
-                // have N = 128 and both operands K-major; O_t has N = 64, A (P) in TMEM and B (the values)
-                // MN-major.
+                // ---- products.  Instruction descriptors: D 32-bit, A and B bfloat16, M = 128, N = 64; the
+                // scores have both operands K-major; O_t has A (P) in TMEM and B (the values) MN-major.
                 constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(AT_BN >> 3) << 17) | ((uint32_t)(AT_BM >> 4) << 24);
                 constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(AT_D >> 3) << 17) |
                                              ((uint32_t)(AT_BM >> 4) << 24);
                 const uint32_t tS = tmem_base, tO = tmem_base + AT_COL_O, tP = tmem_base + AT_COL_P;
                 const uint32_t aQ = at_smem(sQ);
                 bool ok = at_mbar_wait(&q_full, 0, failed);
-                auto scores = [&](int i) {                      // S = Q K^T of tile i
+                auto scores = [&](int i) {                      // S = Q K^T of tile i into score buffer i & 1
                     const int st = i % AT_STAGES;
                     if (!at_mbar_wait(&kv_full[st], (i / AT_STAGES) & 1, failed)) return false;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t aK = at_smem(sKV + (size_t)st * AT_KV_BYTES);
 #pragma unroll
-                    for (int k = 0; k < AT_D / 16; ++k) at_umma(tS, at_desc(aQ + k * 32), at_desc(aK + k * 32), idesc_s, k > 0 ? 1u : 0u);
-                    at_commit(&s_ready);
+                    for (int k = 0; k < AT_D / 16; ++k)
+                        at_umma(tS + (i & 1) * AT_BN, at_desc(aQ + k * 32), at_desc(aK + k * 32), idesc_s, k > 0 ? 1u : 0u);
+                    at_commit(&s_ready[i & 1]);
                     return true;
                 };
+                // the scores run a tile ahead of the softmax: those of tile i + 2 are issued when the softmax
+                // has read those of tile i (same buffer), so tile i + 1's are ready when the softmax of
+                // tile i ends
                 if (ok) ok = scores(0);
+                if (ok && n_tiles > 1) ok = scores(1);
                 for (int i = 0; i < n_tiles && ok; ++i) {
                     const int st = i % AT_STAGES;
-                    ok = at_mbar_wait(&p_ready, i & 1, failed);
+                    ok = at_mbar_wait(&p_ready[i & 1], (i >> 1) & 1, failed);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    // P lies in TMEM beside the scores, which the softmax threads have read: the next
-                    // tile's scores go first (the threads wait for them), then this tile's O_t
-                    if (i + 1 < n_tiles) ok = scores(i + 1);
                     const uint32_t aV = at_smem(sKV + (size_t)st * AT_KV_BYTES + AT_BN * 128);
 #pragma unroll
                     for (int kk = 0; kk < AT_BN / 16; ++kk)     // 16 keys a step: eight columns of P, two groups of 8 keys of V
-                        at_umma_ts(tO, tP + kk * 8, at_desc(aV + kk * 2048), idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
-                    at_commit(&o_ready);
+                        at_umma_ts(tO, tP + (i & 1) * (AT_BN / 2) + kk * 8, at_desc(aV + kk * 2048), idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+                    at_commit(&o_ready[i & 1]);
                     at_commit(&kv_empty[st]);
+                    if (i + 2 < n_tiles) ok = scores(i + 2);
                 }
             }
         } else if (n_tiles > 0) {
@@ -326,31 +339,33 @@ __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_con
             bool alive = true;
             for (int i = 0; i < n_tiles && alive; ++i) {
                 const int key0 = (tile0 + i) * AT_BN;
-                if (!__all_sync(0xffffffffu, at_mbar_wait(&s_ready, i & 1, failed))) { alive = false; break; }    // (the warp leaves together)
+                if (!at_mbar_wait_warp(&s_ready[i & 1], (i >> 1) & 1, failed)) { alive = false; break; }    // (the warp leaves together)
+                const uint32_t tSi = tS + (i & 1) * AT_BN, tPi = tP + (i & 1) * (AT_BN / 2);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 // keys of this tile that the row sees: [lo, hi)
                 const int lo = valid ? max(klo - key0, 0) : AT_BN, hi = valid ? min(qpos + 1 - key0, AT_BN) : 0;
                 const bool full = lo <= 0 && hi >= AT_BN;       // the row sees the whole tile: no masking needed
-                // one walk over the row's 128 scores in chunks of 32 columns, the load of the next chunk in
+                // one walk over the row's 64 scores in chunks of 32 columns, the load of the next chunk in
                 // flight while this one is worked on: the maximum of the visible scores (`mx`), and with
                 // `emit` the probabilities against `ref` into P and their sum (`lt`)
                 auto walk = [&](bool emit, float ref, float& mx, float& lt) {
                     uint32_t r[2][32];
-                    at_tmem_ld32_nowait(tS, r[0]);
+                    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY}, lt4[4] = {0.f, 0.f, 0.f, 0.f};   // four chains each, not one of 64 links
+                    at_tmem_ld32_nowait(tSi, r[0]);
 #pragma unroll
                     for (int k = 0; k < AT_BN / 32; ++k) {
                         at_tmem_wait_ld(r[k & 1]);
-                        if (k + 1 < AT_BN / 32) at_tmem_ld32_nowait(tS + 32 * (k + 1), r[(k + 1) & 1]);
+                        if (k + 1 < AT_BN / 32) at_tmem_ld32_nowait(tSi + 32 * (k + 1), r[(k + 1) & 1]);
                         const uint32_t (&x)[32] = r[k & 1];
                         const int c0 = 32 * k;
                         if (!emit) {
                             if (full) {
 #pragma unroll
-                                for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(x[j]));
+                                for (int j = 0; j < 32; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(x[j]));
                             } else {
 #pragma unroll
                                 for (int j = 0; j < 32; ++j)
-                                    if (c0 + j >= lo && c0 + j < hi) mx = fmaxf(mx, __uint_as_float(x[j]));
+                                    if (c0 + j >= lo && c0 + j < hi) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(x[j]));
                             }
                             continue;
                         }
@@ -359,9 +374,9 @@ __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_con
 #pragma unroll
                             for (int j = 0; j < 32; j += 2) {
                                 const float s0 = __uint_as_float(x[j]), s1 = __uint_as_float(x[j + 1]);
-                                mx = fmaxf(mx, fmaxf(s0, s1));
+                                mx4[(j >> 1) & 3] = fmaxf(mx4[(j >> 1) & 3], fmaxf(s0, s1));
                                 const float p0 = at_exp2(s0 * c - ref), p1 = at_exp2(s1 * c - ref);
-                                lt += p0 + p1;
+                                lt4[(j >> 1) & 3] += p0 + p1;
                                 __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
                                 pk[j >> 1] = *reinterpret_cast<uint32_t*>(&v);
                             }
@@ -372,21 +387,20 @@ __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_con
                                 const int k0 = c0 + j;
                                 const bool v0 = k0 >= lo && k0 < hi, v1 = k0 + 1 >= lo && k0 + 1 < hi;
                                 const float s0 = v0 ? __uint_as_float(x[j]) : -INFINITY, s1 = v1 ? __uint_as_float(x[j + 1]) : -INFINITY;
-                                mx = fmaxf(mx, fmaxf(s0, s1));
+                                mx4[(j >> 1) & 3] = fmaxf(mx4[(j >> 1) & 3], fmaxf(s0, s1));
                                 const float p0 = at_exp2(s0 * c - ref), p1 = at_exp2(s1 * c - ref);
-                                lt += p0 + p1;
+                                lt4[(j >> 1) & 3] += p0 + p1;
                                 __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
                                 pk[j >> 1] = *reinterpret_cast<uint32_t*>(&v);
                             }
                         }
-                        if (k == 0 && i > 0) {
-                            // P of the tile before must have been read by its product, which was issued behind
-                            // this tile's scores: the wait comes after the first chunk's arithmetic, not before
-                            if (!__all_sync(0xffffffffu, at_mbar_wait(&o_ready, (i - 1) & 1, failed))) alive = false;
-                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                        }
-                        at_tmem_st16(tP + 16 * k, pk);          // 32 keys = 16 columns of P
+                        // (This P buffer was read by the product of the tile two before.  That product was issued
+                        // before this tile's scores, and the commit behind the scores covers every product issued
+                        // before it: the scores being ready says the buffer is free.)
+                        at_tmem_st16(tPi + 16 * k, pk);         // 32 keys = 16 columns of P
                     }
+                    mx = fmaxf(mx, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])));
+                    lt += (lt4[0] + lt4[1]) + (lt4[2] + lt4[3]);
                 };
                 // With a reference in every row of the warp, the tile is walked once against it; else the
                 // maximum is found first, as a walk of its own.
@@ -405,7 +419,7 @@ __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_con
                 }
                 const bool moved = __any_sync(0xffffffffu, alpha != 1.f);
                 if (i > 0 && moved) {
-                    if (!__all_sync(0xffffffffu, at_mbar_wait(&o_ready, (i - 1) & 1, failed))) { alive = false; break; }   // the product before has added to O
+                    if (!at_mbar_wait_warp(&o_ready[(i - 1) & 1], ((i - 1) >> 1) & 1, failed)) { alive = false; break; }   // the product before (and with it all before) has added to O
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                     for (int c0 = 0; c0 < AT_D; c0 += 32) {
@@ -428,9 +442,9 @@ __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_con
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) at_mbar_arrive(&p_ready);
+                if (lane == 0) at_mbar_arrive(&p_ready[i & 1]);
             }
-            if (alive && __all_sync(0xffffffffu, at_mbar_wait(&o_ready, (n_tiles - 1) & 1, failed))) {
+            if (alive && at_mbar_wait_warp(&o_ready[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, failed)) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const float inv = l > 0.f ? 1.f / l : 0.f;
                 bf16* dst = a.out + ((size_t)(row0 + i0 + row) * a.Hq + h) * AT_D;
@@ -488,10 +502,11 @@ static int at_make_map(CUtensorMap* map, const void* ptr, cuuint64_t cols, cuuin
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS ? 0 : -6;
 }
 
-// 1 if this kernel takes the sizes: head size 64, a page size that is a power of two from 8 to 128
+// 1 if this kernel takes the sizes: head size 64, a page size that is a power of two from 8 to 128 (a tile
+// of 64 keys is loaded page by page, or as half of a page of 128)
 ZAI_API int zai_prefill_attention_tc_supports(int D, int Hq, int Hkv, int page_size) {
     if (D != AT_D || Hkv < 1 || Hq % Hkv != 0 || Hq > 32767) return 0;
-    if (page_size < 8 || page_size > AT_BN || (page_size & (page_size - 1))) return 0;
+    if (page_size < 8 || page_size > 128 || (page_size & (page_size - 1))) return 0;
     return at_encode_tiled() != nullptr;
 }
 
@@ -517,7 +532,7 @@ ZAI_API int zai_prefill_attention_tc(void* out, const void* q, const void* pages
     a.scale_log2 = scale * 1.4426950408889634f;
     a.page_shift = 0;
     while ((1 << a.page_shift) < page_size) ++a.page_shift;
-    const size_t smem = AT_Q_BYTES + (size_t)AT_STAGES * AT_KV_BYTES + 128;
+    const size_t smem = AT_Q_BYTES + (size_t)AT_STAGES * AT_KV_BYTES + 256;
     static unsigned long long configured = 0;
     if (zai_first_on_device(&configured)) {
         cudaError_t err = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
