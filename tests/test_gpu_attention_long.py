@@ -75,6 +75,60 @@ def test_span_attention_at_the_benchmark_sizes(impl, ctx, q_len, ps, window):
     assert o.read_status() == 0
 
 
+@pytest.mark.parametrize("ps,window,padded", [(64, None, 0), (16, None, 3), (128, 5000, 0), (32, 700, 1)])
+def test_span_attention_few_rows_over_long_contexts(ps, window, padded):
+    """Few tiles of query rows over long contexts: several blocks share a tile's keys, leave their parts in
+    scratch, and the one with the last ticket combines them.  Requests of 40 rows behind 16 000 positions
+    (every block has keys), 3 rows behind 5 (all blocks but one have none), 130 rows behind 700 and 1 row
+    behind 9000; a planted key on both sides of the boundaries between the blocks' shares; twice in a row
+    (the tickets must be zero again), and with more tiles launched than the step has (a captured graph's
+    grid is sized for its bucket)."""
+    o = ops()
+    from zig_ai_b200.kernels import ops as ops_module
+    g = torch.Generator().manual_seed(71)
+    ctx, q_lens = [16000, 5, 700, 9000], [40, 3, 130, 1]
+    num_pages = sum(-(-(c + n) // ps) for c, n in zip(ctx, q_lens)) + 8
+    step = make_step(o, BF16, ctx, q_lens, ps, num_pages, 72)
+    pages = fill_pages(step, ctx, q_lens, ps, Hkv, D, BF16, num_pages, g)
+    q = torch.randn(sum(q_lens), Hq * D, generator=g).to(BF16).cuda()
+    n_tiles = sum(-(-n // 128) for n in q_lens)
+    lib_splits = ops_module._fn("attention_tc", "zai_prefill_attention_tc_splits")(n_tiles + padded, Hq, step.block_tables[0].shape[1], ps)
+    assert lib_splits > 1                                            # the case is one the shared tiles are made for
+    key_tiles = -(-(ctx[0] + q_lens[0]) // 64)
+    per = -(-key_tiles // lib_splits)
+    starts = [0] + q_lens[:-1]
+    row_of = [sum(q_lens[:i]) for i in range(len(q_lens))]
+    planted = set()
+    # request 0: one key per share boundary (last key of a share, first key of the next), seen by different rows and heads
+    for z in range(1, lib_splits):
+        for d, r in ((-1, (2 * z) % q_lens[0]), (0, (2 * z + 1) % q_lens[0])):
+            pos = z * per * 64 + d
+            if window is not None and pos < ctx[0] + r - window + 1:
+                continue
+            h = (z + d) % Hq
+            if (pos, h // G) in planted:
+                continue
+            planted.add((pos, h // G))
+            plant_key(pages, step, ps, 0, pos, h // G, q[row_of[0] + r, h * D:(h + 1) * D].float() * 3.0, distinct_value(z * 2 + d + 1))
+    # the other requests: their first and last visible keys
+    for s_i in (1, 2, 3):
+        r = q_lens[s_i] - 1
+        last = ctx[s_i] + r
+        lo = 0 if window is None else max(last - window + 1, 0)
+        for pos, h in ((lo, 1), (last, 2 + s_i)):
+            plant_key(pages, step, ps, s_i, pos, h // G, q[row_of[s_i] + r, h * D:(h + 1) * D].float() * 3.0, distinct_value(40 + 2 * s_i + h))
+    view = CacheView(0, pages, step.block_tables[0], ps)
+    if padded:
+        step.attn_tiles = n_tiles + padded
+    want = ref_ops.paged_attention(q, step, view, Hq, Hkv, D, D ** -0.5, window)
+    assert want.float().abs().max() > 5.0
+    for _ in range(2):
+        got = o.paged_attention(q, step, view, Hq, Hkv, D, D ** -0.5, window, impl="tcgen05")
+        assert torch.allclose(got.float(), want.float(), atol=3e-2, rtol=3e-2), (got.float() - want.float()).abs().max()
+        assert int(ops_module._tickets[q.device].abs().sum()) == 0
+    assert o.read_status() == 0
+
+
 @pytest.mark.parametrize("tma", [True, False])
 @pytest.mark.parametrize("ps,window", [(64, None), (16, None), (64, 1500)])
 def test_decode_attention_batch_64_at_contexts_2048_to_4095(tma, ps, window):

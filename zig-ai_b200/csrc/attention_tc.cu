@@ -161,8 +161,16 @@ struct AtArgs {
     int num_pages;
     int table_width, S, page_size, page_shift, Hq, Hkv, window;
     float scale_log2;
+    // With few tiles of query rows and long contexts, `splits` blocks (grid z) share a tile's key range; each
+    // leaves its O [64][128], its rows' references and sums here, and the one that takes the last ticket of
+    // the tile combines them (no block waits for another).
+    int splits;
+    float* part_o;              // [tiles of query rows x heads x splits][64][128]
+    float* part_ml;             // [tiles of query rows x heads x splits][2][128]: reference (in the exponent's units), sum
+    int* tickets;               // [tiles of query rows x heads], zero between launches
 };
 
+template <bool SHARED>               // several blocks (grid z) share a tile of query rows' keys
 __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                 const __grid_constant__ CUtensorMap map_kv, const AtArgs a) {
     // All shared memory is dynamic and the tiles come first: 112 KB of tiles, 256 bytes of barriers and
@@ -227,13 +235,25 @@ __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_con
     }
     __syncthreads();
     const int s = s_seq, i0 = s_i0;
+    const int h = blockIdx.x;
+    // the softmax threads' state, kept past the roles for a shared tile's combination
+    float m = -INFINITY, l = 0.f;                               // m: the row's reference, in units of the scores
+    bool have_o = false;                                        // the row's O in TMEM is complete
+    int row0 = 0, rows = 0;
     if (s < a.S && !failed_flag) {
-        const int h = blockIdx.x, hk = h / (a.Hq / a.Hkv);
-        const int row0 = a.cu_q[s], q_len = a.cu_q[s + 1] - row0, ctx = a.ctx_lens[s];
-        const int rows = min(AT_BM, q_len - i0);                    // valid query rows of this block
+        const int hk = h / (a.Hq / a.Hkv);
+        row0 = a.cu_q[s];
+        const int q_len = a.cu_q[s + 1] - row0, ctx = a.ctx_lens[s];
+        rows = min(AT_BM, q_len - i0);                              // valid query rows of this block
         const int kend = ctx + i0 + rows;                           // one past the last visible key of the block
         const int kbeg = a.window > 0 ? max(ctx + i0 - a.window + 1, 0) : 0;
-        const int tile0 = kbeg / AT_BN, tile1 = (kend + AT_BN - 1) / AT_BN, n_tiles = tile1 - tile0;
+        int tile0 = kbeg / AT_BN, tile1 = (kend + AT_BN - 1) / AT_BN;
+        if (SHARED) {                                               // this block's share of the key tiles
+            const int per = (tile1 - tile0 + a.splits - 1) / a.splits;
+            tile0 = min(tile0 + (int)blockIdx.z * per, tile1);
+            tile1 = min(tile0 + per, tile1);
+        }
+        const int n_tiles = tile1 - tile0;
 
         if (warp == 0) {
             if (lane == 0 && n_tiles > 0) {
@@ -335,7 +355,6 @@ __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_con
             const int klo = a.window > 0 ? max(qpos - a.window + 1, 0) : 0;
             const uint32_t tS = tmem_base + ((uint32_t)(qd * 32) << 16), tO = tS + AT_COL_O, tP = tS + AT_COL_P;
             const float c = a.scale_log2;
-            float m = -INFINITY, l = 0.f;                       // m: the row's reference, in units of the scores
             bool alive = true;
             for (int i = 0; i < n_tiles && alive; ++i) {
                 const int key0 = (tile0 + i) * AT_BN;
@@ -446,10 +465,11 @@ __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_con
             }
             if (alive && at_mbar_wait_warp(&o_ready[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, failed)) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                have_o = true;
                 const float inv = l > 0.f ? 1.f / l : 0.f;
                 bf16* dst = a.out + ((size_t)(row0 + i0 + row) * a.Hq + h) * AT_D;
 #pragma unroll
-                for (int c0 = 0; c0 < AT_D; c0 += 32) {
+                for (int c0 = 0; c0 < AT_D && !SHARED; c0 += 32) {
                     uint32_t r[32];
                     at_tmem_ld32(tO + c0, r);
                     if (valid) {
@@ -467,6 +487,64 @@ __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_con
                     }
                 }
             }
+        }
+    }
+    if (SHARED && s < a.S && warp >= 2) {
+        // ---- a shared tile of query rows: this block's part into memory, a ticket, and the last one combines
+        const int qd = warp & 3, row = qd * 32 + lane;
+        const uint32_t tO = tmem_base + ((uint32_t)(qd * 32) << 16) + AT_COL_O;
+        const int slot = ((int)gridDim.y - 1 - (int)blockIdx.y) * a.Hq + h;
+        const size_t mine = (size_t)slot * a.splits + blockIdx.z;
+        float* po = a.part_o + mine * (AT_D * AT_BM);
+        float* pml = a.part_ml + mine * (2 * AT_BM);
+        const bool ok = have_o && !failed_flag;                 // (a block without key tiles, or one that gave up, has no part)
+        pml[row] = (ok && m != -INFINITY) ? m * a.scale_log2 : -INFINITY;
+        pml[AT_BM + row] = ok ? l : 0.f;
+        if (ok) {
+#pragma unroll
+            for (int c0 = 0; c0 < AT_D; c0 += 32) {
+                uint32_t r[32];
+                at_tmem_ld32(tO + c0, r);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) po[(c0 + j) * AT_BM + row] = __uint_as_float(r[j]);
+            }
+        }
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");          // the four softmax warps
+        if (tid == 64) s_seq = atomicAdd(a.tickets + slot, 1);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (s_seq == a.splits - 1) {
+            __threadfence();
+            float top = -INFINITY, sum = 0.f, acc[AT_D];
+#pragma unroll
+            for (int d = 0; d < AT_D; ++d) acc[d] = 0.f;
+            for (int z = 0; z < a.splits; ++z) {
+                const size_t other = (size_t)slot * a.splits + z;
+                const volatile float* qml = a.part_ml + other * (2 * AT_BM);
+                const float mz = qml[row], lz = qml[AT_BM + row];
+                if (mz == -INFINITY) continue;                  // nothing from this part (its O may be unwritten)
+                const float ntop = fmaxf(top, mz);
+                const float f_old = top == -INFINITY ? 0.f : at_exp2(top - ntop), f_new = at_exp2(mz - ntop);
+                const volatile float* qo = a.part_o + other * (AT_D * AT_BM);
+                sum = sum * f_old + lz * f_new;
+#pragma unroll
+                for (int d = 0; d < AT_D; ++d) acc[d] = acc[d] * f_old + qo[d * AT_BM + row] * f_new;
+                top = ntop;
+            }
+            const float inv = sum > 0.f ? 1.f / sum : 0.f;
+            if (row < rows) {
+                bf16* dst = a.out + ((size_t)(row0 + i0 + row) * a.Hq + h) * AT_D;
+#pragma unroll
+                for (int d = 0; d < AT_D; d += 8) {
+                    uint4 v;
+                    __nv_bfloat162 p0 = __floats2bfloat162_rn(acc[d] * inv, acc[d + 1] * inv), p1 = __floats2bfloat162_rn(acc[d + 2] * inv, acc[d + 3] * inv);
+                    __nv_bfloat162 p2 = __floats2bfloat162_rn(acc[d + 4] * inv, acc[d + 5] * inv), p3 = __floats2bfloat162_rn(acc[d + 6] * inv, acc[d + 7] * inv);
+                    v.x = *reinterpret_cast<uint32_t*>(&p0); v.y = *reinterpret_cast<uint32_t*>(&p1);
+                    v.z = *reinterpret_cast<uint32_t*>(&p2); v.w = *reinterpret_cast<uint32_t*>(&p3);
+                    *reinterpret_cast<uint4*>(dst + d) = v;
+                }
+            }
+            if (tid == 64) a.tickets[slot] = 0;                 // ready for the next launch
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -510,14 +588,31 @@ ZAI_API int zai_prefill_attention_tc_supports(int D, int Hq, int Hkv, int page_s
     return at_encode_tiled() != nullptr;
 }
 
+// How many blocks should share a tile of query rows' keys: 1 when the tiles alone fill the SMs (two blocks
+// each) or the contexts are short; else enough to fill them, with at least eight key tiles for each at the
+// longest context a block-table row holds, and 16 at most.
+ZAI_API int zai_prefill_attention_tc_splits(int n_tiles, int Hq, int table_width, int page_size) {
+    int sms = 148, dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long blocks = (long long)n_tiles * Hq, places = 2LL * sms;
+    if (blocks <= 0 || 2 * blocks > places) return 1;
+    long long want = (places + blocks - 1) / blocks;
+    const long long key_tiles = ((long long)table_width * page_size + AT_BN - 1) / AT_BN;
+    if (want > key_tiles / 8) want = key_tiles / 8;
+    if (want > 16) want = 16;
+    return want < 2 ? 1 : (int)want;
+}
+
 // out [N, Hq, 64] = attention of q [N, Hq, 64] (N rows in all, `n_tiles` blocks of 128 rows over the
 // requests' spans) over the pages [num_pages, 2, Hkv, page_size, 64]; arguments as
 // zai_prefill_attention_mma, plus the row and page counts and the status word that a block raises
-// if one of its waits ran out or a page id lay outside the pool.
+// if one of its waits ran out or a page id lay outside the pool.  With splits > 1 (zai_prefill_attention_tc_splits
+// proposes a number) the caller gives the scratch for the parts: part_o [n_tiles * Hq * splits * 64 * 128]
+// and part_ml [n_tiles * Hq * splits * 2 * 128] floats, and tickets [n_tiles * Hq] ints that are zero.
 ZAI_API int zai_prefill_attention_tc(void* out, const void* q, const void* pages, int num_pages, int* status,
                                      const int* block_table, int table_width, const int* cu_q, const int* ctx_lens, int N,
                                      int S, int n_tiles, int page_size, int Hq, int Hkv, int D, float scale, int window,
-                                     cudaStream_t stream) {
+                                     int splits, float* part_o, float* part_ml, int* tickets, cudaStream_t stream) {
     if (N <= 0 || S <= 0 || n_tiles <= 0) return ZAI_OK;
     if (!zai_prefill_attention_tc_supports(D, Hq, Hkv, page_size) || n_tiles > 65535) return ZAI_BAD_SIZE;
     if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(pages) | reinterpret_cast<uintptr_t>(out)) & 15) return ZAI_BAD_SIZE;
@@ -530,16 +625,20 @@ ZAI_API int zai_prefill_attention_tc(void* out, const void* q, const void* pages
     a.out = (bf16*)out; a.block_table = block_table; a.cu_q = cu_q; a.ctx_lens = ctx_lens; a.status = status; a.num_pages = num_pages;
     a.table_width = table_width; a.S = S; a.page_size = page_size; a.Hq = Hq; a.Hkv = Hkv; a.window = window;
     a.scale_log2 = scale * 1.4426950408889634f;
+    if (splits < 1 || splits > 64 || (splits > 1 && (!part_o || !part_ml || !tickets))) return ZAI_BAD_SIZE;
+    a.splits = splits; a.part_o = part_o; a.part_ml = part_ml; a.tickets = tickets;
     a.page_shift = 0;
     while ((1 << a.page_shift) < page_size) ++a.page_shift;
     const size_t smem = AT_Q_BYTES + (size_t)AT_STAGES * AT_KV_BYTES + 256;
     static unsigned long long configured = 0;
     if (zai_first_on_device(&configured)) {
-        cudaError_t err = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (err != cudaSuccess) return (int)err;
+        cudaError_t err = cudaFuncSetAttribute(prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err == cudaSuccess) err = cudaFuncSetAttribute(prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         // two blocks per SM: ask for the largest shared-memory carve-out
-        err = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        if (err == cudaSuccess) err = cudaFuncSetAttribute(prefill_tc_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        if (err == cudaSuccess) err = cudaFuncSetAttribute(prefill_tc_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         if (err != cudaSuccess) return (int)err;
     }
-    return launch_pdl(prefill_tc_kernel, dim3(Hq, n_tiles), dim3(AT_THREADS), smem, stream, mq, mkv, a);
+    if (splits > 1) return launch_pdl(prefill_tc_kernel<true>, dim3(Hq, n_tiles, splits), dim3(AT_THREADS), smem, stream, mq, mkv, a);
+    return launch_pdl(prefill_tc_kernel<false>, dim3(Hq, n_tiles), dim3(AT_THREADS), smem, stream, mq, mkv, a);
 }

@@ -79,7 +79,8 @@ _SIGNATURES = {
     },
     "attention_tc": {
         "zai_prefill_attention_tc_supports": [_I, _I, _I, _I],
-        "zai_prefill_attention_tc": [_P, _P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+        "zai_prefill_attention_tc": [_P, _P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P, _P, _P],
+        "zai_prefill_attention_tc_splits": [_I, _I, _I, _I],
     },
     "sampling": {
         "zai_argmax": [_P, _P, _I, _I, _P, _P],
@@ -707,6 +708,18 @@ def kv_write(k, v, step, cache, kv_heads, head_dim):
 USE_TC_ATTENTION = os.environ.get("ZAI_TC_ATTENTION", "1") == "1"     # tcgen05 prefill attention where the sizes allow
 
 
+
+_tickets = {}
+
+
+def _attention_tickets(device, n):
+    """Zeroed counters for the span attention's shared tiles (the kernel leaves them zero)."""
+    t = _tickets.get(device)
+    if t is None or t.numel() < n:
+        t = torch.zeros((max(n, 1024),), dtype=torch.int32, device=device)
+        _tickets[device] = t
+    return t
+
 @_timed("attention")
 def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=None, impl=None):
     """Causal attention of the step's rows over their requests' pages.  bfloat16 runs on the
@@ -748,10 +761,19 @@ def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=Non
             n_tiles = (step.attn_tiles - ns) if getattr(step, "attn_tiles", None) else sum(-(-n // block_rows) for n in step.q_lens[ns:])
             if (impl != "mma" and (USE_TC_ATTENTION or impl == "tcgen05") and q.is_contiguous()
                     and _fn("attention_tc", "zai_prefill_attention_tc_supports")(head_dim, heads, kv_heads, cache.page_size)):
+                # few tiles of query rows over long contexts: several blocks share a tile's keys and leave their
+                # parts in scratch, the last to finish combines them (tickets: zero before and after)
+                splits = _fn("attention_tc", "zai_prefill_attention_tc_splits")(n_tiles, heads, bt.shape[1], cache.page_size)
+                part_o = part_ml = tickets = None
+                if splits > 1:
+                    part_o = torch.empty((n_tiles * heads * splits, 64 * 128), dtype=torch.float32, device=q.device)
+                    part_ml = torch.empty((n_tiles * heads * splits, 2 * 128), dtype=torch.float32, device=q.device)
+                    tickets = _attention_tickets(q.device, n_tiles * heads)
                 _check(_fn("attention_tc", "zai_prefill_attention_tc")(
                     _ptr(out), _ptr(q), _ptr(cache.pages), cache.pages.shape[0], _status_ptr(q.device), _ptr(bt), bt.shape[1],
                     _ptr(cu_q), _ptr(ctx_lens), N, S, n_tiles, cache.page_size, heads, kv_heads,
-                    head_dim, float(scale), int(window or 0), _stream()), "prefill attention (tcgen05)")
+                    head_dim, float(scale), int(window or 0), splits, _ptr(part_o), _ptr(part_ml), _ptr(tickets),
+                    _stream()), "prefill attention (tcgen05)")
                 return out
             _check(_fn("attention_mma", "zai_prefill_attention_mma")(
                 _ptr(out), _ptr(q), _ptr(cache.pages), _ptr(bt), bt.shape[1], _ptr(cu_q), _ptr(ctx_lens),
