@@ -592,8 +592,12 @@ ZAI_API int zai_prefill_attention_tc_supports(int D, int Hq, int Hkv, int page_s
 // each) or the contexts are short; else enough to fill them, with at least eight key tiles for each at the
 // longest context a block-table row holds, and 16 at most.
 ZAI_API int zai_prefill_attention_tc_splits(int n_tiles, int Hq, int table_width, int page_size) {
-    int sms = 148, dev = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) sms = n;
+        else sms = 148;
+    }
     const long long blocks = (long long)n_tiles * Hq, places = 2LL * sms;
     if (blocks <= 0 || 2 * blocks > places) return 1;
     long long want = (places + blocks - 1) / blocks;

@@ -347,6 +347,8 @@ _last_weight = [0]
 def _hint_next_weights(w) -> None:
     p = w.data_ptr()
     last = _last_weight[0]
+    if len(_follower) > 8192:                     # many models have come and gone: start over
+        _follower.clear()
     if last and last != p:
         known = _follower.get(last)
         if known is None or known() is not w:
@@ -764,11 +766,11 @@ def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=Non
                 # few tiles of query rows over long contexts: several blocks share a tile's keys and leave their
                 # parts in scratch, the last to finish combines them (tickets: zero before and after)
                 splits = _fn("attention_tc", "zai_prefill_attention_tc_splits")(n_tiles, heads, bt.shape[1], cache.page_size)
-                part_o = part_ml = tickets = None
+                part_o = part_ml = None
+                tickets = _attention_tickets(q.device, n_tiles * heads if splits > 1 else 0)   # (made at the first call, which no graph captures)
                 if splits > 1:
                     part_o = torch.empty((n_tiles * heads * splits, 64 * 128), dtype=torch.float32, device=q.device)
                     part_ml = torch.empty((n_tiles * heads * splits, 2 * 128), dtype=torch.float32, device=q.device)
-                    tickets = _attention_tickets(q.device, n_tiles * heads)
                 _check(_fn("attention_tc", "zai_prefill_attention_tc")(
                     _ptr(out), _ptr(q), _ptr(cache.pages), cache.pages.shape[0], _status_ptr(q.device), _ptr(bt), bt.shape[1],
                     _ptr(cu_q), _ptr(ctx_lens), N, S, n_tiles, cache.page_size, heads, kv_heads,
