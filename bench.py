@@ -266,7 +266,7 @@ def run_ours(args):
             print(json.dumps({"only": "decode", "batch": args.batch, "ms_per_step": round(ms, 4),
                               "e2e_ms_per_step": round(e2e, 4), "launches_per_step": launches}))
             return 0
-        prefill_ms = time_prefill(eng)
+        prefill_ms = time_prefill(eng, reps=15)
         clocks = ClockSampler()
         dev_ms, e2e_ms, ctx_tokens, launches, h2d, d2h, clock_info = time_decode(eng, 8, args.steps, args.warmup, clocks)
         points = {}
