@@ -125,7 +125,7 @@ def test_span_attention_few_rows_over_long_contexts(ps, window, padded):
     for _ in range(2):
         got = o.paged_attention(q, step, view, Hq, Hkv, D, D ** -0.5, window, impl="tcgen05")
         assert torch.allclose(got.float(), want.float(), atol=3e-2, rtol=3e-2), (got.float() - want.float()).abs().max()
-        assert int(ops_module._tickets[q.device].abs().sum()) == 0
+        assert int(ops_module._span_tickets[q.device].abs().sum()) == 0
     assert o.read_status() == 0
 
 

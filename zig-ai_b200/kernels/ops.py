@@ -711,15 +711,15 @@ USE_TC_ATTENTION = os.environ.get("ZAI_TC_ATTENTION", "1") == "1"     # tcgen05 
 
 
 
-_tickets = {}
+_span_tickets = {}
 
 
 def _attention_tickets(device, n):
     """Zeroed counters for the span attention's shared tiles (the kernel leaves them zero)."""
-    t = _tickets.get(device)
+    t = _span_tickets.get(device)
     if t is None or t.numel() < n:
         t = torch.zeros((max(n, 1024),), dtype=torch.int32, device=device)
-        _tickets[device] = t
+        _span_tickets[device] = t
     return t
 
 @_timed("attention")
