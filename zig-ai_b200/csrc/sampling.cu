@@ -114,31 +114,19 @@ __global__ void repetition_penalty_kernel(float* __restrict__ logits, const int*
     }
 }
 
-__global__ void sample_kernel(int* __restrict__ out, const float* __restrict__ logits,
-                              const float* __restrict__ temperature, const int* __restrict__ top_k,
-                              const float* __restrict__ top_p, const float* __restrict__ uniform, int V,
-                              const int* __restrict__ status) {
-    __shared__ MaxIdx redm[33];
+// The general way, for rows whose kept set may be large (a top-k above SAMPLE_CAP, many ties, a nucleus that the
+// SAMPLE_CAP largest values do not cover): thresholds by bisection over the bit patterns, about seventy walks over
+// the row.  `x` is the row's maximum and its first index.
+__device__ __noinline__ void sample_row_by_bisection(int* __restrict__ out, const float* __restrict__ row, float T, int k, float tp,
+                                                     float u, int V, int r, MaxIdx x) {
     __shared__ float red[33];
     __shared__ float scan[SAMPLE_THREADS];
     __shared__ int chosen;
-    pdl_trigger();
-    pdl_wait();
-    if (status && blockIdx.x == 0 && threadIdx.x == 0) out[gridDim.x] = *status;
-    const int r = blockIdx.x, tid = threadIdx.x;
-    const float* row = logits + (size_t)r * V;
-    const float T = temperature[r];
-    MaxIdx x = scan_row(row, V);
-    x = block_argmax(x, redm);
-    if (T <= 0.f) {
-        if (tid == 0) out[r] = x.i == 0x7fffffff ? 0 : x.i;
-        return;
-    }
+    const int tid = threadIdx.x;
     const float inv_t = 1.f / T;
     const float mx = x.v * inv_t;
     // top-k: the k-th largest scaled value, by bisection on the ordered bit pattern
     float floor_val = -INFINITY;
-    const int k = top_k[r];
     if (k > 0 && k < V) {
         unsigned lo = 0u, hi = 0xffffffffu;           // largest key with count(key >= .) >= k
         while (lo < hi) {
@@ -159,7 +147,6 @@ __global__ void sample_kernel(int* __restrict__ out, const float* __restrict__ l
     float mass = block_sum(part, red);
     // top-p: the largest threshold whose kept mass still reaches p * mass
     float p_floor = 0.f;
-    const float tp = top_p[r];
     if (tp < 1.f) {
         const float target = tp * mass;
         unsigned lo = ordered_key(0.f), hi = ordered_key(1.f);
@@ -210,7 +197,7 @@ __global__ void sample_kernel(int* __restrict__ out, const float* __restrict__ l
     }
     __syncthreads();
     const float total = red[0];
-    const float target = uniform[r] * total;
+    const float target = u * total;
     float cum = scan[tid];
     if (target >= cum) {      // later pieces start past the target; the lowest pick wins
         int pick = -1;
@@ -234,6 +221,322 @@ __global__ void sample_kernel(int* __restrict__ out, const float* __restrict__ l
     }
 }
 
+
+// ---- the quick way.  The kept set is almost always small: top-k says so, and a nucleus seldom has more than a
+// few thousand tokens.  So the SAMPLE_CAP largest values (or the k largest) are found by a radix selection over
+// the ordered bit patterns (four walks over the row, counting by byte; the first also finds the maximum), the
+// values at or above that floor are laid into shared memory in index order, and the rest (masses, the nucleus,
+// the inverse CDF) runs on that list, in one warp.  A warp owns a contiguous range of the row and reads it 32
+// consecutive values at a time, so every walk is coalesced and what a warp counts is what lies in its range.
+// Probabilities are summed as integers (exp(w - max) in units of 2^-40), so a sum does not depend on the order
+// in which it is taken and the same row with the same u gives the same token in whatever batch it runs.
+#define SAMPLE_CAP 4096
+#define SAMPLE_UNIT 1099511627776.f                     // 2^40
+#define SAMPLE_WARPS (SAMPLE_THREADS / 32)
+
+typedef unsigned long long u64;
+
+__device__ __forceinline__ u64 unit_of(float e) { return __float2ull_rz(e * SAMPLE_UNIT); }
+__device__ __forceinline__ u64 warp_sum_u64(u64 v) {
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+// inclusive prefix over the lanes of a warp
+__device__ __forceinline__ u64 warp_scan_u64(u64 v, int lane) {
+    for (int o = 1; o < 32; o <<= 1) {
+        const u64 y = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += y;
+    }
+    return v;
+}
+
+struct SampleShared {
+    unsigned whist[SAMPLE_WARPS][256];                  // a histogram per warp (= per range of the row)
+    unsigned hist[256];
+    float le[SAMPLE_CAP];                               // the list: exp(w - max),
+    int li[SAMPLE_CAP];                                 //   index
+    u64 wmass[SAMPLE_WARPS];                            // per range: mass
+    unsigned wcount[SAMPLE_WARPS];                      // per range: values above the floor's first three bytes
+    unsigned woffset[SAMPLE_WARPS];                     // per range: where its kept values start in the list
+    MaxIdx redm[33];
+    unsigned sel_digit, sel_above;
+    int chosen, pick_warp;
+    u64 pick_before, pick_target;
+};
+
+// One count into a warp's histogram, with runs of the same bin counted in a register first (the top bytes of a
+// row's values are nearly all the same, and atomics of a warp on one address are served one after the other).
+struct RunCount {
+    unsigned bin, n;
+    __device__ __forceinline__ void add(unsigned* hist, unsigned b) {
+        if (b == bin) { ++n; return; }
+        if (n) atomicAdd(hist + bin, n);
+        bin = b;
+        n = 1;
+    }
+    __device__ __forceinline__ void flush(unsigned* hist) { if (n) atomicAdd(hist + bin, n); n = 0; }
+};
+
+__global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(int* __restrict__ out, const float* __restrict__ logits,
+                              const float* __restrict__ temperature, const int* __restrict__ top_k,
+                              const float* __restrict__ top_p, const float* __restrict__ uniform, int V,
+                              const int* __restrict__ status) {
+    extern __shared__ __align__(16) unsigned char sample_smem[];
+    SampleShared& sh = *reinterpret_cast<SampleShared*>(sample_smem);
+    pdl_trigger();
+    pdl_wait();
+    if (status && blockIdx.x == 0 && threadIdx.x == 0) out[gridDim.x] = *status;
+    const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* row = logits + (size_t)r * V;
+    const float T = temperature[r];
+    if (T <= 0.f) {
+        MaxIdx x = scan_row(row, V);
+        x = block_argmax(x, sh.redm);
+        if (tid == 0) out[r] = x.i == 0x7fffffff ? 0 : x.i;
+        return;
+    }
+    const float inv_t = 1.f / T, u = uniform[r], tp = top_p[r];
+    const int k = top_k[r];
+    const bool use_k = k > 0 && k < V, use_p = tp < 1.f;
+    // this warp's range of the row: [ra, rb), a multiple of 32 long (but for the row's end)
+    const int range = ((V + SAMPLE_WARPS - 1) / SAMPLE_WARPS + 31) / 32 * 32;
+    const int ra = min(warp * range, V), rb = min(ra + range, V);
+    const int want = use_k ? k : min(SAMPLE_CAP, V);
+    const bool select = (use_k || use_p) && want <= SAMPLE_CAP;
+
+    // ---- walk one: the maximum and its first index, and the count by the top byte of the key
+    for (int j = lane; j < 256; j += 32) sh.whist[warp][j] = 0;
+    __syncwarp();
+    MaxIdx x{-INFINITY, 0x7fffffff};
+    {
+        RunCount rc{0u, 0u};
+        for (int i = ra + lane; i < rb; i += 32) {
+            const float v = row[i];
+            if (v > x.v) { x.v = v; x.i = i; }               // (a lane's indices rise)
+            if (select) rc.add(sh.whist[warp], ordered_key(v * inv_t) >> 24);
+        }
+        rc.flush(sh.whist[warp]);
+    }
+    x = block_argmax(x, sh.redm);                            // (syncs the block)
+    const float mx = x.v * inv_t;
+
+    // the floor: the key of the `want`-th largest scaled value, byte by byte from the top
+    unsigned floor_key = 0, n_keep = 0;
+    u64 all_mass = 0;                                        // of the whole row
+    bool quick = select;
+    if (select) {
+        unsigned prefix = 0, remaining = (unsigned)want, above = 0;
+        for (int byte = 3; byte >= 0; --byte) {
+            const int shift = byte * 8;
+            if (byte < 3) {
+                for (int j = lane; j < 256; j += 32) sh.whist[warp][j] = 0;
+                __syncwarp();
+                const unsigned high_mask = 0xffffffffu << (shift + 8);
+                RunCount rc{0u, 0u};
+                u64 part = 0;
+                unsigned gt = 0;
+                for (int i = ra + lane; i < rb; i += 32) {
+                    const float w = row[i] * inv_t;
+                    const unsigned key = ordered_key(w);
+                    if ((key & high_mask) == (prefix & high_mask)) rc.add(sh.whist[warp], (key >> shift) & 255u);
+                    if (byte == 2) part += unit_of(expf(w - mx));
+                    if (byte == 0) gt += (key & high_mask) > (prefix & high_mask) ? 1u : 0u;
+                }
+                rc.flush(sh.whist[warp]);
+                if (byte == 2) {
+                    part = warp_sum_u64(part);
+                    if (lane == 0) sh.wmass[warp] = part;
+                }
+                if (byte == 0) {
+                    gt = __reduce_add_sync(0xffffffffu, gt);
+                    if (lane == 0) sh.wcount[warp] = gt;
+                }
+            }
+            __syncthreads();
+            if (tid < 256) {
+                unsigned c = 0;
+                for (int w2 = 0; w2 < SAMPLE_WARPS; ++w2) c += sh.whist[w2][tid];
+                sh.hist[tid] = c;
+            }
+            __syncthreads();
+            if (warp == 0) {
+                // lane l owns bins 8l..8l+7; the digit is the highest bin at which the count from the top reaches `remaining`
+                unsigned mine = 0;
+                for (int j = 0; j < 8; ++j) mine += sh.hist[lane * 8 + j];
+                unsigned incl = mine;                        // sum over lanes >= this one
+                for (int o = 1; o < 32; o <<= 1) {
+                    const unsigned y = __shfl_down_sync(0xffffffffu, incl, o);
+                    if (lane + o < 32) incl += y;
+                }
+                const unsigned higher = incl - mine;         // in the lanes above this one
+                if (higher < remaining && remaining <= incl) {
+                    unsigned cum = higher;
+                    for (int j = 7; j >= 0; --j) {
+                        const unsigned c = sh.hist[lane * 8 + j];
+                        if (cum + c >= remaining) { sh.sel_digit = (unsigned)(lane * 8 + j); sh.sel_above = cum; break; }
+                        cum += c;
+                    }
+                }
+            }
+            __syncthreads();
+            prefix |= sh.sel_digit << shift;
+            above += sh.sel_above;                            // values whose key is larger in this byte (and equal above it)
+            remaining -= sh.sel_above;
+            if (byte == 0) n_keep = above + sh.hist[sh.sel_digit];
+            if (byte == 2) {
+                for (int w2 = 0; w2 < SAMPLE_WARPS; ++w2) all_mass += sh.wmass[w2];
+            }
+            if (byte > 0) __syncthreads();                   // (the last walk's histograms are still needed below)
+        }
+        floor_key = prefix;
+        quick = n_keep <= SAMPLE_CAP;                        // (ties at the floor are all kept)
+    }
+    if (select && !quick) {
+        sample_row_by_bisection(out, row, T, k, tp, u, V, r, x);
+        return;
+    }
+
+    if (!select) {
+        if (use_k || use_p) {                                // a top-k above what the list holds
+            sample_row_by_bisection(out, row, T, k, tp, u, V, r, x);
+            return;
+        }
+        // ---- nothing to select: the inverse CDF over the whole row.  The ranges' masses, then the range that
+        // holds the target walks again.
+        u64 part = 0;
+        for (int i = ra + lane; i < rb; i += 32) part += unit_of(expf(row[i] * inv_t - mx));
+        part = warp_sum_u64(part);
+        if (lane == 0) sh.wmass[warp] = part;
+        if (tid == 0) sh.chosen = 0x7fffffff;
+        __syncthreads();
+        if (warp == 0) {
+            const u64 mine = lane < SAMPLE_WARPS ? sh.wmass[lane] : 0ull;
+            const u64 incl = warp_scan_u64(mine, lane);
+            const u64 total = __shfl_sync(0xffffffffu, incl, 31);
+            const u64 target = (u64)((double)u * (double)total);
+            // the first range whose cumulative mass reaches the target (and that has mass)
+            const unsigned hit = __ballot_sync(0xffffffffu, mine > 0 && target <= incl);
+            if (lane == 0) {
+                sh.pick_warp = hit ? __ffs(hit) - 1 : -1;
+                sh.pick_target = target;
+            }
+            if (hit && lane == __ffs(hit) - 1) sh.pick_before = incl - mine;
+        }
+        __syncthreads();
+        if (warp == sh.pick_warp) {
+            u64 cum = sh.pick_before;
+            const u64 target = sh.pick_target;
+            for (int i0 = ra; i0 < rb; i0 += 32) {
+                const int i = i0 + lane;
+                const u64 e = i < rb ? unit_of(expf(row[i] * inv_t - mx)) : 0ull;
+                const u64 incl = warp_scan_u64(e, lane) + cum;
+                const unsigned hit = __ballot_sync(0xffffffffu, e > 0 && target <= incl);
+                if (hit) {
+                    if (lane == 0) sh.chosen = i0 + __ffs(hit) - 1;
+                    break;
+                }
+                cum = __shfl_sync(0xffffffffu, incl, 31);
+            }
+        }
+        __syncthreads();
+        if (tid == 0) out[r] = sh.chosen == 0x7fffffff ? x.i : sh.chosen;   // (rounding left the target past the last token)
+        return;
+    }
+
+    // ---- the list, in index order: a range's kept values follow those of the ranges before it
+    {
+        unsigned mine = 0;                                   // kept in this range: above the floor's first bytes, or at them with a last byte >= the floor's
+        const unsigned digit = floor_key & 255u;
+        for (int j = lane; j < 256; j += 32) mine += (unsigned)j >= digit ? sh.whist[warp][j] : 0u;
+        mine = __reduce_add_sync(0xffffffffu, mine) + sh.wcount[warp];
+        if (lane == 0) sh.woffset[warp] = mine;
+        __syncthreads();
+        if (warp == 0) {
+            const unsigned c = lane < SAMPLE_WARPS ? sh.woffset[lane] : 0u;
+            unsigned incl = c;
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned y = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += y;
+            }
+            if (lane < SAMPLE_WARPS) sh.woffset[lane] = incl - c;
+        }
+        __syncthreads();
+        unsigned at = sh.woffset[warp];
+        for (int i0 = ra; i0 < rb; i0 += 32) {
+            const int i = i0 + lane;
+            const float w = i < rb ? row[i] * inv_t : 0.f;
+            const bool keep = i < rb && ordered_key(w) >= floor_key;
+            const unsigned m = __ballot_sync(0xffffffffu, keep);
+            if (keep) {
+                const unsigned pos = at + __popc(m & ((1u << lane) - 1u));
+                if (pos < SAMPLE_CAP) {
+                    sh.le[pos] = expf(w - mx);
+                    sh.li[pos] = i;
+                }
+            }
+            at += __popc(m);
+        }
+        __syncthreads();
+    }
+    // ---- on the list, in one warp: its mass, the nucleus, the inverse CDF
+    if (warp == 0) {
+        const int n = (int)n_keep;
+        u64 list_mass = 0;
+        for (int j = lane; j < n; j += 32) list_mass += unit_of(sh.le[j]);
+        list_mass = warp_sum_u64(list_mass);
+        bool ok = true;
+        float p_floor = 0.f;
+        if (use_p) {
+            // with top-p alone the list has to hold the whole nucleus
+            const u64 base = use_k ? list_mass : all_mass;
+            const u64 target = (u64)((double)tp * (double)base);
+            if (list_mass < target) ok = false;
+            // the largest threshold on exp(w - max) whose tokens still hold p of the mass (positive floats order as their bits do)
+            unsigned lo = __float_as_uint(0.f), hi = __float_as_uint(1.f);
+            while (ok && lo < hi) {
+                const unsigned mid = lo + ((hi - lo + 1) >> 1);
+                const float th = __uint_as_float(mid);
+                u64 s2 = 0;
+                for (int j = lane; j < n; j += 32) {
+                    const float e = sh.le[j];
+                    if (e >= th) s2 += unit_of(e);
+                }
+                s2 = warp_sum_u64(s2);
+                if (s2 >= target) lo = mid; else hi = mid - 1;
+            }
+            p_floor = __uint_as_float(lo);
+        }
+        int pick = ok ? 0x7fffffff : -1;
+        if (ok) {
+            // the list is in index order: lanes take 32 consecutive entries at a time
+            u64 total = 0;
+            for (int j = lane; j < n; j += 32) {
+                const float e = sh.le[j];
+                if (e >= p_floor) total += unit_of(e);
+            }
+            total = warp_sum_u64(total);
+            const u64 target = (u64)((double)u * (double)total);
+            u64 cum = 0;
+            for (int j0 = 0; j0 < n; j0 += 32) {
+                const int j = j0 + lane;
+                const float e = j < n ? sh.le[j] : 0.f;
+                const u64 ei = (j < n && e >= p_floor) ? unit_of(e) : 0ull;
+                const u64 incl = warp_scan_u64(ei, lane) + cum;
+                const unsigned hit = __ballot_sync(0xffffffffu, ei > 0 && target <= incl);
+                if (hit) { pick = sh.li[j0 + __ffs(hit) - 1]; break; }
+                cum = __shfl_sync(0xffffffffu, incl, 31);
+            }
+        }
+        if (lane == 0) sh.chosen = pick;
+    }
+    __syncthreads();
+    if (sh.chosen == -1) {                                   // the nucleus is larger than the list
+        sample_row_by_bisection(out, row, T, k, tp, u, V, r, x);
+        return;
+    }
+    if (tid == 0) out[r] = sh.chosen == 0x7fffffff ? x.i : sh.chosen;       // (rounding left the target past the last kept token)
+}
+
 // out holds R ids, and the status word behind them if `status` is given (R + 1 ints then).
 ZAI_API int zai_argmax(int* out, const float* logits, int R, int V, const int* status, cudaStream_t stream) {
     if (R <= 0) return ZAI_OK;
@@ -250,6 +553,12 @@ ZAI_API int zai_repetition_penalty(float* logits, const int* tokens, const int* 
 ZAI_API int zai_sample(int* out, const float* logits, const float* temperature, const int* top_k, const float* top_p,
                        const float* uniform, int R, int V, const int* status, cudaStream_t stream) {
     if (R <= 0) return ZAI_OK;
-    return launch_pdl(sample_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, stream, out, logits, temperature, top_k, top_p, uniform, V,
+    const size_t smem = sizeof(SampleShared);
+    static unsigned long long configured = 0;
+    if (zai_first_on_device(&configured)) {
+        cudaError_t e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return launch_pdl(sample_kernel, dim3(R), dim3(SAMPLE_THREADS), smem, stream, out, logits, temperature, top_k, top_p, uniform, V,
                       status);
 }
