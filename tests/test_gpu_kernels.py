@@ -299,6 +299,32 @@ def test_sampling_matches_plain_version(V):
             assert ok, (trial, r, int(a[r]), int(b[r]))
 
 
+def test_sampling_large_kept_sets():
+    """Rows whose kept set does not fit the kernel's list of 4096 tokens, which take its general way: a flat
+    distribution under top-p (a nucleus of tens of thousands of tokens), a top-k above 4096, values with so many
+    ties that the k largest are more than 4096 tokens; and beside them rows that fit, with ties at the floor."""
+    o = ops()
+    V, R = 65536, 6
+    g = torch.Generator().manual_seed(113)
+    logits = (torch.randn(R, V, generator=g) * 3)
+    logits[2] = torch.round(logits[2])                      # a few dozen distinct values: thousands of ties each
+    logits[3] = torch.round(logits[3] * 4) / 4
+    logits = logits.cuda()
+    temperature = torch.tensor([3.0, 1.0, 1.0, 1.0, 2.5, 1.0]).cuda()
+    top_k = torch.tensor([0, 5000, 40, 40, 3000, 4096], dtype=torch.int32).cuda()
+    top_p = torch.tensor([0.95, 1.0, 1.0, 0.7, 0.9, 0.99]).cuda()
+    for trial in range(4):
+        u = torch.rand(R, generator=g).cuda()
+        a = o.sample(logits, temperature, top_k, top_p, u).cpu()
+        b = ref_ops.sample(logits.cpu(), temperature.cpu(), top_k.cpu(), top_p.cpu(), u.cpu())
+        for r in range(R):
+            if int(a[r]) == int(b[r]):
+                continue
+            ok = any(_u_in_interval(p, int(a[r]), float(u[r])) for p in _kept_distributions(
+                logits[r].double().cpu(), float(temperature[r]), int(top_k[r]), float(top_p[r])))
+            assert ok, (trial, r, int(a[r]), int(b[r]))
+
+
 def _kept_distributions(row, T, k, tp):
     """The probabilities of the kept tokens (zero elsewhere, not normalised) as the plain version
     keeps them, and the two neighbouring choices of the top-p edge."""

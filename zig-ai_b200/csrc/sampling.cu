@@ -8,8 +8,11 @@
 // token is the first index whose cumulative probability reaches u times the kept mass (:39-52,
 // :141-149), u being a uniform number in [0, 1) that the caller supplies for the row.  The scan
 // runs in index order over the kept set (the reference scans its nucleus in sorted order; the
-// distribution is the same).  Thresholds of top-k and top-p are found by bisection over the bit
-// patterns of the values, so no sort is needed; ties at a threshold are all kept.
+// distribution is the same).  No sort: the k-th largest value (or the 4096-th, a bound on the nucleus) is
+// found by a radix selection over the ordered bit patterns, the values at or above it are laid into
+// shared memory in index order, and the nucleus and the inverse CDF run on that list; ties at a
+// threshold are all kept.  A row whose kept set does not fit the list (a top-k above 4096, many ties,
+// a nucleus of more than 4096 tokens) takes the general way, thresholds by bisection over the row.
 #include "common.cuh"
 
 #define SAMPLE_THREADS 1024
@@ -233,6 +236,21 @@ __device__ __noinline__ void sample_row_by_bisection(int* __restrict__ out, cons
 #define SAMPLE_CAP 4096
 #define SAMPLE_UNIT 1099511627776.f                     // 2^40
 #define SAMPLE_WARPS (SAMPLE_THREADS / 32)
+#define SAMPLE_BATCH 8                                  // loads of a lane in flight in a walk
+// a walk over this warp's range [ra, rb): BODY sees the index `i` and the value `v`, eight loads asked for at once
+#define SAMPLE_WALK(BODY)                                                        \
+    for (int i0_ = ra + lane; i0_ < rb; i0_ += 32 * SAMPLE_BATCH) {              \
+        float v_[SAMPLE_BATCH];                                                  \
+        _Pragma("unroll") for (int u_ = 0; u_ < SAMPLE_BATCH; ++u_) {            \
+            const int i_ = i0_ + 32 * u_;                                        \
+            v_[u_] = i_ < rb ? row[i_] : 0.f;                                    \
+        }                                                                        \
+        _Pragma("unroll") for (int u_ = 0; u_ < SAMPLE_BATCH; ++u_) {            \
+            const int i = i0_ + 32 * u_;                                         \
+            const float v = v_[u_];                                              \
+            if (i < rb) { BODY }                                                 \
+        }                                                                        \
+    }
 
 typedef unsigned long long u64;
 
@@ -310,11 +328,10 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(int* __restrict_
     MaxIdx x{-INFINITY, 0x7fffffff};
     {
         RunCount rc{0u, 0u};
-        for (int i = ra + lane; i < rb; i += 32) {
-            const float v = row[i];
+        SAMPLE_WALK(
             if (v > x.v) { x.v = v; x.i = i; }               // (a lane's indices rise)
             if (select) rc.add(sh.whist[warp], ordered_key(v * inv_t) >> 24);
-        }
+        )
         rc.flush(sh.whist[warp]);
     }
     x = block_argmax(x, sh.redm);                            // (syncs the block)
@@ -335,13 +352,13 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(int* __restrict_
                 RunCount rc{0u, 0u};
                 u64 part = 0;
                 unsigned gt = 0;
-                for (int i = ra + lane; i < rb; i += 32) {
-                    const float w = row[i] * inv_t;
+                SAMPLE_WALK(
+                    const float w = v * inv_t;
                     const unsigned key = ordered_key(w);
                     if ((key & high_mask) == (prefix & high_mask)) rc.add(sh.whist[warp], (key >> shift) & 255u);
                     if (byte == 2) part += unit_of(expf(w - mx));
                     if (byte == 0) gt += (key & high_mask) > (prefix & high_mask) ? 1u : 0u;
-                }
+                )
                 rc.flush(sh.whist[warp]);
                 if (byte == 2) {
                     part = warp_sum_u64(part);
@@ -404,7 +421,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(int* __restrict_
         // ---- nothing to select: the inverse CDF over the whole row.  The ranges' masses, then the range that
         // holds the target walks again.
         u64 part = 0;
-        for (int i = ra + lane; i < rb; i += 32) part += unit_of(expf(row[i] * inv_t - mx));
+        SAMPLE_WALK(part += unit_of(expf(v * inv_t - mx));)
         part = warp_sum_u64(part);
         if (lane == 0) sh.wmass[warp] = part;
         if (tid == 0) sh.chosen = 0x7fffffff;
@@ -462,78 +479,128 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(int* __restrict_
         }
         __syncthreads();
         unsigned at = sh.woffset[warp];
-        for (int i0 = ra; i0 < rb; i0 += 32) {
-            const int i = i0 + lane;
-            const float w = i < rb ? row[i] * inv_t : 0.f;
-            const bool keep = i < rb && ordered_key(w) >= floor_key;
-            const unsigned m = __ballot_sync(0xffffffffu, keep);
-            if (keep) {
-                const unsigned pos = at + __popc(m & ((1u << lane) - 1u));
-                if (pos < SAMPLE_CAP) {
-                    sh.le[pos] = expf(w - mx);
-                    sh.li[pos] = i;
-                }
+        for (int i0 = ra; i0 < rb; i0 += 32 * SAMPLE_BATCH) {
+            float v[SAMPLE_BATCH];
+#pragma unroll
+            for (int q = 0; q < SAMPLE_BATCH; ++q) {
+                const int i = i0 + 32 * q + lane;
+                v[q] = i < rb ? row[i] : 0.f;
             }
-            at += __popc(m);
+#pragma unroll
+            for (int q = 0; q < SAMPLE_BATCH; ++q) {
+                const int i = i0 + 32 * q + lane;
+                const float w = v[q] * inv_t;
+                const bool keep = i < rb && ordered_key(w) >= floor_key;
+                const unsigned m = __ballot_sync(0xffffffffu, keep);
+                if (keep) {
+                    const unsigned pos = at + __popc(m & ((1u << lane) - 1u));
+                    if (pos < SAMPLE_CAP) {
+                        sh.le[pos] = expf(w - mx);
+                        sh.li[pos] = i;
+                    }
+                }
+                at += __popc(m);
+            }
         }
         __syncthreads();
     }
-    // ---- on the list, in one warp: its mass, the nucleus, the inverse CDF
-    if (warp == 0) {
-        const int n = (int)n_keep;
-        u64 list_mass = 0;
-        for (int j = lane; j < n; j += 32) list_mass += unit_of(sh.le[j]);
-        list_mass = warp_sum_u64(list_mass);
-        bool ok = true;
-        float p_floor = 0.f;
-        if (use_p) {
-            // with top-p alone the list has to hold the whole nucleus
-            const u64 base = use_k ? list_mass : all_mass;
-            const u64 target = (u64)((double)tp * (double)base);
-            if (list_mass < target) ok = false;
-            // the largest threshold on exp(w - max) whose tokens still hold p of the mass (positive floats order as their bits do)
-            unsigned lo = __float_as_uint(0.f), hi = __float_as_uint(1.f);
-            while (ok && lo < hi) {
+    // ---- on the list: its mass, the nucleus, the inverse CDF.  A warp owns a contiguous part of the list.
+    const int n = (int)n_keep;
+    const int lrange = ((n + SAMPLE_WARPS - 1) / SAMPLE_WARPS + 31) / 32 * 32;
+    const int la = min(warp * lrange, n), lb = min(la + lrange, n);
+    auto block_sum = [&](u64 v) {                            // over the block, to every thread
+        v = warp_sum_u64(v);
+        if (lane == 0) sh.wmass[warp] = v;
+        __syncthreads();
+        u64 t = 0;
+        for (int w2 = 0; w2 < SAMPLE_WARPS; ++w2) t += sh.wmass[w2];
+        __syncthreads();
+        return t;
+    };
+    u64 part = 0;
+    for (int j = la + lane; j < lb; j += 32) part += unit_of(sh.le[j]);
+    const u64 list_mass = block_sum(part);
+    float p_floor = 0.f;
+    if (use_p) {
+        // with top-p alone the list has to hold the whole nucleus
+        const u64 base = use_k ? list_mass : all_mass;
+        const u64 target = (u64)((double)tp * (double)base);
+        if (list_mass < target) {
+            sample_row_by_bisection(out, row, T, k, tp, u, V, r, x);
+            return;
+        }
+        // the largest threshold on exp(w - max) whose tokens still hold p of the mass (positive floats order as their bits do)
+        unsigned lo = __float_as_uint(0.f), hi = __float_as_uint(1.f);
+        if (n <= 1024) {                                     // a short list: one warp, no block-wide sums
+            if (warp == 0) {
+                while (lo < hi) {
+                    const unsigned mid = lo + ((hi - lo + 1) >> 1);
+                    const float th = __uint_as_float(mid);
+                    u64 s2 = 0;
+                    for (int j = lane; j < n; j += 32) {
+                        const float e = sh.le[j];
+                        if (e >= th) s2 += unit_of(e);
+                    }
+                    if (warp_sum_u64(s2) >= target) lo = mid; else hi = mid - 1;
+                }
+                if (lane == 0) sh.sel_digit = lo;
+            }
+            __syncthreads();
+            lo = sh.sel_digit;
+        } else {
+            while (lo < hi) {
                 const unsigned mid = lo + ((hi - lo + 1) >> 1);
                 const float th = __uint_as_float(mid);
                 u64 s2 = 0;
-                for (int j = lane; j < n; j += 32) {
+                for (int j = la + lane; j < lb; j += 32) {
                     const float e = sh.le[j];
                     if (e >= th) s2 += unit_of(e);
                 }
-                s2 = warp_sum_u64(s2);
-                if (s2 >= target) lo = mid; else hi = mid - 1;
-            }
-            p_floor = __uint_as_float(lo);
-        }
-        int pick = ok ? 0x7fffffff : -1;
-        if (ok) {
-            // the list is in index order: lanes take 32 consecutive entries at a time
-            u64 total = 0;
-            for (int j = lane; j < n; j += 32) {
-                const float e = sh.le[j];
-                if (e >= p_floor) total += unit_of(e);
-            }
-            total = warp_sum_u64(total);
-            const u64 target = (u64)((double)u * (double)total);
-            u64 cum = 0;
-            for (int j0 = 0; j0 < n; j0 += 32) {
-                const int j = j0 + lane;
-                const float e = j < n ? sh.le[j] : 0.f;
-                const u64 ei = (j < n && e >= p_floor) ? unit_of(e) : 0ull;
-                const u64 incl = warp_scan_u64(ei, lane) + cum;
-                const unsigned hit = __ballot_sync(0xffffffffu, ei > 0 && target <= incl);
-                if (hit) { pick = sh.li[j0 + __ffs(hit) - 1]; break; }
-                cum = __shfl_sync(0xffffffffu, incl, 31);
+                if (block_sum(s2) >= target) lo = mid; else hi = mid - 1;
             }
         }
-        if (lane == 0) sh.chosen = pick;
+        p_floor = __uint_as_float(lo);
+    }
+    // the kept mass of every part, then the part that holds the target walks again (the list is in index order)
+    part = 0;
+    for (int j = la + lane; j < lb; j += 32) {
+        const float e = sh.le[j];
+        if (e >= p_floor) part += unit_of(e);
+    }
+    part = warp_sum_u64(part);
+    if (lane == 0) sh.wmass[warp] = part;
+    if (tid == 0) sh.chosen = 0x7fffffff;
+    __syncthreads();
+    if (warp == 0) {
+        const u64 mine = lane < SAMPLE_WARPS ? sh.wmass[lane] : 0ull;
+        const u64 incl = warp_scan_u64(mine, lane);
+        const u64 total = __shfl_sync(0xffffffffu, incl, 31);
+        const u64 target = (u64)((double)u * (double)total);
+        const unsigned hit = __ballot_sync(0xffffffffu, mine > 0 && target <= incl);
+        if (lane == 0) {
+            sh.pick_warp = hit ? __ffs(hit) - 1 : -1;
+            sh.pick_target = target;
+        }
+        if (hit && lane == __ffs(hit) - 1) sh.pick_before = incl - mine;
     }
     __syncthreads();
-    if (sh.chosen == -1) {                                   // the nucleus is larger than the list
-        sample_row_by_bisection(out, row, T, k, tp, u, V, r, x);
-        return;
+    if (warp == sh.pick_warp) {
+        u64 cum = sh.pick_before;
+        const u64 target = sh.pick_target;
+        for (int j0 = la; j0 < lb; j0 += 32) {
+            const int j = j0 + lane;
+            const float e = j < lb ? sh.le[j] : 0.f;
+            const u64 ei = (j < lb && e >= p_floor) ? unit_of(e) : 0ull;
+            const u64 incl = warp_scan_u64(ei, lane) + cum;
+            const unsigned hit = __ballot_sync(0xffffffffu, ei > 0 && target <= incl);
+            if (hit) {
+                if (lane == 0) sh.chosen = sh.li[j0 + __ffs(hit) - 1];
+                break;
+            }
+            cum = __shfl_sync(0xffffffffu, incl, 31);
+        }
     }
+    __syncthreads();
     if (tid == 0) out[r] = sh.chosen == 0x7fffffff ? x.i : sh.chosen;       // (rounding left the target past the last kept token)
 }
 
