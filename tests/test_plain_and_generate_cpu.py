@@ -116,3 +116,24 @@ def test_top_k_top_p_and_penalty_through_the_entry_point(tiny_models):
     assert a == b and len(a[0]) == 12
     assert eng.generate([[1, 2, 3]], max_new_tokens=4, temperature=1.0, top_k=1) == \
         eng.generate([[1, 2, 3]], max_new_tokens=4, temperature=0.0)
+
+
+def test_array_uniforms_and_incremental_histories():
+    """The array form of the per-request random numbers gives the scalar form's numbers, and a history kept up
+    token by token (also across a list that was replaced by a shorter one) counts what a recount counts."""
+    import random
+    from collections import Counter
+    import numpy as np
+    from zig_ai_b200.sampling.sampler import _History, uniform, uniforms
+    g = random.Random(5)
+    seeds = [g.randrange(-9, 1 << 70) for _ in range(500)]
+    idx = [g.randrange(0, 1 << 22) for _ in range(500)]
+    assert [float(np.float32(uniform(s, i))) for s, i in zip(seeds, idx)] == [float(v) for v in uniforms(seeds, idx)]
+    h, out = _History(), []
+    for step in range(300):
+        out.append(g.randrange(40) if step % 3 else g.randrange(100000))
+        if step in (120, 250):
+            out = out[:7]                                    # (a request that was started again)
+        h.update(out)
+        got = dict(zip(h.tokens[:h.n].tolist(), h.counts[:h.n].tolist()))
+        assert got == dict(Counter(out)), step

@@ -96,7 +96,8 @@ class Engine:
         on_device = logits.device.type == "cuda"
         n = len(wanting)
         ids = self.sampler.sample_device(logits, [r.params for r in wanting], [len(r.output) + ahead for r in wanting],
-                                         [r.output for r in wanting], with_status=on_device and n > 0)
+                                         [r.output for r in wanting], with_status=on_device and n > 0,
+                                         keys=[r.request_id for r in wanting])
         if self.profile:
             kind = "decode steps" if all(len(e.tokens) == 1 for e in plan.entries) else "steps with prompt portions"
             acc = self._profile.setdefault(kind, {"steps": 0, "tokens": 0})
