@@ -246,6 +246,8 @@ def run_ours(args):
         return run_mixed(args, cfg)
     if args.only == "long":
         return run_long(args)
+    if args.only == "sample":
+        return run_sample(args)
     if args.only == "table":
         return run_table(args)
     if args.only == "stream":
@@ -413,6 +415,64 @@ def run_long(args):
                           "e2e_tokens_per_s": round(B / e2e_ms * 1e3), "gb": round(step_bytes / 1e9, 3),
                           "achieved_gbs": round(step_bytes / dev_ms / 1e6),
                           "frac_of_peak": round(step_bytes / (dev_ms * 1e-3) / 1e9 / hbm_peak, 3), "peaks": peak_src}), flush=True)
+    return 0
+
+
+def run_sample(args):
+    """Sampling: the kernel alone at the shape's vocabulary (1, 8 and 64 rows; twenty eager calls, so about 13 us
+    of each figure are the launch), and decode steps through Engine.step() with sampled requests."""
+    import torch
+    import zig_ai_b200 as z
+    from zig_ai_b200.config import config_from_dict
+    from zig_ai_b200.kernels import ops
+    from zig_ai_b200.sampling import SamplingParams
+    cfg = config_from_dict(shape_config(args.model))
+    V = cfg.vocab_size
+    ops.require(torch.bfloat16)
+    kinds = (("temperature 0.8", 0, 1.0), ("top-k 40", 40, 1.0), ("top-p 0.9", 0, 0.9), ("top-k 40, top-p 0.9", 40, 0.9))
+    for R in (1, 8, 64):
+        logits = torch.randn(R, V, device="cuda") * 3
+        row = {"only": "sample", "rows": R, "vocab": V}
+        for name, tk, tp in kinds:
+            t = torch.full((R,), 0.8, device="cuda")
+            k = torch.full((R,), tk, dtype=torch.int32, device="cuda")
+            p = torch.full((R,), tp, device="cuda")
+            u = torch.rand(R, device="cuda")
+            for _ in range(3):
+                ops.sample(logits, t, k, p, u)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(20):
+                ops.sample(logits, t, k, p, u)
+            b.record()
+            torch.cuda.synchronize()
+            row[name + " us"] = round(a.elapsed_time(b) * 50, 1)
+        print(json.dumps(row), flush=True)
+    g = random.Random(3)
+    with tempfile.TemporaryDirectory(prefix="lfm2_sample_") as d:
+        z.write_random_model(cfg, 0, d)
+        for name, sp in (("greedy", dict(temperature=0.0)), ("temperature 0.8", dict(temperature=0.8)),
+                         ("temperature 0.8, top-k 40, top-p 0.9", dict(temperature=0.8, top_k=40, top_p=0.9)),
+                         ("and repetition penalty 1.1", dict(temperature=0.8, top_k=40, top_p=0.9, repetition_penalty=1.1))):
+            eng = z.Engine(d, "bfloat16", max_num_seqs=64, max_batched_tokens=2048 + 64, max_model_len=CONTEXT, max_tokens=64 * CONTEXT)
+            row = {"only": "sample", "requests": name}
+            for B in (8, 64):
+                ids = [eng.add_request([g.randrange(V) for _ in range(2048 + 20 * i)], SamplingParams(max_new_tokens=300, seed=i, **sp))
+                       for i in range(B)]
+                while any(eng.requests[i].computed < len(eng.requests[i].prompt) or not eng.requests[i].output for i in ids):
+                    eng.step()
+                for _ in range(20):
+                    eng.step()
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                for _ in range(100):
+                    eng.step()
+                torch.cuda.synchronize()
+                row[f"ms a step at batch {B}"] = round((time.perf_counter() - t0) * 10, 4)
+                while eng.has_work():
+                    eng.step()
+            print(json.dumps(row), flush=True)
+            del eng
     return 0
 
 
@@ -633,7 +693,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "gemm", "timeline", "table", "stream", "long"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "gemm", "timeline", "table", "stream", "long", "sample"],
                     help="profiling aid: run only the batch-8 decode steps or only the prefill (prints a short line); "
                          "table: every figure of the 350M, 700M and 1.2B shapes (profiles/measurements.md)")
     ap.add_argument("--batch", type=int, default=8, help="with --only decode: the batch size; with --only stream: 24, 64 or "
