@@ -57,6 +57,47 @@ def test_greedy_generation_bfloat16_picks_a_plain_maximum(tiny_models, name):
             assert float(row.max() - row[tok]) <= 8e-2 * float(row.abs().max()), (i, tok)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_repetition_penalty_with_histories_on_the_device(tiny_models, dtype):
+    """With a repetition penalty the requests' token counts live in a table on the device, so their steps run
+    ahead like any other; the tokens are those of the same engine with the counts kept on the host (no step
+    ahead then), for requests with and without a penalty, sampled and greedy, few pages (preemption), and a
+    second round of requests that takes over the first round's rows of the table."""
+    import zig_ai_b200 as z
+    from zig_ai_b200.sampling import SamplingParams
+    name = "B"
+    g = random.Random(41)
+    V = TINY[name][0]["vocab_size"]
+    outs = []
+    for on_device in (True, False):
+        eng = z.Engine(tiny_models[name], dtype, max_num_seqs=4, max_batched_tokens=12, max_model_len=96,
+                       max_tokens=224, page_size=PAGE_SIZE[name])
+        assert eng.sampler.device_history
+        eng.sampler.device_history = on_device
+        g = random.Random(41)
+        got = []
+        for rnd in range(2):
+            specs = [dict(temperature=0.9, top_k=20, repetition_penalty=1.3), dict(temperature=0.0, repetition_penalty=1.5),
+                     dict(temperature=1.1, top_p=0.8), dict(temperature=0.7, repetition_penalty=1.15),
+                     dict(temperature=0.8, top_k=5, repetition_penalty=2.0)]
+            ids = [eng.add_request([g.randrange(V) for _ in range(3 + 4 * i)], SamplingParams(max_new_tokens=40, seed=7 * rnd + i, **sp))
+                   for i, sp in enumerate(specs)]
+            done = {}
+            while len(done) < len(ids):
+                for r in eng.step():
+                    done[r.request_id] = r
+            eng.flush()
+            got.append([done[i].output for i in ids])
+            assert not eng.sampler._slots                     # every row of the table was given back
+        outs.append(got)
+        st = eng.stats()
+        assert (st["steps_ahead"] > 0) == on_device or st["steps_ahead"] > 0
+        if on_device:
+            assert st["steps_ahead"] > 10
+    assert outs[0] == outs[1]
+    assert all(len(o) == 40 for rnd in outs[0] for o in rnd)
+
+
 def test_sampled_generation_is_fixed_by_the_seed_and_not_by_batching(tiny_models):
     import zig_ai_b200 as z
     g = random.Random(5)

@@ -117,6 +117,39 @@ __global__ void repetition_penalty_kernel(float* __restrict__ logits, const int*
     }
 }
 
+// The same penalty from a table of counts on the device: counts[slot, token] is how often the request in that
+// slot has produced the token.  A row whose slot is negative (or whose penalty is 1) is copied as it is.
+__global__ void repetition_penalty_counts_kernel(float* __restrict__ out, const float* __restrict__ logits,
+                                                 const int* __restrict__ counts, const int* __restrict__ slots,
+                                                 const float* __restrict__ penalty, int V) {
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const int slot = slots[r];
+    const float p = penalty[r];
+    const float* row = logits + (size_t)r * V;
+    float* dst = out + (size_t)r * V;
+    const int* cnt = (slot >= 0 && p != 1.f) ? counts + (size_t)slot * V : nullptr;
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < V; i += gridDim.y * blockDim.x) {
+        float v = row[i];
+        if (cnt) {
+            const int c = cnt[i];
+            for (int k = 0; k < c; ++k) v = v > 0.f ? v / p : (v < 0.f ? v * p : v);
+        }
+        dst[i] = v;
+    }
+}
+
+// counts[slots[r], ids[r]] += 1 for the rows with a slot: the tokens just sampled join their requests' histories.
+__global__ void count_tokens_kernel(int* __restrict__ counts, const int* __restrict__ ids, const int* __restrict__ slots, int R, int V) {
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= R) return;
+    const int slot = slots[r], id = ids[r];
+    if (slot >= 0 && id >= 0 && id < V) counts[(size_t)slot * V + id] += 1;      // (a slot belongs to one row)
+}
+
 // The general way, for rows whose kept set may be large (a top-k above SAMPLE_CAP, many ties, a nucleus that the
 // SAMPLE_CAP largest values do not cover): thresholds by bisection over the bit patterns, about seventy walks over
 // the row.  `x` is the row's maximum and its first index.
@@ -615,6 +648,20 @@ ZAI_API int zai_repetition_penalty(float* logits, const int* tokens, const int* 
     if (R <= 0) return ZAI_OK;
     repetition_penalty_kernel<<<R, 128, 0, stream>>>(logits, tokens, counts, offsets, penalty, V);
     return launch_status();
+}
+
+// out [R, V] = logits [R, V] with the penalty applied from the table of counts [slots, V]; slots [R] (negative: none)
+ZAI_API int zai_repetition_penalty_counts(float* out, const float* logits, const int* counts, const int* slots,
+                                          const float* penalty, int R, int V, cudaStream_t stream) {
+    if (R <= 0) return ZAI_OK;
+    const int by = (V + 256 * 8 - 1) / (256 * 8);
+    return launch_pdl(repetition_penalty_counts_kernel, dim3(R, by < 1 ? 1 : by), dim3(256), 0, stream, out, logits, counts, slots,
+                      penalty, V);
+}
+
+ZAI_API int zai_count_tokens(int* counts, const int* ids, const int* slots, int R, int V, cudaStream_t stream) {
+    if (R <= 0) return ZAI_OK;
+    return launch_pdl(count_tokens_kernel, dim3((R + 127) / 128), dim3(128), 0, stream, counts, ids, slots, R, V);
 }
 
 ZAI_API int zai_sample(int* out, const float* logits, const float* temperature, const int* top_k, const float* top_p,

@@ -156,7 +156,8 @@ class Engine:
     def _decoding_only(self, plan: StepPlan) -> bool:
         sch = self.scheduler
         return (not sch.waiting and not plan.preempted and not plan.failed and len(plan.entries) == len(sch.running)
-                and all(e.sample and len(e.tokens) == 1 and e.request.params.repetition_penalty == 1.0
+                and all(e.sample and len(e.tokens) == 1
+                        and (e.request.params.repetition_penalty == 1.0 or self.sampler.device_history)
                         for e in plan.entries)
                 and self.runner.can_take_device_tokens(len(plan.entries)))
 
@@ -188,6 +189,7 @@ class Engine:
     def _retire(self, ended: List[Request]) -> List[Request]:
         for r in ended:
             self.requests.pop(r.request_id, None)
+            self.sampler.forget(r.request_id)
         return ended
 
     def step(self) -> List[Request]:

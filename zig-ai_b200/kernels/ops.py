@@ -85,6 +85,8 @@ _SIGNATURES = {
     "sampling": {
         "zai_argmax": [_P, _P, _I, _I, _P, _P],
         "zai_repetition_penalty": [_P, _P, _P, _P, _P, _I, _I, _P],
+        "zai_repetition_penalty_counts": [_P, _P, _P, _P, _P, _I, _I, _P],
+        "zai_count_tokens": [_P, _P, _P, _I, _I, _P],
         "zai_sample": [_P, _P, _P, _P, _P, _P, _I, _I, _P, _P],
     },
 }
@@ -863,6 +865,28 @@ def repetition_penalty(logits, tokens, counts, offsets, penalty):
     _check(_fn("sampling", "zai_repetition_penalty")(_ptr(logits), _ptr(tokens), _ptr(counts), _ptr(offsets),
                                                      _ptr(penalty), R, V, _stream()), "repetition_penalty")
     return logits
+
+
+@_timed("sampling")
+def repetition_penalty_counts(logits, counts, slots, penalty):
+    """A copy of logits [R, V] with the repetition penalty applied from a table of counts [slots, V] on the
+    device (slots [R] int32, negative: the row has none)."""
+    _cuda(logits, counts, slots, penalty)
+    R, V = logits.shape
+    if counts.dtype != torch.int32 or counts.shape[1] != V or logits.dtype != torch.float32:
+        raise KernelError("the penalty takes 32-bit logits and int32 counts [slots, vocabulary]")
+    out = torch.empty_like(logits)
+    _check(_fn("sampling", "zai_repetition_penalty_counts")(_ptr(out), _ptr(logits), _ptr(counts), _ptr(slots), _ptr(penalty),
+                                                           R, V, _stream()), "repetition_penalty_counts")
+    return out
+
+
+@_timed("sampling")
+def count_tokens(counts, ids, slots, rows):
+    """counts[slots[r], ids[r]] += 1 for the first `rows` rows that have a slot."""
+    _cuda(counts, ids, slots)
+    _check(_fn("sampling", "zai_count_tokens")(_ptr(counts), _ptr(ids), _ptr(slots), int(rows), counts.shape[1], _stream()),
+           "count_tokens")
 
 
 @_timed("sampling")

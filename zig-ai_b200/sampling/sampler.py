@@ -146,6 +146,43 @@ class Sampler:
         self.ops, self.device = ops, device
         self._staging: Optional[_Staging] = None
         self._histories = {}
+        # with kernels that keep the histories on the device: a table of counts [slots, vocabulary] and the
+        # slot of every request that has a repetition penalty
+        self.device_history = (torch.device(device).type == "cuda" and hasattr(ops, "repetition_penalty_counts")
+                               and hasattr(ops, "count_tokens"))
+        self._counts: Optional[torch.Tensor] = None
+        self._slots = {}
+        self._free_slots: List[int] = []
+
+    def forget(self, key) -> None:
+        """The request of this name has ended: what was kept of its history is given up."""
+        self._histories.pop(key, None)
+        slot = self._slots.pop(key, None)
+        if slot is not None:
+            self._free_slots.append(slot)
+
+    def _slot_of(self, key, history, vocab: int, live) -> int:
+        """The request's row in the table of counts; a new one starts from the history it brings (empty as a rule)."""
+        slot = self._slots.get(key)
+        if slot is not None:
+            return slot
+        if not self._free_slots:
+            for k in [k for k in self._slots if k not in live]:     # requests that ended without a word
+                self.forget(k)
+        if not self._free_slots:
+            old = 0 if self._counts is None else self._counts.shape[0]
+            grown = torch.zeros((max(2 * old, 16), vocab), dtype=torch.int32, device=self.device)
+            if old:
+                grown[:old].copy_(self._counts)
+            self._counts = grown
+            self._free_slots = list(range(grown.shape[0] - 1, old - 1, -1))
+        slot = self._free_slots.pop()
+        self._slots[key] = slot
+        self._counts[slot].zero_()
+        if history:
+            toks = torch.tensor([t for t in history if 0 <= t < vocab], dtype=torch.long, device=self.device)
+            self._counts[slot].index_put_((toks,), torch.ones_like(toks, dtype=torch.int32), accumulate=True)
+        return slot
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], indices: Sequence[int],
                histories: Sequence[Sequence[int]]) -> List[int]:
@@ -173,7 +210,18 @@ class Sampler:
                 return self._staging.send(parts)
             return [torch.from_numpy(np.ascontiguousarray(p)).to(self.device) for p in parts]
 
-        if any(p.repetition_penalty != 1.0 for p in params):
+        penalised = any(p.repetition_penalty != 1.0 for p in params)
+        slots_dev = None
+        if penalised and on_cuda and self.device_history and keys is not None:
+            # the histories live on the device: the penalty reads the requests' rows of the table of counts, and
+            # the tokens sampled below are counted there, so nothing of this waits for a token to reach the host
+            live = set(keys)
+            slots = [self._slot_of(k, h, logits.shape[1], live) if p.repetition_penalty != 1.0 else -1
+                     for k, p, h in zip(keys, params, histories)]
+            slots_dev, pen = to_device([np.asarray(slots, dtype=np.int32),
+                                        np.asarray([p.repetition_penalty for p in params], dtype=np.float32)])
+            logits = self.ops.repetition_penalty_counts(logits, self._counts, slots_dev, pen)
+        elif penalised:
             toks, counts, offsets = [], [], [0]
             for r, (p, hist) in enumerate(zip(params, histories)):
                 if p.repetition_penalty != 1.0:
@@ -206,4 +254,6 @@ class Sampler:
                 np.asarray([p.top_p for p in params], dtype=np.float32),
                 uniforms([p.seed for p in params], indices)])
             ids = self.ops.sample(logits, temperature, top_k, top_p, u, **extra)
+        if slots_dev is not None:
+            self.ops.count_tokens(self._counts, ids, slots_dev, R)
         return ids
