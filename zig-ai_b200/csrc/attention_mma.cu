@@ -717,9 +717,12 @@ __global__ void __launch_bounds__(NTHREADS) decode_fused_kernel(const FusedDecod
     }
 
     // ---- the last block of this (request, key/value head) combines the chunks
-    __threadfence();
+    // (one fence, by the thread that takes the ticket, behind the block's barrier: the fence is cumulative)
     __syncthreads();
-    if (tid == 0) s_ticket = atomicAdd(&a.tickets[b * Hkv + hk], 1);
+    if (tid == 0) {
+        __threadfence();
+        s_ticket = atomicAdd(&a.tickets[b * Hkv + hk], 1);
+    }
     __syncthreads();
     if (s_ticket != n_chunks - 1) return;
     __threadfence();

@@ -509,9 +509,11 @@ __global__ void __launch_bounds__(AT_THREADS) prefill_tc_kernel(const __grid_con
                 for (int j = 0; j < 32; ++j) po[(c0 + j) * AT_BM + row] = __uint_as_float(r[j]);
             }
         }
-        __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");          // the four softmax warps
-        if (tid == 64) s_seq = atomicAdd(a.tickets + slot, 1);
+        if (tid == 64) {
+            __threadfence();                                    // (one fence behind the barrier: it is cumulative)
+            s_seq = atomicAdd(a.tickets + slot, 1);
+        }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (s_seq == a.splits - 1) {
             __threadfence();

@@ -375,9 +375,14 @@ __global__ void __maxnreg__(128) decode_tma_kernel(const __grid_constant__ CUten
     if (tid == 0 && failed_flag) zai_raise(a.status, ZAI_ST_WAIT);
 
     // ---- the last block of this (request, key/value head) combines the chunks
-    __threadfence();
+    // (one fence, by the thread that takes the ticket, behind the block's barrier: the barrier puts every
+    // thread's stores before it and the fence is cumulative; a fence in every thread costs each of them the
+    // wait for the memory system, which is busy with the other blocks' keys)
     __syncthreads();
-    if (tid == 0) s_ticket = atomicAdd(&a.tickets[b * Hkv + hk], 1);
+    if (tid == 0) {
+        __threadfence();
+        s_ticket = atomicAdd(&a.tickets[b * Hkv + hk], 1);
+    }
     __syncthreads();
     if (s_ticket != n_chunks - 1) return;
     __threadfence();
