@@ -114,15 +114,21 @@ def main(argv=None) -> int:
                  max_tokens=args.num_pages * args.page_size if args.num_pages else None, profile=args.profile,
                  unexpected_tensors="warn" if args.allow_unused_tensors else "error")
     print(f"[+] model {args.model}: {eng.config.architecture}, dtype {args.dtype}, {len(prompts)} sequence(s)")
+    if torch.cuda.is_available() and not args.profile:
+        t_w = time.perf_counter()
+        eng.warm_up(min(len(prompts), n_seqs))               # (first calls and the decode graph: not the prompts' time)
+        torch.cuda.synchronize()
+        print(f"[+] warm-up: {(time.perf_counter() - t_w) * 1e3:.0f} ms")
     ids = [eng.add_request(p, SamplingParams(
         temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
         repetition_penalty=args.repetition_penalty, seed=args.seed + i, max_new_tokens=args.max_tokens,
         eos_id=args.eos_id)) for i, p in enumerate(prompts)]
+    gen0 = eng.n_generated
     done, t0, t_first = {}, time.perf_counter(), None
     while len(done) < len(ids):
         for r in eng.step():
             done[r.request_id] = r
-        if t_first is None and eng.n_generated > 0:
+        if t_first is None and eng.n_generated > gen0:
             torch.cuda.synchronize()
             t_first = time.perf_counter()
     eng.flush()

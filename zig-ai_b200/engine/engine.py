@@ -239,6 +239,20 @@ class Engine:
             raise RuntimeError(f"{len(failed)} request(s) could not be served: out of pages")
         return [done[i].output for i in ids]
 
+    def warm_up(self, n_seqs: int = 1) -> None:
+        """What only the first steps pay (libraries' first calls, the capture of the decode graph for `n_seqs`
+        requests), paid now: a request of two tokens is run to its second new token, and the graph of the bucket is
+        captured from a dry run.  For a caller that wants its first request timed like the ones after it."""
+        rid = self.add_request([0, 0], SamplingParams(temperature=0.0, max_new_tokens=2), request_id=("warm-up", self._next_id))
+        while rid in self.requests:
+            self.step()
+        self.flush()
+        graphs = getattr(self.runner, "graphs", None)
+        if graphs is not None and getattr(self.runner, "use_graphs", False):
+            bucket = graphs.bucket(max(int(n_seqs), 1))
+            if bucket is not None and bucket not in graphs.graphs:
+                graphs._capture(bucket)
+
     def profile_report(self) -> Dict[str, Dict[str, float]]:
         """With `profile=True`: per kind of step, the number of steps and tokens and the milliseconds
         its kernels took by class (the reference's PERF_STAGE table, src/main.zig:1369-1412)."""
