@@ -140,9 +140,17 @@ def main(argv=None) -> int:
     n_prompt = sum(len(p) for p in prompts)
     prefill_ms = ((t_first or t1) - t0) * 1e3
     decode_s = max(t1 - (t_first or t1), 1e-9)
-    print(f"[+] prefill: {n_prompt} tokens in {prefill_ms:.1f} ms ({n_prompt / max(prefill_ms, 1e-6) * 1e3:.1f} tok/s)")
-    print(f"[+] decode: {max(n_gen - len(ids), 0)} tokens in {decode_s * 1e3:.1f} ms "
-          f"({max(n_gen - len(ids), 0) / decode_s:.1f} tok/s)")
+    if len(ids) == 1:
+        print(f"[+] prefill: {n_prompt} tokens in {prefill_ms:.1f} ms ({n_prompt / max(prefill_ms, 1e-6) * 1e3:.1f} tok/s)")
+        print(f"[+] decode: {max(n_gen - len(ids), 0)} tokens in {decode_s * 1e3:.1f} ms "
+              f"({max(n_gen - len(ids), 0) / decode_s:.1f} tok/s)")
+    else:
+        # with several prompts their portions run beside the decoding of the ones that are through, so there is no
+        # prefill time apart from the decode time: the first token's time, and the whole
+        total_s = max(t1 - t0, 1e-9)
+        print(f"[+] prefill: first token after {prefill_ms:.1f} ms; {n_prompt} prompt tokens in portions beside decoding")
+        print(f"[+] decode: {n_gen} tokens of {len(ids)} sequences in {total_s * 1e3:.1f} ms ({n_gen / total_s:.1f} tok/s; "
+              f"{(n_gen + n_prompt) / total_s:.1f} tok/s with the prompts)")
     st = eng.stats()
     print(f"[+] cache: {eng.runner.cache.num_pages} pages of {args.page_size} positions, high water "
           + ", ".join(f"{v}" for k, v in st.items() if k.endswith("_pages_high_water")) + f"; {st['preemptions']} preemption(s)")
