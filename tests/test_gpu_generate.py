@@ -133,7 +133,26 @@ def test_command_line(tiny_models):
     line = next(l for l in out.stdout.splitlines() if l.startswith("[0]"))
     ids = [int(x) for x in line.split(")")[1].split()]
     assert ids == plain_greedy(tiny_models["A"], [5, 17, 3], 6)
-    assert "decode:" in out.stdout and "prefill:" in out.stdout
+    assert "decode:" in out.stdout and "prefill:" in out.stdout and "warm-up:" in out.stdout
+
+
+def test_warm_up_leaves_nothing_behind(tiny_models):
+    """Engine.warm_up runs a request of its own and captures the bucket's decode graph; afterwards no request, page
+    or slot is held, request ids start where they would have, and generation gives the tokens it gives without it."""
+    import zig_ai_b200 as z
+    prompts = [[5, 17, 3], [9, 1, 200, 7, 7, 41]]
+    want = [plain_greedy(tiny_models["A"], p, 6) for p in prompts]
+    eng = z.Engine(tiny_models["A"], "float32", max_num_seqs=2, max_batched_tokens=8, max_model_len=64, page_size=PAGE_SIZE["A"])
+    eng.warm_up(2)
+    assert not eng.requests and not eng.has_work()
+    assert eng.runner.graphs.bucket(2) in eng.runner.graphs.graphs
+    assert all(v == 0 for k, v in eng.stats().items() if k.endswith("pages_used"))
+    from zig_ai_b200.sampling import SamplingParams
+    assert eng.add_request(prompts[0], SamplingParams(temperature=0.0, max_new_tokens=2)) == 0    # (the warm-up request took a name of its own)
+    while eng.has_work():
+        eng.step()
+    eng.flush()
+    assert eng.generate(prompts, max_new_tokens=6, temperature=0.0) == want
 
 
 def test_command_line_sizes_the_pool_and_profiles(tiny_models):
@@ -149,6 +168,7 @@ def test_command_line_sizes_the_pool_and_profiles(tiny_models):
     lines = [l for l in out.stdout.splitlines() if l.startswith("[") and ") " in l and not l.startswith("[+]")]
     assert len(lines) == 4 and all([int(x) for x in l.split(")")[1].split()] == want for l in lines)
     assert "12 pages of 8 positions" in out.stdout
+    assert "tokens of 4 sequences" in out.stdout and "first token after" in out.stdout
     out = subprocess.run(base + ["--dtype", "bfloat16", "--profile"], capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stderr
     prof = [l for l in out.stdout.splitlines() if l.startswith("[profile]")]
