@@ -272,7 +272,7 @@ def test_argmax_first_maximum(R, V):
     assert int(o.argmax(logits)[0]) == V // 3
 
 
-@pytest.mark.parametrize("V", [517, 65536])
+@pytest.mark.parametrize("V", [517, 16391, 50001, 65536])
 def test_sampling_matches_plain_version(V):
     o = ops()
     g = torch.Generator().manual_seed(13)
@@ -297,6 +297,28 @@ def test_sampling_matches_plain_version(V):
             ok = any(_u_in_interval(p, int(a[r]), float(u[r])) for p in _kept_distributions(
                 logits[r].double().cpu(), float(temperature[r]), int(top_k[r]), float(top_p[r])))
             assert ok, (trial, r, int(a[r]), int(b[r]))
+
+
+def test_sampling_many_rows_one_block_a_row():
+    """More than 32 rows run with one block a row (fewer share a row among a cluster of eight blocks): the same
+    checks at 40 rows with every kind of selection, some rows with a kept set beyond the list."""
+    o = ops()
+    V, R = 20011, 40
+    g = torch.Generator().manual_seed(213)
+    logits = (torch.randn(R, V, generator=g) * 3).cuda()
+    temperature = torch.tensor([[0.0, 1.0, 0.7, 1.3, 2.5][r % 5] for r in range(R)]).cuda()
+    top_k = torch.tensor([[0, 40, 0, 5, 6000, 1, 0, 300][r % 8] for r in range(R)], dtype=torch.int32).cuda()
+    top_p = torch.tensor([[1.0, 1.0, 0.9, 0.5, 0.95, 1.0, 0.3][r % 7] for r in range(R)]).cuda()
+    u = torch.rand(R, generator=g).cuda()
+    a = o.sample(logits, temperature, top_k, top_p, u).cpu()
+    b = ref_ops.sample(logits.cpu(), temperature.cpu(), top_k.cpu(), top_p.cpu(), u.cpu())
+    for r in range(R):
+        if int(a[r]) == int(b[r]):
+            continue
+        assert float(temperature[r]) > 0
+        ok = any(_u_in_interval(p, int(a[r]), float(u[r])) for p in _kept_distributions(
+            logits[r].double().cpu(), float(temperature[r]), int(top_k[r]), float(top_p[r])))
+        assert ok, (r, int(a[r]), int(b[r]))
 
 
 def test_sampling_large_kept_sets():
