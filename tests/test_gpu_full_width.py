@@ -92,3 +92,52 @@ def test_benchmark_layer_sizes_against_plain(full_width_models, width, dtype):
     for k in toks:
         want = plain_lfm2.forward(c, W, toks[k], rows=rows[k]).numpy()
         traces.check_request(np.stack(got[k]), want, dtype, f"{dtype} request {k}")
+
+
+@pytest.mark.parametrize("width,page_size", [("350m", 64), ("1.2b", 16)])
+def test_serving_at_full_width_leaves_nothing_behind(full_width_models, width, page_size):
+    """A hundred and twenty requests of 3 to 4000 prompt tokens, greedy and sampled (top-k, top-p, repetition
+    penalty), arriving while others run, through a pool too small for all of them at once: every request ends with the length
+    it asked for (or is refused pages it can never have), the kernels' status word stays clear, and no page, state
+    slot or row of the sampler's table of counts is held at the end."""
+    import torch
+    import zig_ai_b200 as z
+    from zig_ai_b200.kernels import ops
+    from zig_ai_b200.sampling import SamplingParams
+    d = full_width_models(width)
+    g = random.Random(7)
+    eng = z.Engine(d, "bfloat16", max_num_seqs=24, max_batched_tokens=1024, max_model_len=4096, max_tokens=24 * 1024,
+                   page_size=page_size)
+    V = 65536
+    pending = []
+    for i in range(120):
+        n = g.choice([3, 17, 64, 200, 700, 1500, 3500]) + g.randrange(50)
+        sp = dict(max_new_tokens=g.choice([1, 8, 40, 150]), seed=i)
+        kind = g.randrange(5)
+        if kind == 0:
+            sp.update(temperature=0.0)
+        elif kind == 1:
+            sp.update(temperature=0.9)
+        elif kind == 2:
+            sp.update(temperature=0.8, top_k=g.choice([1, 40, 5000]), top_p=g.choice([1.0, 0.9]))
+        elif kind == 3:
+            sp.update(temperature=1.2, top_p=0.95, repetition_penalty=1.2)
+        else:
+            sp.update(temperature=0.0, repetition_penalty=1.5)
+        pending.append(([g.randrange(V) for _ in range(n)], SamplingParams(**sp)))
+    done, added, asked = 0, 0, {}
+    while done < len(pending):
+        while added < len(pending) and (g.random() < 0.3 or not eng.has_work()):
+            rid = eng.add_request(*pending[added])
+            asked[rid] = pending[added][1].max_new_tokens
+            added += 1
+        for r in eng.step():
+            done += 1
+            assert r.finish_reason in ("length", "out_of_pages"), r.finish_reason
+            assert r.finish_reason != "length" or len(r.output) == asked[r.request_id]
+    eng.flush()
+    torch.cuda.synchronize()
+    st = eng.stats()
+    assert ops.read_status() == 0
+    assert not eng.sampler._slots and not eng.requests
+    assert all(v == 0 for k, v in st.items() if k.endswith("pages_used"))
